@@ -1,0 +1,147 @@
+/*
+ * sc_b200 - C ABI of the B200-native SparseCore embedding path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns an
+ * int32 status (SC_OK == 0) and never throws or aborts.  Pointers named "device"
+ * are CUDA device pointers of the current device; everything else is host
+ * memory.  No entry point allocates: scratch memory is a caller-owned device
+ * workspace whose size comes from the matching *_workspace_bytes query.  Work is
+ * enqueued on the given stream (a cudaStream_t passed as void*; NULL = default
+ * stream) and is asynchronous unless stated otherwise.
+ *
+ * Each declaration cites the interface of the reference project
+ * (jax-ml/jax-tpu-embedding, paths relative to jax_tpu_embedding/sparsecore/)
+ * that it replaces.
+ */
+#ifndef SC_B200_H_
+#define SC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* sc_stream_t;
+
+enum sc_status {
+  SC_OK = 0,
+  SC_INVALID_ARGUMENT = 1,    /* maps to ValueError, like absl::InvalidArgument in pybind_input_preprocessing.cc:163-170 */
+  SC_WORKSPACE_TOO_SMALL = 2,
+  SC_ID_LIMIT_EXCEEDED = 3,   /* the reference LOG(FATAL)s: sort_and_group_coo_tensors_impl.h:61-68 */
+  SC_CUDA_ERROR = 4,          /* maps to RuntimeError */
+  SC_UNSUPPORTED = 5
+};
+
+enum sc_combiner { SC_COMBINER_SUM = 0, SC_COMBINER_MEAN = 1, SC_COMBINER_SQRTN = 2 };
+
+#define SC_MAX_SHARDS 64       /* largest num_scs one call can address */
+#define SC_MAX_FEATURES 1024   /* features per stacked table in one preprocessing call */
+#define SC_PADDING_VALUE 2147483647 /* lib/core/constants.py:17 */
+
+/* Library identification and the message of the last failing call on this thread. */
+int32_t sc_version(void);
+const char* sc_status_name(int32_t status);
+int32_t sc_last_error(char* buffer, int32_t buffer_bytes);
+
+/* ---------------------------------------------------------------- buffer sizing
+ * Replaces ComputeCooBufferSizePerDevice / GetRowPointersSizePerDevice
+ * (lib/core/input_preprocessing_util.cc:242-312, input_preprocessing_util.h:503-511;
+ * Python bindings pybind_input_preprocessing.cc:218-253).  Host arithmetic only.
+ * A negative result means the suggested size exceeds the theoretical maximum or
+ * the size leaves (0, INT_MAX). */
+int64_t sc_compute_theoretical_max_coo_buffer_size(int32_t max_ids_per_partition, int32_t global_device_count,
+                                                   int32_t num_sc_per_device);
+int64_t sc_compute_coo_buffer_size_per_device(int32_t max_ids_per_partition, int32_t global_device_count,
+                                              int32_t num_sc_per_device, int64_t suggested_or_negative);
+int32_t sc_compute_row_pointers_size_per_device(int32_t global_device_count, int32_t num_sc_per_device);
+
+/* ---------------------------------------------------------------- preprocessing
+ * Replaces PreprocessSparseDenseMatmulInput for one stacked table and one local
+ * device (lib/core/input_preprocessing.h:62-68, input_preprocessing.cc:800-959):
+ * extract -> sort by (SparseCore, shard, row of the shard, sample) -> dedup with
+ * f32 gain sums -> optional id dropping -> stats -> CSR-wrapped COO buffers,
+ * bit-exact with the reference over the region the reference writes.  The rest of
+ * each buffer is filled with (SC_PADDING_VALUE, SC_PADDING_VALUE, NaN).
+ *
+ * The batch of the device is given as one CSR: `ids`/`weights` hold the ids of
+ * all features back to back (features ordered by row_offset, rows in order) and
+ * `row_offsets[total_rows + 1]` delimits the rows. */
+typedef struct {
+  int32_t row_begin;  /* first row of this feature inside row_offsets */
+  int32_t rows;       /* rows of this feature held by the device (divisible by num_sc_per_device) */
+  int32_t row_offset; /* FeatureIdTransformation.row_offset (global samples before this feature) */
+  int32_t col_offset; /* row_offset_in_shard * num_scs of the feature's table */
+  int32_t col_shift;  /* shard rotation of the feature's table */
+} sc_feature_desc_t;
+
+typedef struct {
+  int32_t global_device_count;
+  int32_t num_sc_per_device;
+  int32_t combiner;                      /* enum sc_combiner */
+  int32_t max_ids_per_partition;
+  int32_t max_unique_ids_per_partition;
+  int32_t allow_id_dropping;
+  int32_t coo_buffer_size_per_device;    /* from sc_compute_coo_buffer_size_per_device */
+  int32_t stack_vocab_size;              /* padded vocabulary of the stack; bounds the sort key */
+} sc_preprocess_options_t;
+
+/* Layout of the int32 stats block written on the device (P = num_scs, S = num_sc_per_device):
+ * [0, P) ids per partition (max over local SparseCores), [P, 2P) unique ids per partition,
+ * [2P, 2P+S) required buffer size per SparseCore, [2P+S] dropped id count,
+ * [2P+S+1] status (SC_OK or SC_ID_LIMIT_EXCEEDED), [2P+S+2] ids written to the buffers. */
+int32_t sc_preprocess_stats_size(int32_t global_device_count, int32_t num_sc_per_device);
+size_t sc_preprocess_workspace_bytes(int64_t nnz, int64_t total_rows, const sc_preprocess_options_t* options);
+int32_t sc_preprocess_table(const int32_t* ids_device, const int32_t* row_offsets_device, const float* weights_device_or_null,
+                            int64_t nnz, int64_t total_rows, const sc_feature_desc_t* features_host, int32_t num_features,
+                            const sc_preprocess_options_t* options, int32_t* row_pointers_device,
+                            int32_t* embedding_ids_device, int32_t* sample_ids_device, float* gains_device,
+                            int32_t* stats_device, void* workspace_device, size_t workspace_bytes, sc_stream_t stream);
+
+/* ---------------------------------------------------------------- lookup / update
+ * One device buffer of CSR-wrapped COO input plus the geometry of the stacked table. */
+typedef struct {
+  const int32_t* row_pointers;   /* device, [num_sc_per_device * max(num_scs, 8)] */
+  const int32_t* embedding_ids;  /* device, [coo_buffer_size] row inside the destination shard */
+  const int32_t* sample_ids;     /* device, [coo_buffer_size] sample inside the source SparseCore */
+  const float* gains;            /* device, [coo_buffer_size] */
+  int32_t coo_buffer_size;
+  int32_t num_sc_per_device;
+  int32_t num_scs;
+  int32_t device_batch_size;     /* samples of the stack on this device */
+  int32_t dim;                   /* floats per table row */
+  int32_t max_ids_per_sample;    /* 1: at most one id per sample (enables the store-only forward); 0: unknown */
+  int64_t rows_per_shard;
+} sc_csr_t;
+
+/* Forward: activations[s * B/S + sample] = sum gain * shard[g][embedding_id].
+ * Replaces the custom call "SparseDenseMatmulOp" behind
+ * tpu_sparse_dense_matmul_csr_primitive (lib/core/primitives/sparse_dense_matmul_csr.py:114-207).
+ * `shard_tables_host[g]` is the device pointer of shard g ([rows_per_shard, dim] floats). */
+size_t sc_sparse_dense_matmul_fwd_workspace_bytes(const sc_csr_t* csr);
+int32_t sc_sparse_dense_matmul_fwd(const sc_csr_t* csr, const float* const* shard_tables_host, float* activations_device,
+                                   void* workspace_device, size_t workspace_bytes, sc_stream_t stream);
+
+/* Backward fused with the optimizer: G[row] = sum gain * activation_grad[sample] over every
+ * entry of the row, then ONE update of the row and its slot variables, in place;
+ * untouched rows keep their values.  Replaces "SparseDenseMatmulGradOpWithOptimizerUpdate"
+ * behind the sgd / adagrad / adam primitives (lib/core/primitives/
+ * sparse_dense_matmul_grad_with_sgd.py:98-238, ..._adagrad.py:119-292, ..._adam.py:144-405).
+ * clip_min / clip_max clamp the table only (primitives/utils.py:24-59); pass NaN for "no bound". */
+typedef struct {
+  int32_t optimizer;      /* 0 sgd, 1 adagrad, 2 adam */
+  float hyper[4];         /* sgd/adagrad: {learning_rate}; adam: {alpha_t, beta_1, beta_2, epsilon_hat} */
+  float clip_min, clip_max;
+} sc_optimizer_t;
+
+size_t sc_sparse_dense_matmul_grad_workspace_bytes(const sc_csr_t* csr);
+int32_t sc_sparse_dense_matmul_grad(const sc_csr_t* csr, const float* activation_grad_device,
+                                    float* const* shard_tables_host, float* const* shard_slot0_host,
+                                    float* const* shard_slot1_host, const sc_optimizer_t* optimizer,
+                                    void* workspace_device, size_t workspace_bytes, sc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SC_B200_H_ */

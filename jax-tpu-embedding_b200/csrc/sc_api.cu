@@ -1,0 +1,87 @@
+// Library-wide entry points: version, status names, last-error text and the host-side
+// buffer sizing arithmetic.
+#include <stdarg.h>
+#include <string.h>
+
+#include "sc_common.cuh"
+
+namespace sc {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace sc
+
+extern "C" int32_t sc_version(void) { return 100; }
+
+extern "C" const char* sc_status_name(int32_t status) {
+  switch (status) {
+    case SC_OK: return "OK";
+    case SC_INVALID_ARGUMENT: return "INVALID_ARGUMENT";
+    case SC_WORKSPACE_TOO_SMALL: return "WORKSPACE_TOO_SMALL";
+    case SC_ID_LIMIT_EXCEEDED: return "ID_LIMIT_EXCEEDED";
+    case SC_CUDA_ERROR: return "CUDA_ERROR";
+    case SC_UNSUPPORTED: return "UNSUPPORTED";
+    default: return "UNKNOWN";
+  }
+}
+
+extern "C" int32_t sc_last_error(char* buffer, int32_t buffer_bytes) {
+  if (!buffer || buffer_bytes <= 0) return (int32_t)strlen(sc::g_error);
+  strncpy(buffer, sc::g_error, (size_t)buffer_bytes - 1);
+  buffer[buffer_bytes - 1] = '\0';
+  return (int32_t)strlen(buffer);
+}
+
+// ComputeTheoreticalMaxCooBufferSize (input_preprocessing_util.cc:242-254), minibatching off.
+extern "C" int64_t sc_compute_theoretical_max_coo_buffer_size(int32_t max_ids_per_partition, int32_t global_device_count,
+                                                              int32_t num_sc_per_device) {
+  const int64_t num_scs = (int64_t)global_device_count * num_sc_per_device;
+  const int64_t rounded = ((int64_t)max_ids_per_partition + sc::kAlign - 1) / sc::kAlign * sc::kAlign;
+  return rounded * num_sc_per_device * num_scs;
+}
+
+// ComputeCooBufferSizePerDevice + MayBeUpdateBufferSize (input_preprocessing_util.cc:219-312).
+extern "C" int64_t sc_compute_coo_buffer_size_per_device(int32_t max_ids_per_partition, int32_t global_device_count,
+                                                         int32_t num_sc_per_device, int64_t suggested) {
+  const int64_t theoretical = sc_compute_theoretical_max_coo_buffer_size(max_ids_per_partition, global_device_count, num_sc_per_device);
+  int64_t v = theoretical;
+  if (suggested >= 0) {
+    const int64_t m = (int64_t)sc::kAlign * num_sc_per_device;
+    v = (suggested + m - 1) / m * m;
+    if (v > theoretical) {
+      sc::set_error("Suggested Coo Buffer Size is larger than the theoretical max: %lld vs %lld. Adjust the suggested size or the "
+                    "max_ids_per_partition values.", (long long)v, (long long)theoretical);
+      return -1;
+    }
+  }
+  if (!(v > 0 && v < 2147483647LL)) {
+    sc::set_error("Computed Coo Buffer Size (%lld) is out of the valid range (0, INT_MAX).", (long long)v);
+    return -1;
+  }
+  return v;
+}
+
+// GetRowPointersSizePerDevice (input_preprocessing_util.h:503-511), minibatching off.
+extern "C" int32_t sc_compute_row_pointers_size_per_device(int32_t global_device_count, int32_t num_sc_per_device) {
+  const int32_t num_scs = global_device_count * num_sc_per_device;
+  return (num_scs > sc::kAlign ? num_scs : sc::kAlign) * num_sc_per_device;
+}

@@ -1,0 +1,67 @@
+// Shared helpers of the sc_b200 library: status/error plumbing and small device utilities.
+#ifndef SC_COMMON_CUH_
+#define SC_COMMON_CUH_
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "sc_b200.h"
+
+namespace sc {
+
+// Message of the last failing call on this host thread (returned by sc_last_error).
+void set_error(const char* fmt, ...);
+
+#define SC_FAIL(status, ...)      \
+  do {                            \
+    ::sc::set_error(__VA_ARGS__); \
+    return (status);              \
+  } while (0)
+
+#define SC_CUDA_OK(expr)                                                                      \
+  do {                                                                                        \
+    cudaError_t err__ = (expr);                                                               \
+    if (err__ != cudaSuccess) SC_FAIL(SC_CUDA_ERROR, "%s: %s", #expr, cudaGetErrorString(err__)); \
+  } while (0)
+
+#define SC_LAUNCH_OK(name)                                                                        \
+  do {                                                                                            \
+    cudaError_t err__ = cudaGetLastError();                                                       \
+    if (err__ != cudaSuccess) SC_FAIL(SC_CUDA_ERROR, "launch %s: %s", name, cudaGetErrorString(err__)); \
+  } while (0)
+
+constexpr int kAlign = 8;  // alignment (in slots) of every partition inside a COO buffer
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int bit_width_u32(uint32_t v) {
+  int b = 0;
+  while (v) { ++b; v >>= 1; }
+  return b;
+}
+
+// Carves typed, 256-byte aligned regions out of a caller-owned device workspace.
+class Workspace {
+ public:
+  Workspace(void* base, size_t bytes) : base_(static_cast<char*>(base)), bytes_(bytes) {}
+  template <typename T>
+  T* take(size_t count) {
+    size_t off = align_up(used_, 256);
+    used_ = off + count * sizeof(T);
+    return reinterpret_cast<T*>(base_ + off);  // valid only if ok()
+  }
+  size_t used() const { return align_up(used_, 256); }
+  bool ok() const { return base_ != nullptr && used() <= bytes_; }
+
+ private:
+  char* base_;
+  size_t bytes_;
+  size_t used_ = 0;
+};
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+}  // namespace sc
+#endif  // SC_COMMON_CUH_

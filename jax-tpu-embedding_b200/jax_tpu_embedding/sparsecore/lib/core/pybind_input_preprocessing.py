@@ -1,0 +1,365 @@
+"""Input preprocessing front end: same module name and call signatures as the
+reference's pybind11 extension, executed by CUDA kernels on the current device.
+
+Replaces jax_tpu_embedding/sparsecore/lib/core/pybind_input_preprocessing.cc
+(`preprocess_sparse_dense_matmul_input` :190-216 / :124-188,
+`compute_row_pointers_size_per_device` :218-229,
+`compute_theoretical_max_coo_buffer_size` :315, `compute_coo_buffer_size_per_device`
+:231-253, `SparseDenseMatmulInputStats` :320-330).  The host side only flattens the
+numpy inputs into one CSR per stacked table and local device; sorting, deduplication,
+id dropping, statistics and buffer filling run in `sc_preprocess_table`.
+
+Differences from the reference, all deliberate:
+  * exceeding `max_ids_per_partition` without `allow_id_dropping` raises ValueError
+    instead of aborting the process;
+  * slots past the last row pointer of a SparseCore slice hold padding
+    (PADDING_VALUE / NaN) instead of uninitialised memory;
+  * `device_output=True` keeps the four buffers on the GPU as torch tensors.
+Minibatching (and its `all_reduce_interface`) only exists to fit TPU on-chip memory
+and is rejected.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import dataclasses
+import enum
+from typing import Any, Sequence
+
+import numpy as np
+
+from jax_tpu_embedding.sparsecore import _native
+
+
+class ShardingStrategy(enum.IntEnum):
+  MOD = 1
+
+
+MOD = ShardingStrategy.MOD
+
+
+class AllReduceInterface:  # placeholder type for signature compatibility
+  pass
+
+
+@dataclasses.dataclass
+class RaggedInput:
+  """A ragged feature already in CSR form (values + row_splits), host or device memory.
+
+  Leaf type accepted wherever a feature array is expected; `weights` is optional.
+  Device tensors (torch, CUDA) are used in place without a host round trip.
+  """
+
+  values: Any  # int32 [nnz]
+  row_splits: Any  # int32/int64 [rows + 1]
+  weights: Any = None  # float32 [nnz]
+
+  @property
+  def shape(self):
+    return (len(self.row_splits) - 1,)
+
+
+class SparseDenseMatmulInputStats:
+  """Per stacked table: ids / unique ids per partition, required buffer sizes, drops."""
+
+  def __init__(self):
+    self.max_ids_per_partition: dict[str, np.ndarray] = {}
+    self.max_unique_ids_per_partition: dict[str, np.ndarray] = {}
+    self.required_buffer_sizes: dict[str, np.ndarray] = {}
+    self.dropped_id_count: dict[str, int] = {}
+
+
+def compute_row_pointers_size_per_device(global_device_count: int, num_sc_per_device: int,
+                                         enable_minibatching: bool = False) -> int:
+  _reject_minibatching(enable_minibatching)
+  return int(_native.lib().sc_compute_row_pointers_size_per_device(global_device_count, num_sc_per_device))
+
+
+def compute_theoretical_max_coo_buffer_size(max_ids_per_partition: int, global_device_count: int,
+                                            num_sc_per_device: int, enable_minibatching: bool = False) -> int:
+  _reject_minibatching(enable_minibatching)
+  return int(_native.lib().sc_compute_theoretical_max_coo_buffer_size(
+      max_ids_per_partition, global_device_count, num_sc_per_device))
+
+
+def _coo_buffer_size(max_ids: int, global_device_count: int, num_sc_per_device: int, suggested) -> int:
+  v = _native.lib().sc_compute_coo_buffer_size_per_device(
+      int(max_ids), int(global_device_count), int(num_sc_per_device), -1 if suggested is None else int(suggested))
+  if v < 0:
+    raise ValueError(_native.last_error())
+  return int(v)
+
+
+def compute_coo_buffer_size_per_device(feature_specs: Sequence[Any], global_device_count: int,
+                                       num_sc_per_device: int, enable_minibatching: bool = False) -> dict[str, int]:
+  _reject_minibatching(enable_minibatching)
+  out = {}
+  for name, members in _group_by_stack(feature_specs).items():
+    stacked = members[0][1].table_spec.stacked_table_spec
+    out[name] = _coo_buffer_size(stacked.max_ids_per_partition, global_device_count, num_sc_per_device,
+                                 stacked.suggested_coo_buffer_size_per_device)
+  return out
+
+
+def _reject_minibatching(enable_minibatching: bool) -> None:
+  if enable_minibatching:
+    raise NotImplementedError(
+        "enable_minibatching=True is not supported: minibatching splits a batch to fit TPU SparseCore "
+        "on-chip memory, a limit that does not exist on B200.")
+
+
+def _group_by_stack(feature_specs):
+  """{stack name: [(feature index, spec), ...] ordered by row_offset} (pybind...cc:55-122)."""
+  stacks: dict[str, list] = {}
+  for i, spec in enumerate(feature_specs):
+    name = spec.table_spec.setting_in_stack.stack_name
+    stacks.setdefault(name, []).append((i, spec))
+  for members in stacks.values():
+    members.sort(key=lambda m: _transform(m[1])[0])
+  return stacks
+
+
+def _transform(spec):
+  t = spec._id_transformation  # pylint: disable=protected-access
+  return (0, 0, 0) if t is None else (int(t.row_offset), int(t.col_offset), int(t.col_shift))
+
+
+# ------------------------------------------------------------------------------ host flattening
+
+
+def _is_torch(x) -> bool:
+  return type(x).__module__.startswith("torch")
+
+
+def _feature_rows(feature) -> int:
+  if isinstance(feature, RaggedInput):
+    return len(feature.row_splits) - 1
+  return feature.shape[0]
+
+
+def _slice_to_csr(feature, weights, lo: int, hi: int):
+  """Rows [lo, hi) of one feature as (ids, lengths-or-offsets..., weights) host arrays."""
+  if isinstance(feature, RaggedInput):
+    splits = feature.row_splits
+    b, e = int(splits[lo]), int(splits[hi])
+    w = feature.weights if feature.weights is not None else weights
+    return feature.values[b:e], splits[lo:hi + 1] - splits[lo], (None if w is None else w[b:e])
+  arr = np.asarray(feature)
+  if arr.dtype != object and arr.ndim == 2:
+    rows = arr[lo:hi]
+    ids = np.ascontiguousarray(rows, dtype=np.int32).reshape(-1)
+    offsets = np.arange(hi - lo + 1, dtype=np.int64) * arr.shape[1]
+    w = None
+    if weights is not None:
+      w = np.ascontiguousarray(np.asarray(weights)[lo:hi], dtype=np.float32).reshape(-1)
+    return ids, offsets, w
+  if arr.ndim != 1:
+    raise ValueError("Only 1D and 2D numpy arrays supported as inputs.")
+  rows = [np.asarray(r, dtype=np.int32).reshape(-1) for r in arr[lo:hi]]
+  lens = np.fromiter((len(r) for r in rows), dtype=np.int64, count=len(rows))
+  offsets = np.zeros(len(rows) + 1, dtype=np.int64)
+  np.cumsum(lens, out=offsets[1:])
+  ids = np.concatenate(rows) if rows else np.zeros(0, np.int32)
+  w = None
+  if weights is not None:
+    wr = [np.asarray(r, dtype=np.float32).reshape(-1) for r in np.asarray(weights, dtype=object)[lo:hi]]
+    w = np.concatenate(wr) if wr else np.zeros(0, np.float32)
+    if len(w) != len(ids):
+      raise ValueError("Dimension mismatch for features and weights")
+  return ids, offsets, w
+
+
+def _concat(parts, dtype):
+  torch = _native.torch_mod()
+  if any(_is_torch(p) for p in parts):
+    tdt = {np.int32: torch.int32, np.float32: torch.float32}[dtype]
+    ts = [p.to(device="cuda", dtype=tdt) if _is_torch(p) else torch.from_numpy(np.ascontiguousarray(p, dtype=dtype)).cuda()
+          for p in parts]
+    return ts[0] if len(ts) == 1 else torch.cat(ts)
+  arrs = [np.ascontiguousarray(p, dtype=dtype) for p in parts]
+  return arrs[0] if len(arrs) == 1 else np.concatenate(arrs)
+
+
+def _to_cuda(x, tdt):
+  torch = _native.torch_mod()
+  if _is_torch(x):
+    return x.to(device="cuda", dtype=tdt).contiguous()
+  return torch.from_numpy(np.ascontiguousarray(x)).to(device="cuda", dtype=tdt, non_blocking=True)
+
+
+# ------------------------------------------------------------------------------ device call
+
+
+def preprocess_stack_on_device(ids, row_offsets, weights, feature_descs, *, global_device_count: int,
+                               num_sc_per_device: int, combiner: str, max_ids_per_partition: int,
+                               max_unique_ids_per_partition: int, allow_id_dropping: bool,
+                               coo_buffer_size_per_device: int, stack_vocab_size: int, outputs=None):
+  """Runs `sc_preprocess_table` for one stacked table and one device, asynchronously.
+
+  Args:
+    ids, row_offsets, weights: CUDA int32 / int32 / float32 (or None) tensors, the CSR of the
+      device's rows with the features of the stack back to back in row_offset order.
+    feature_descs: list of (rows, row_offset, col_offset, col_shift) per feature.
+    outputs: optional (row_pointers, embedding_ids, sample_ids, gains) tensors to fill.
+
+  Returns:
+    (row_pointers, embedding_ids, sample_ids, gains, stats) CUDA tensors; `stats` is the
+    int32 block described in include/sc_b200.h.  Nothing is synchronised.
+  """
+  torch = _native.require_cuda()
+  lib = _native.lib()
+  nfeat = len(feature_descs)
+  descs = (_native.FeatureDesc * nfeat)()
+  row = 0
+  for i, (rows, row_offset, col_offset, col_shift) in enumerate(feature_descs):
+    descs[i] = _native.FeatureDesc(row, int(rows), int(row_offset), int(col_offset), int(col_shift))
+    row += int(rows)
+  total_rows = row
+  nnz = int(ids.numel())
+  if row_offsets.numel() != total_rows + 1:
+    raise ValueError("row_offsets must have one entry per row plus one")
+  opt = _native.PreprocessOptions(int(global_device_count), int(num_sc_per_device), _native.COMBINERS.get(combiner, 0),
+                                  int(max_ids_per_partition), int(max_unique_ids_per_partition),
+                                  int(bool(allow_id_dropping)), int(coo_buffer_size_per_device), int(stack_vocab_size))
+  p = global_device_count * num_sc_per_device
+  rp_size = max(p, 8) * num_sc_per_device
+  if outputs is None:
+    dev = ids.device
+    outputs = (torch.empty(rp_size, dtype=torch.int32, device=dev),
+               torch.empty(coo_buffer_size_per_device, dtype=torch.int32, device=dev),
+               torch.empty(coo_buffer_size_per_device, dtype=torch.int32, device=dev),
+               torch.empty(coo_buffer_size_per_device, dtype=torch.float32, device=dev))
+  rp, eids, sids, gains = outputs
+  stats = torch.empty(2 * p + num_sc_per_device + 3, dtype=torch.int32, device=ids.device)
+  nbytes = lib.sc_preprocess_workspace_bytes(nnz, total_rows, ctypes.byref(opt))
+  if nbytes == 0:
+    _native.check(_native.SC_INVALID_ARGUMENT)
+  ws = _native.workspace(nbytes, "preprocess")
+  status = lib.sc_preprocess_table(
+      ids.data_ptr() if nnz else None, row_offsets.data_ptr(), None if weights is None else weights.data_ptr(), nnz,
+      total_rows, descs, nfeat, ctypes.byref(opt), rp.data_ptr(), eids.data_ptr(), sids.data_ptr(), gains.data_ptr(),
+      stats.data_ptr(), ws.data_ptr(), ws.numel(), _native.current_stream_ptr())
+  _native.check(status)
+  return rp, eids, sids, gains, stats
+
+
+def _raise_for_status(stats_host: np.ndarray, p: int, s: int, table: str, max_ids: int, max_unique: int) -> None:
+  status = int(stats_host[2 * p + s + 1])
+  if status == _native.SC_OK:
+    return
+  if status == _native.SC_ID_LIMIT_EXCEEDED:
+    obs_ids, obs_unique = int(stats_host[:p].max()), int(stats_host[p:2 * p].max())
+    if obs_ids > max_ids:
+      raise ValueError(
+          f"Observed max ids per partition: {obs_ids} for table: {table} is greater than the set max ids per "
+          f"partition: {max_ids}. Use `allow_id_dropping` or increase the `max_ids_per_partition`. You could "
+          "also try to reduce the batch size.")
+    raise ValueError(
+        f"Observed max unique ids per partition: {obs_unique} for table: {table} is greater than the set max "
+        f"unique ids per partition: {max_unique}. Use `allow_id_dropping` or increase the "
+        "`max_ids_per_partition`. You could also try to reduce the batch size.")
+  raise ValueError(
+      f"Invalid input for table {table}: an embedding id is negative or outside the stacked vocabulary, or the "
+      "feature row offsets do not match the batch.")
+
+
+def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_specs, local_device_count: int,
+                                         global_device_count: int, *, num_sc_per_device: int,
+                                         sharding_strategy: ShardingStrategy = ShardingStrategy.MOD,
+                                         has_leading_dimension: bool = False, allow_id_dropping: bool = False,
+                                         batch_number: int = 0, enable_minibatching: bool = False,
+                                         all_reduce_interface=None, device_output: bool = False):
+  """Flat lists of features / weights / specs -> (row_pointers, embedding_ids, sample_ids, gains,
+  num_minibatches, stats), the first four being dicts keyed by stacked table name."""
+  del batch_number, all_reduce_interface
+  _reject_minibatching(enable_minibatching)
+  if int(sharding_strategy) != int(ShardingStrategy.MOD):
+    raise ValueError("Only mod sharding is supported for now.")
+  # PreprocessSparseDenseMatmulInputOptions::Validate (input_preprocessing_util.cc:490-522).
+  if local_device_count <= 0:
+    raise ValueError(f"local_device_count must be greater than 0, but got {local_device_count}")
+  if global_device_count <= 0:
+    raise ValueError(f"global_device_count must be greater than 0, but got {global_device_count}")
+  if global_device_count < local_device_count:
+    raise ValueError(
+        "global_device_count must be greater than or equal to local_device_count, but got "
+        f"{global_device_count} vs {local_device_count}")
+  if num_sc_per_device <= 0:
+    raise ValueError(f"num_sc_per_device must be greater than 0, but got {num_sc_per_device}")
+  p = num_sc_per_device * global_device_count
+  if p & (p - 1):
+    raise ValueError(f"Total number of SparseCores ({p}) must be a power of 2.")
+  features = list(features)
+  if not features:
+    raise ValueError("input_batches cannot be empty.")
+  feature_specs = list(feature_specs)
+  if feature_weights is not None:
+    feature_weights = list(feature_weights)
+    if len(feature_weights) != len(features):
+      raise ValueError("features and feature_weights must have the same length")
+  if len(features) != len(feature_specs):
+    raise ValueError("features and feature_specs must have the same length")
+
+  torch = _native.require_cuda()
+  l, s = local_device_count, num_sc_per_device
+  out_rp, out_ids, out_sids, out_gains = {}, {}, {}, {}
+  stats = SparseDenseMatmulInputStats()
+  pending = []
+  for stack_name, members in _group_by_stack(feature_specs).items():
+    stacked = members[0][1].table_spec.stacked_table_spec
+    coo = _coo_buffer_size(stacked.max_ids_per_partition, global_device_count, s,
+                           stacked.suggested_coo_buffer_size_per_device)
+    rp_size = max(p, 8) * s
+    dev_out = (torch.empty((l, rp_size), dtype=torch.int32, device="cuda"),
+               torch.empty((l, coo), dtype=torch.int32, device="cuda"),
+               torch.empty((l, coo), dtype=torch.int32, device="cuda"),
+               torch.empty((l, coo), dtype=torch.float32, device="cuda"))
+    stats_dev = []
+    for d in range(l):
+      ids_parts, off_parts, w_parts, descs = [], [], [], []
+      base = 0
+      for idx, spec in members:
+        rows_total = _feature_rows(features[idx])
+        per_dev = rows_total // l
+        w_in = None if feature_weights is None else feature_weights[idx]
+        ids_f, off_f, w_f = _slice_to_csr(features[idx], w_in, d * per_dev, (d + 1) * per_dev)
+        ids_parts.append(ids_f)
+        off_parts.append(off_f[:-1] + base)
+        base += int(off_f[-1])
+        if w_f is not None:
+          w_parts.append(w_f)
+        elif feature_weights is not None:
+          w_parts.append(np.ones(len(ids_f), np.float32))
+        descs.append((per_dev,) + _transform(spec))
+      tail = torch.tensor([base]) if any(_is_torch(o) for o in off_parts) else np.asarray([base], np.int64)
+      off_parts.append(tail)
+      ids_t = _to_cuda(_concat(ids_parts, np.int32), torch.int32)
+      if any(_is_torch(o) for o in off_parts):
+        off_t = torch.cat([o.to(device="cuda", dtype=torch.int32) if _is_torch(o)
+                           else torch.from_numpy(np.asarray(o)).to(device="cuda", dtype=torch.int32) for o in off_parts])
+      else:
+        off_t = _to_cuda(np.concatenate(off_parts), torch.int32)
+      w_t = _to_cuda(_concat(w_parts, np.float32), torch.float32) if w_parts else None
+      outs = tuple(t[d] for t in dev_out)
+      *_, st = preprocess_stack_on_device(
+          ids_t, off_t, w_t, descs, global_device_count=global_device_count, num_sc_per_device=s,
+          combiner=stacked.combiner, max_ids_per_partition=stacked.max_ids_per_partition,
+          max_unique_ids_per_partition=stacked.max_unique_ids_per_partition, allow_id_dropping=allow_id_dropping,
+          coo_buffer_size_per_device=coo, stack_vocab_size=stacked.stack_vocab_size, outputs=outs)
+      stats_dev.append(st)
+    pending.append((stack_name, stacked, dev_out, torch.stack(stats_dev)))
+
+  for stack_name, stacked, dev_out, stats_dev in pending:
+    host = stats_dev.cpu().numpy()  # synchronises with the stream
+    for d in range(l):
+      _raise_for_status(host[d], p, s, stack_name, stacked.max_ids_per_partition,
+                        stacked.max_unique_ids_per_partition)
+    stats.max_ids_per_partition[stack_name] = host[:, :p].reshape(-1).copy()
+    stats.max_unique_ids_per_partition[stack_name] = host[:, p:2 * p].reshape(-1).copy()
+    stats.required_buffer_sizes[stack_name] = host[:, 2 * p:2 * p + s].reshape(-1).copy()
+    stats.dropped_id_count[stack_name] = int(host[:, 2 * p + s].sum())
+    arrays = dev_out if has_leading_dimension else tuple(t.reshape(-1) for t in dev_out)
+    if not device_output:
+      arrays = tuple(t.cpu().numpy() for t in arrays)
+    out_rp[stack_name], out_ids[stack_name], out_sids[stack_name], out_gains[stack_name] = arrays
+  return out_rp, out_ids, out_sids, out_gains, 1, stats

@@ -1,0 +1,174 @@
+"""numpy restatement of the SparseCore lookup and optimizer update (test infrastructure).
+
+TEST INFRASTRUCTURE - NOT THE PRODUCT.  The device kernels of the reference are
+closed libtpu custom calls (`SparseDenseMatmulOp`,
+`SparseDenseMatmulGradOpWithOptimizerUpdate`); what they compute is pinned by the
+CPU expected-value code of the reference's own tests, which this file restates:
+
+* forward  - jax_tpu_embedding/sparsecore/lib/core/primitives/tests/
+             sparse_dense_matmul_csr_test.py:343-404,499-556
+* gradient - .../sparse_dense_matmul_grad_with_adagrad_test.py:356-367
+             (`grad.at[cols].add(vals * activation_grad[rows])`)
+* SGD      - .../sparse_dense_matmul_grad_with_sgd_test.py:149-163
+* Adagrad  - .../sparse_dense_matmul_grad_with_adagrad_test.py:369-400 and the
+             update body of sparse_dense_matmul_grad_with_adagrad.py:206-226
+* Adam     - .../sparse_dense_matmul_grad_with_adam_test.py:403-437 and
+             sparse_dense_matmul_grad_with_adam.py:296-341
+* clipping - primitives/utils.py:24-59 (table only)
+
+Everything is float32; sums run in buffer order (device, SparseCore, partition,
+slot), which is ascending table row per sample and ascending sample per row.
+Only the touched rows change ("lazy" update).
+
+Parity status: pinned for the arithmetic by the integer-valued fixtures restated
+in tests/test_oracle_lookup.py.  One behaviour is unpinned in the reference: how
+the device orders a non-linear optimizer when one row is hit from several source
+SparseCores.  The contract here is: reduce every contribution first, apply once.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+PADDING_VALUE = 2**31 - 1
+
+
+def _round_up(v, m=8):
+  return (v + m - 1) // m * m
+
+
+def partition_ranges(row_pointers, num_sc_per_device, num_scs, coo_size):
+  """Yields (local_sc, partition, begin, end) slot ranges of one device buffer."""
+  rp = np.asarray(row_pointers).reshape(-1)
+  r_per_sc = max(num_scs, 8)
+  coo_per_sc = coo_size // num_sc_per_device
+  for s in range(num_sc_per_device):
+    for g in range(num_scs):
+      begin = 0 if g == 0 else _round_up(int(rp[s * r_per_sc + g - 1]))
+      end = int(rp[s * r_per_sc + g])
+      if end > begin:
+        yield s, g, s * coo_per_sc + begin, s * coo_per_sc + end
+
+
+def forward(csr_per_device, shards, *, num_sc_per_device, device_batch_size):
+  """Activations per device.
+
+  csr_per_device: list over ALL devices of (row_pointers, embedding_ids,
+    sample_ids, gains) 1-D arrays.
+  shards: float32 [num_scs, rows_per_shard, D]; shard g holds rows
+    {i : i % num_scs == g} of the stacked table at local row i // num_scs.
+  """
+  shards = np.asarray(shards, np.float32)
+  num_scs = shards.shape[0]
+  bsc = device_batch_size // num_sc_per_device
+  out = []
+  for rp, ids, sids, gains in csr_per_device:
+    act = np.zeros((device_batch_size,) + shards.shape[2:], np.float32)
+    for s, g, b, e in partition_ranges(rp, num_sc_per_device, num_scs, len(ids)):
+      rows = shards[g][ids[b:e]]
+      w = gains[b:e].astype(np.float32).reshape((-1,) + (1,) * (rows.ndim - 1))
+      np.add.at(act, s * bsc + sids[b:e], w * rows)
+    out.append(act)
+  return out
+
+
+def table_gradient(csr_per_device, act_grads, shard_shape, *, num_sc_per_device):
+  """(G, touched): summed row gradients per shard and the touched-row mask."""
+  num_scs = shard_shape[0]
+  g_sum = np.zeros(shard_shape, np.float32)
+  touched = np.zeros(shard_shape[:2], bool)
+  for (rp, ids, sids, gains), grad in zip(csr_per_device, act_grads):
+    grad = np.asarray(grad, np.float32)
+    bsc = grad.shape[0] // num_sc_per_device
+    for s, g, b, e in partition_ranges(rp, num_sc_per_device, num_scs, len(ids)):
+      rows = grad[s * bsc + sids[b:e]]
+      w = gains[b:e].astype(np.float32).reshape((-1,) + (1,) * (rows.ndim - 1))
+      np.add.at(g_sum[g], ids[b:e], w * rows)
+      touched[g][ids[b:e]] = True
+  return g_sum, touched
+
+
+def _clip(x, lo, hi):
+  if lo is None and hi is None:
+    return x
+  return np.clip(x, lo, hi).astype(np.float32)
+
+
+def apply_sgd(table, g, touched, lr, lo=None, hi=None):
+  lr = np.float32(lr)
+  new = _clip(table - lr * g, lo, hi)
+  m = touched[..., None]
+  return (np.where(m, new, table).astype(np.float32),)
+
+
+def apply_adagrad(table, acc, g, touched, lr, lo=None, hi=None):
+  lr = np.float32(lr)
+  new_acc = acc + g * g
+  with np.errstate(divide="ignore", invalid="ignore"):
+    new = table - (lr * g) / np.sqrt(new_acc)
+  new = _clip(new, lo, hi)
+  m = touched[..., None]
+  return (np.where(m, new, table).astype(np.float32),
+          np.where(m, new_acc, acc).astype(np.float32))
+
+
+def apply_adam(table, mom, vel, g, touched, alpha_t, beta_1, beta_2, eps_hat, lo=None, hi=None):
+  alpha_t, beta_1, beta_2, eps_hat = (np.float32(x) for x in (alpha_t, beta_1, beta_2, eps_hat))
+  one = np.float32(1.0)
+  m_new = mom + (one - beta_1) * (g - mom)
+  v_new = vel + (one - beta_2) * (g * g - vel)
+  with np.errstate(divide="ignore", invalid="ignore"):
+    new = table - (alpha_t * m_new) / (np.sqrt(v_new) + eps_hat)
+  new = _clip(new, lo, hi)
+  m = touched[..., None]
+  return (np.where(m, new, table).astype(np.float32),
+          np.where(m, m_new, mom).astype(np.float32),
+          np.where(m, v_new, vel).astype(np.float32))
+
+
+def adam_hyperparameters(lr, beta_1, beta_2, eps, step):
+  """embedding_spec.py:506-539 (AdamOptimizerSpec.get_hyperparameters), float32."""
+  b1, b2 = np.float32(beta_1), np.float32(beta_2)
+  b1t = np.power(b1, np.float32(step + 1), dtype=np.float32)
+  b2t = np.power(b2, np.float32(step + 1), dtype=np.float32)
+  c2 = np.sqrt(np.float32(1.0) - b2t)
+  alpha_t = np.float32(lr) * c2 / (np.float32(1.0) - b1t)
+  return np.float32(alpha_t), b1, b2, np.float32(np.float32(eps) * c2)
+
+
+def shard_table(table, num_scs):
+  """[V, D] -> [num_scs, V / num_scs, D] (row i -> shard i % num_scs, local row i // num_scs)."""
+  table = np.asarray(table)
+  return np.ascontiguousarray(
+      table.reshape((-1, num_scs) + table.shape[1:]).swapaxes(0, 1))
+
+
+def unshard_table(shards):
+  shards = np.asarray(shards)
+  return np.ascontiguousarray(shards.swapaxes(0, 1)).reshape((-1,) + shards.shape[2:])
+
+
+def dense_reference(features, weights, combiner, table, act_grad=None):
+  """Brute-force per-sample lookup straight from the raw inputs (float64).
+
+  Used to cross-check the whole chain preprocessing -> forward against the
+  definition of the combiners (docs: sum, mean = sum / sum(w), sqrtn = sum /
+  sqrt(sum(w^2))).  Returns activations [B, D] (and the dense table gradient when
+  act_grad is given).
+  """
+  table = np.asarray(table, np.float64)
+  out = np.zeros((len(features), table.shape[1]))
+  grad = np.zeros_like(table) if act_grad is not None else None
+  for i, row in enumerate(features):
+    row = np.asarray(row).reshape(-1)
+    w = np.ones(len(row)) if weights is None else np.asarray(weights[i], np.float64).reshape(-1)
+    if len(row) == 0:
+      continue
+    if combiner == "mean":
+      w = w / w.sum()
+    elif combiner == "sqrtn":
+      w = w / np.sqrt((w * w).sum())
+    out[i] = (w[:, None] * table[row]).sum(0)
+    if grad is not None:
+      np.add.at(grad, row, w[:, None] * np.asarray(act_grad[i], np.float64)[None, :])
+  return (out, grad) if grad is not None else out

@@ -1,0 +1,80 @@
+"""Runs unit tests of the reference project against this repository's implementation.
+
+The reference's test modules import `jax_tpu_embedding.sparsecore...`; with this repository's
+package first on sys.path those imports resolve to the B200 drop-in.  Modules the tests import
+but the hot path does not provide (FDO client, portpicker) are stubbed.  Only usable where the
+reference checkout is mounted; nothing here ships.
+"""
+
+from __future__ import annotations
+
+import importlib
+import importlib.util
+import os
+import sys
+import types
+import unittest
+
+REFERENCE = "/root/reference"
+_CORE_TESTS = os.path.join(REFERENCE, "jax_tpu_embedding/sparsecore/lib/core/tests")
+
+
+def _stub(name, **attrs):
+  mod = types.ModuleType(name)
+  for k, v in attrs.items():
+    setattr(mod, k, v)
+  sys.modules[name] = mod
+  return mod
+
+
+def _load(name, path):
+  spec = importlib.util.spec_from_file_location(name, path)
+  mod = importlib.util.module_from_spec(spec)
+  sys.modules[name] = mod
+  spec.loader.exec_module(mod)
+  return mod
+
+
+class _NullFdoClient:
+  def __init__(self, *a, **k):
+    pass
+
+  def record(self, stats):
+    pass
+
+  def publish(self):
+    pass
+
+
+def load_pybind_test_module(backend):
+  """Imports the reference's pybind_input_preprocessing_test with `backend` as the preprocessor."""
+  from absl import flags
+  from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+
+  if not flags.FLAGS.is_parsed():
+    flags.FLAGS(["reference_harness"])
+  pip.preprocess_sparse_dense_matmul_input = backend
+  _stub("portpicker", pick_unused_port=lambda: 0)
+  _stub("jax_tpu_embedding.sparsecore.lib.fdo")
+  _stub("jax_tpu_embedding.sparsecore.lib.fdo.file_fdo_client", NPZFileFDOClient=_NullFdoClient)
+  sys.modules["jax_tpu_embedding.sparsecore.lib.fdo"].file_fdo_client = sys.modules[
+      "jax_tpu_embedding.sparsecore.lib.fdo.file_fdo_client"]
+  _stub("jax_tpu_embedding.sparsecore.lib.core.tests")
+  tu = _load("jax_tpu_embedding.sparsecore.lib.core.tests.test_utils", os.path.join(_CORE_TESTS, "test_utils.py"))
+  sys.modules["jax_tpu_embedding.sparsecore.lib.core.tests"].test_utils = tu
+  return _load("reference_pybind_input_preprocessing_test",
+               os.path.join(_CORE_TESTS, "pybind_input_preprocessing_test.py"))
+
+
+def run_cases(module, skip_classes=("MinibatchingNodeTest",)):
+  """Runs every TestCase of `module`; returns (unittest result, number of tests run)."""
+  loader = unittest.TestLoader()
+  suite = unittest.TestSuite()
+  for name in dir(module):
+    obj = getattr(module, name)
+    if isinstance(obj, type) and issubclass(obj, unittest.TestCase) and name not in skip_classes:
+      if obj.__module__ != module.__name__:
+        continue
+      suite.addTests(loader.loadTestsFromTestCase(obj))
+  result = unittest.TextTestRunner(verbosity=0, stream=open(os.devnull, "w")).run(suite)
+  return result
