@@ -1,0 +1,167 @@
+"""Forward and fused backward kernels vs the numpy oracle, on oracle-produced CSR buffers.
+
+Tolerance: 1e-5 relative (float32).  Sums whose terms cancel have no elementwise relative bound,
+so the absolute floor is 1e-6 of the largest magnitude of the expected array.  Where all terms are
+added in the oracle's order (the whole forward pass) the results are compared bit for bit.
+"""
+
+import numpy as np
+import pytest
+
+import cases
+import oracle_backend as ob
+from oracle import lookup_oracle as lo
+from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_csr
+from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_grad_with_adagrad
+from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_grad_with_adam
+from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_grad_with_sgd
+
+pytestmark = pytest.mark.gpu
+
+RTOL = 1e-5
+
+
+def assert_close(got, want):
+  want = np.asarray(want)
+  np.testing.assert_allclose(np.asarray(got).reshape(want.shape), want, rtol=RTOL,
+                             atol=1e-6 * float(np.abs(want).max()) + 1e-12)
+
+CASES = [c for c in cases.standard_cases() if c.local_device_count == c.global_device_count]
+
+
+def _setup(case, seed=0):
+  """Oracle CSR per stack plus random shards / gradients."""
+  import torch
+
+  out = ob.oracle_preprocess(case.features, case.weights, case.feature_specs, case.local_device_count,
+                             case.global_device_count, num_sc_per_device=case.num_sc_per_device,
+                             allow_id_dropping=case.allow_id_dropping, has_leading_dimension=True)
+  rng = np.random.default_rng(seed)
+  stacks = {}
+  p = case.global_device_count * case.num_sc_per_device
+  for name in out[0]:
+    spec = next(f.table_spec.stacked_table_spec for f in case.feature_specs
+                if f.table_spec.stacked_table_spec.stack_name == name)
+    rows = spec.stack_vocab_size // p
+    dim = spec.stack_embedding_dim
+    bdev = spec.total_sample_count // case.global_device_count
+    shards = rng.normal(0, 0.01, size=(p, rows, dim)).astype(np.float32)
+    csr = [tuple(out[i][name][d] for i in range(4)) for d in range(case.local_device_count)]
+    grads = [(rng.normal(0, 1, size=(bdev, dim)) * 1e-2).astype(np.float32) for _ in csr]
+    stacks[name] = dict(spec=spec, shards=shards, csr=csr, grads=grads, bdev=bdev, flat=[
+        torch.from_numpy(np.concatenate([c[i] for c in csr])).cuda() for i in range(4)])
+  return stacks
+
+
+def _kw(case, spec):
+  return dict(max_ids_per_partition=spec.max_ids_per_partition,
+              max_unique_ids_per_partition=spec.max_unique_ids_per_partition,
+              num_sc_per_device=case.num_sc_per_device, global_device_count=case.global_device_count,
+              local_device_count=case.local_device_count)
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_forward_matches_oracle(case):
+  import torch
+
+  for name, st in _setup(case).items():
+    want = np.concatenate(lo.forward(st["csr"], st["shards"], num_sc_per_device=case.num_sc_per_device,
+                                     device_batch_size=st["bdev"]))
+    table = torch.from_numpy(st["shards"].reshape(-1, st["shards"].shape[-1])).cuda()
+    got = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
+        *st["flat"], np.int32(1), table, device_batch_size=st["bdev"], **_kw(case, st["spec"]))
+    got2 = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
+        *st["flat"], np.int32(1), table, device_batch_size=st["bdev"], **_kw(case, st["spec"]))
+    assert torch.equal(got, got2), "forward is not run-to-run reproducible"
+    # Same summation order as the oracle (ascending shard, row): identical bits.
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("opt", ["sgd", "adagrad", "adam"])
+@pytest.mark.parametrize("clip", [None, (-0.012, 0.011)])
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+def test_backward_matches_oracle(case, opt, clip):
+  import torch
+
+  rng = np.random.default_rng(7)
+  for name, st in _setup(case).items():
+    shards = st["shards"]
+    g, touched = lo.table_gradient(st["csr"], st["grads"], shards.shape, num_sc_per_device=case.num_sc_per_device)
+    lo_, hi_ = clip if clip else (None, None)
+    slot0 = rng.uniform(0.05, 0.2, size=shards.shape).astype(np.float32)
+    slot1 = rng.uniform(0.0, 1e-4, size=shards.shape).astype(np.float32)
+    dev = lambda a: torch.from_numpy(a.reshape(-1, a.shape[-1]).copy()).cuda()
+    grad = torch.from_numpy(np.concatenate(st["grads"])).cuda()
+    kw = dict(_kw(case, st["spec"]), min_value=lo_, max_value=hi_)
+    if opt == "sgd":
+      want = lo.apply_sgd(shards, g, touched, 0.01, lo_, hi_)
+      got = (sparse_dense_matmul_grad_with_sgd.tpu_sparse_dense_matmul_grad_with_sgd_primitive.bind(
+          *st["flat"], np.int32(1), dev(shards), grad, np.float32(0.01), **kw),)
+    elif opt == "adagrad":
+      want = lo.apply_adagrad(shards, slot0, g, touched, 0.01, lo_, hi_)
+      got = sparse_dense_matmul_grad_with_adagrad.tpu_sparse_dense_matmul_grad_with_adagrad_primitive.bind(
+          *st["flat"], np.int32(1), dev(shards), dev(slot0), grad, np.float32(0.01), **kw)
+    else:
+      hyp = lo.adam_hyperparameters(1e-3, 0.9, 0.999, 1e-8, 3)
+      want = lo.apply_adam(shards, slot0, slot1, g, touched, *hyp, lo_, hi_)
+      got = sparse_dense_matmul_grad_with_adam.tpu_sparse_dense_matmul_grad_with_adam_primitive.bind(
+          *st["flat"], np.int32(1), dev(shards), dev(slot0), dev(slot1), grad, *hyp, **kw)
+    for a, b in zip(got, want):
+      assert_close(a.cpu().numpy(), b)
+    # Untouched rows must be bit-identical to the inputs.
+    untouched = ~touched
+    np.testing.assert_array_equal(got[0].cpu().numpy().reshape(shards.shape)[untouched], shards[untouched])
+
+
+def test_backward_is_reproducible_and_hot_rows():
+  """One row hit by thousands of entries: chunked partial sums stay deterministic and accurate."""
+  import torch
+
+  case = cases.make_case("hot", seed=11, tables=[dict(vocab=64, dim=128, features=[dict(kind="dense", valency=1, dist="zipf", a=2.0)])],
+                         batch=8192, optimizer="adagrad")
+  st = _setup(case)["table_0"]
+  g, touched = lo.table_gradient(st["csr"], st["grads"], st["shards"].shape, num_sc_per_device=1)
+  acc = np.full(st["shards"].shape, 0.1, np.float32)
+  want = lo.apply_adagrad(st["shards"], acc, g, touched, 0.01)
+  outs = []
+  for _ in range(2):
+    table = torch.from_numpy(st["shards"][0].copy()).cuda()
+    accd = torch.from_numpy(acc[0].copy()).cuda()
+    grad = torch.from_numpy(st["grads"][0]).cuda()
+    outs.append(sparse_dense_matmul_grad_with_adagrad.tpu_sparse_dense_matmul_grad_with_adagrad_primitive.bind(
+        *st["flat"], np.int32(1), table, accd, grad, np.float32(0.01), **_kw(case, st["spec"])))
+  assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+  assert_close(outs[0][0].cpu().numpy(), want[0][0])
+  assert_close(outs[0][1].cpu().numpy(), want[1][0])
+
+
+def test_rank1_table():
+  """Tables of rank 1 (dim 1), as in the reference's dim-1 forward test."""
+  import torch
+
+  case = cases.make_case("r1", seed=3, tables=[dict(vocab=64, dim=8, features=[dict(kind="dense", valency=2)])], batch=32)
+  st = _setup(case)["table_0"]
+  table = (np.arange(st["shards"].shape[1], dtype=np.float32) + 1.0)
+  want = lo.forward(st["csr"], table.reshape(1, -1), num_sc_per_device=1, device_batch_size=st["bdev"])[0]
+  got = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
+      *st["flat"], np.int32(1), torch.from_numpy(table).cuda(), device_batch_size=st["bdev"], **_kw(case, st["spec"]))
+  assert got.shape == (st["bdev"],)
+  np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+def test_operand_validation():
+  import torch
+
+  case = CASES[0]
+  st = _setup(case)["table_0"]
+  table = torch.from_numpy(st["shards"][0]).cuda()
+  bind = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind
+  kw = dict(device_batch_size=st["bdev"], **_kw(case, st["spec"]))
+  with pytest.raises(ValueError, match="lhs_gains must have type"):
+    bind(st["flat"][0], st["flat"][1], st["flat"][2], st["flat"][3].double(), np.int32(1), table, **kw)
+  with pytest.raises(ValueError, match="sharding_strategy must be MOD"):
+    bind(*st["flat"], np.int32(1), table, sharding_strategy=2, **kw)
+  with pytest.raises(ValueError, match="max_ids_per_partition must be positive"):
+    bind(*st["flat"], np.int32(1), table, **dict(kw, max_ids_per_partition=0))
+  with pytest.raises(ValueError, match="equal rank 1 shapes"):
+    bind(st["flat"][0], st["flat"][1][:-8], st["flat"][2], st["flat"][3], np.int32(1), table, **kw)

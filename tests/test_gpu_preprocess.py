@@ -1,0 +1,99 @@
+"""GPU preprocessing vs the CPU oracle: bit-exact buffers, row pointers and statistics."""
+
+import numpy as np
+import pytest
+
+import cases
+import oracle_backend as ob
+from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+from jax_tpu_embedding.sparsecore.lib.nn import embedding
+
+pytestmark = pytest.mark.gpu
+
+CASES = cases.standard_cases()
+
+
+def _compare(case, got, want):
+  slices = case.local_device_count * case.num_sc_per_device
+  for name in want[0]:
+    ob.written_region_equal(got[0][name], want[0][name], [got[i][name] for i in (1, 2, 3)],
+                            [want[i][name] for i in (1, 2, 3)], slices)
+    gs, ws = got[5], want[5]
+    np.testing.assert_array_equal(gs.max_ids_per_partition[name], ws.max_ids_per_partition[name])
+    np.testing.assert_array_equal(gs.max_unique_ids_per_partition[name], ws.max_unique_ids_per_partition[name])
+    np.testing.assert_array_equal(gs.required_buffer_sizes[name], ws.required_buffer_sizes[name])
+    assert gs.dropped_id_count[name] == ws.dropped_id_count[name]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c.name for c in CASES])
+@pytest.mark.parametrize("leading", [False, True])
+def test_preprocess_matches_oracle(case, leading):
+  kw = dict(num_sc_per_device=case.num_sc_per_device, has_leading_dimension=leading,
+            allow_id_dropping=case.allow_id_dropping)
+  got = pip.preprocess_sparse_dense_matmul_input(case.features, case.weights, case.feature_specs,
+                                                 case.local_device_count, case.global_device_count, **kw)
+  want = ob.oracle_preprocess(case.features, case.weights, case.feature_specs, case.local_device_count,
+                              case.global_device_count, **kw)
+  _compare(case, got, want)
+  if leading:
+    for name in want[0]:
+      assert got[1][name].shape == want[1][name].shape
+
+
+def test_tail_is_padding():
+  case = CASES[0]
+  rp, ids, sids, gains, _, _ = pip.preprocess_sparse_dense_matmul_input(
+      case.features, None, case.feature_specs, 1, 1, num_sc_per_device=1)
+  for name in rp:
+    last = rp[name][-1]
+    assert (ids[name][last:] == 2**31 - 1).all() and (sids[name][last:] == 2**31 - 1).all()
+    assert np.isnan(gains[name][last:]).all()
+
+
+def test_id_limit_raises_value_error():
+  case = cases.make_case("limit", seed=1, tables=[dict(vocab=64, dim=8)], batch=64, max_ids=4, max_unique=4)
+  with pytest.raises(ValueError, match="is greater than the set max"):
+    pip.preprocess_sparse_dense_matmul_input(case.features, None, case.feature_specs, 1, 1, num_sc_per_device=1)
+
+
+def test_unity_weights_same_as_none():
+  for combiner in ("sum", "mean", "sqrtn"):
+    case = cases.make_case("u", seed=5, tables=[dict(vocab=500, dim=8, features=[dict(kind="dense", valency=6)])],
+                           batch=128, combiner=combiner, dup_prob=0.2)
+    ones = [np.ones_like(case.features[0], dtype=np.float32)]
+    a = pip.preprocess_sparse_dense_matmul_input(case.features, None, case.feature_specs, 1, 1, num_sc_per_device=1)
+    b = pip.preprocess_sparse_dense_matmul_input(case.features, ones, case.feature_specs, 1, 1, num_sc_per_device=1)
+    for name in a[0]:
+      np.testing.assert_array_equal(a[0][name], b[0][name])
+      last = a[0][name][-1]
+      np.testing.assert_array_equal(a[1][name][:last], b[1][name][:last])
+      np.testing.assert_allclose(a[3][name][:last], b[3][name][:last], rtol=1e-6)
+
+
+def test_ragged_input_leaf_and_device_output():
+  import torch
+
+  case = CASES[3]
+  rows = case.features[0]
+  lens = np.array([len(r) for r in rows])
+  splits = np.concatenate([[0], np.cumsum(lens)]).astype(np.int64)
+  ragged = embedding.RaggedInput(np.concatenate(list(rows)).astype(np.int32), splits)
+  pre_a, stats_a = embedding.preprocess_sparse_dense_matmul_input(
+      [ragged], None, case.feature_specs, 1, 1, num_sc_per_device=1)
+  pre_b, stats_b = embedding.preprocess_sparse_dense_matmul_input(
+      case.features, None, case.feature_specs, 1, 1, num_sc_per_device=1, device_output=False)
+  for name in pre_b.lhs_row_pointers:
+    assert isinstance(pre_a.lhs_embedding_ids[name], torch.Tensor) and pre_a.lhs_embedding_ids[name].is_cuda
+    np.testing.assert_array_equal(pre_a.lhs_row_pointers[name].cpu().numpy(), pre_b.lhs_row_pointers[name])
+    np.testing.assert_array_equal(pre_a.lhs_embedding_ids[name].cpu().numpy(), pre_b.lhs_embedding_ids[name])
+    np.testing.assert_array_equal(stats_a.max_ids_per_partition[name], stats_b.max_ids_per_partition[name])
+
+
+def test_invalid_arguments():
+  case = CASES[0]
+  with pytest.raises(ValueError, match="local_device_count must be greater than 0"):
+    pip.preprocess_sparse_dense_matmul_input(case.features, None, case.feature_specs, 0, 1, num_sc_per_device=1)
+  with pytest.raises(ValueError, match="must be a power of 2"):
+    pip.preprocess_sparse_dense_matmul_input(case.features, None, case.feature_specs, 1, 3, num_sc_per_device=1)
+  with pytest.raises(ValueError, match="cannot be empty"):
+    pip.preprocess_sparse_dense_matmul_input([], None, [], 1, 1, num_sc_per_device=1)
