@@ -300,6 +300,8 @@ def main():
   ap.add_argument("--impl", default="b200")
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--profile-range", action="store_true",
+                  help="bracket the timed steps with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
   args = ap.parse_args()
   rank = int(os.environ.get("RANK", "0"))
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -369,11 +371,15 @@ def main():
   sampler = ClockSampler(local_rank)
   sampler.start()
   ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  if args.profile_range:
+    torch.cuda.profiler.start()
   ev0.record()
   for _ in range(args.steps):
     lookup_update()
   ev1.record()
   barrier()
+  if args.profile_range:
+    torch.cuda.profiler.stop()
   clocks = sampler.stop()
   ms = ev0.elapsed_time(ev1) / args.steps
   if world > 1:

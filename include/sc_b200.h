@@ -141,6 +141,32 @@ int32_t sc_sparse_dense_matmul_grad(const sc_csr_t* csr, const float* activation
                                     float* const* shard_slot1_host, const sc_optimizer_t* optimizer,
                                     void* workspace_device, size_t workspace_bytes, sc_stream_t stream);
 
+/* Grouped variants: ONE launch sequence serves every stacked table of a model (the loop over
+ * stacked tables in lib/nn/embedding.py:1145-1172 and :1422-1527 of the reference issues one
+ * custom call per table).  All tables of a group must have row lengths in the same class
+ * (dim divisible by 4 and the same number of 128-float blocks, or the same scalar class). */
+typedef struct {
+  sc_csr_t csr;
+  const float* const* shard_tables; /* host array [num_scs] of device pointers */
+  float* activations;               /* device, [device_batch_size, dim] */
+} sc_fwd_item_t;
+
+typedef struct {
+  sc_csr_t csr;
+  const float* activation_grad;     /* device, [device_batch_size, dim] */
+  float* const* shard_tables;       /* host arrays [num_scs] of device pointers */
+  float* const* shard_slot0;
+  float* const* shard_slot1;
+  sc_optimizer_t optimizer;
+} sc_grad_item_t;
+
+size_t sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(const sc_fwd_item_t* items, int32_t count);
+int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items, int32_t count, void* workspace_device,
+                                           size_t workspace_bytes, sc_stream_t stream);
+size_t sc_sparse_dense_matmul_grad_grouped_workspace_bytes(const sc_grad_item_t* items, int32_t count);
+int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* items, int32_t count, void* workspace_device,
+                                            size_t workspace_bytes, sc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

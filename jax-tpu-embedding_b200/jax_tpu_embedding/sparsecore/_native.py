@@ -51,6 +51,15 @@ class Optimizer(ctypes.Structure):
   _fields_ = [("optimizer", c_i32), ("hyper", c_f32 * 4), ("clip_min", c_f32), ("clip_max", c_f32)]
 
 
+class FwdItem(ctypes.Structure):
+  _fields_ = [("csr", Csr), ("shard_tables", ctypes.POINTER(c_vp)), ("activations", c_vp)]
+
+
+class GradItem(ctypes.Structure):
+  _fields_ = [("csr", Csr), ("activation_grad", c_vp), ("shard_tables", ctypes.POINTER(c_vp)),
+              ("shard_slot0", ctypes.POINTER(c_vp)), ("shard_slot1", ctypes.POINTER(c_vp)), ("optimizer", Optimizer)]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -99,6 +108,14 @@ def lib() -> ctypes.CDLL:
     l.sc_sparse_dense_matmul_grad.restype = c_i32
     l.sc_sparse_dense_matmul_grad.argtypes = [ctypes.POINTER(Csr), c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
                                               ctypes.POINTER(c_vp), ctypes.POINTER(Optimizer), c_vp, c_sz, c_vp]
+    l.sc_sparse_dense_matmul_fwd_grouped_workspace_bytes.restype = c_sz
+    l.sc_sparse_dense_matmul_fwd_grouped_workspace_bytes.argtypes = [ctypes.POINTER(FwdItem), c_i32]
+    l.sc_sparse_dense_matmul_fwd_grouped.restype = c_i32
+    l.sc_sparse_dense_matmul_fwd_grouped.argtypes = [ctypes.POINTER(FwdItem), c_i32, c_vp, c_sz, c_vp]
+    l.sc_sparse_dense_matmul_grad_grouped_workspace_bytes.restype = c_sz
+    l.sc_sparse_dense_matmul_grad_grouped_workspace_bytes.argtypes = [ctypes.POINTER(GradItem), c_i32]
+    l.sc_sparse_dense_matmul_grad_grouped.restype = c_i32
+    l.sc_sparse_dense_matmul_grad_grouped.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
     _lib = l
   return _lib
 

@@ -28,15 +28,21 @@ from jax_tpu_embedding.sparsecore.utils import utils as sc_utils
 
 
 class Primitive:
-  """Named operator with a `bind` entry point."""
+  """Named operator.  `prepare` validates operands and returns a request; `bind` runs it.
 
-  def __init__(self, name: str, impl, multiple_results: bool = False):
+  Requests of several operators can be executed together with `run_forward_group` /
+  `run_grad_group`, which is how the embedding API serves all stacked tables in one launch.
+  """
+
+  def __init__(self, name: str, prepare, runner, multiple_results: bool = False, unwrap=None):
     self.name = name
-    self._impl = impl
+    self.prepare = prepare
+    self._runner = runner
+    self._unwrap = unwrap or (lambda r: r)
     self.multiple_results = multiple_results
 
   def bind(self, *operands, **attributes):
-    return self._impl(*operands, **attributes)
+    return self._unwrap(self._runner([self.prepare(*operands, **attributes)])[0])
 
   def __repr__(self):
     return self.name
@@ -108,54 +114,174 @@ def _device_operands(rp, ids, sids, gains):
           _native.as_device(gains, torch.float32, "lhs_gains"))
 
 
-def run_forward(rp, ids, sids, gains, table, *, device_batch_size, num_sc_per_device=None, global_device_count=None,
-                local_device_count=None, max_ids_per_sample=0):
-  torch = _native.require_cuda()
-  lib = _native.lib()
-  rp, ids, sids, gains = _device_operands(rp, ids, sids, gains)
-  table = _native.as_device(table, torch.float32, "embedding_table")
-  geo = Geometry(rp, ids, table, device_batch_size, num_sc_per_device, global_device_count, local_device_count)
-  csr = geo.csr(rp, ids, sids, gains, max_ids_per_sample)
-  out_shape = (geo.batch, geo.dim) if table.dim() > 1 else (geo.batch,)
-  act = torch.empty(out_shape, dtype=torch.float32, device=table.device)
-  nbytes = lib.sc_sparse_dense_matmul_fwd_workspace_bytes(ctypes.byref(csr))
-  ws = _native.workspace(nbytes, "lookup")
-  ptrs = geo.shard_pointers(table)
-  _native.check(lib.sc_sparse_dense_matmul_fwd(ctypes.byref(csr), ptrs, act.data_ptr(), ws.data_ptr(), ws.numel(),
-                                               _native.current_stream_ptr()))
-  return act
+def shape_class(dim: int) -> tuple[int, int]:
+  """(vector width, vectors per lane) the kernels use for a row of `dim` floats."""
+  w = 4 if dim % 4 == 0 else 1
+  need = -(-(dim // w) // 32)
+  for k in (1, 2, 4, 8):
+    if need <= k:
+      return w, k
+  raise ValueError(f"embedding dimension {dim} is too large")
+
+
+class ForwardRequest:
+  """One stacked table of a grouped forward call (operands already validated)."""
+
+  def __init__(self, rp, ids, sids, gains, table, *, device_batch_size, num_sc_per_device=None,
+               global_device_count=None, local_device_count=None, max_ids_per_sample=0):
+    torch = _native.require_cuda()
+    self.rp, self.ids, self.sids, self.gains = _device_operands(rp, ids, sids, gains)
+    self.table = _native.as_device(table, torch.float32, "embedding_table")
+    self.geo = Geometry(self.rp, self.ids, self.table, device_batch_size, num_sc_per_device, global_device_count,
+                        local_device_count)
+    out_shape = (self.geo.batch, self.geo.dim) if self.table.dim() > 1 else (self.geo.batch,)
+    self.act = torch.empty(out_shape, dtype=torch.float32, device=self.table.device)
+    self.csr = self.geo.csr(self.rp, self.ids, self.sids, self.gains, max_ids_per_sample)
+    self.ptrs = self.geo.shard_pointers(self.table)
+
+
+class ForwardGroupCall:
+  """Validated requests turned into ready-to-launch descriptor arrays (one per shape class).
+
+  Holds only addresses and sizes, so it can be replayed whenever the same buffers are passed
+  again; outputs are allocated per run.
+  """
+
+  def __init__(self, requests):
+    lib = _native.lib()
+    self.requests = requests
+    self.groups = []
+    by_class: dict = {}
+    for i, r in enumerate(requests):
+      by_class.setdefault(shape_class(r.geo.dim), []).append(i)
+    for idxs in by_class.values():
+      items = (_native.FwdItem * len(idxs))()
+      for j, i in enumerate(idxs):
+        r = requests[i]
+        items[j].csr = r.csr
+        items[j].shard_tables = r.ptrs
+        items[j].activations = r.act.data_ptr()
+      nbytes = lib.sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(items, len(idxs))
+      if nbytes == 0:
+        _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), None, 0, None))
+      self.groups.append((items, idxs, nbytes))
+    self.shapes = [tuple(r.act.shape) for r in requests]
+    self.first = True
+    self.keep = [(r.ptrs,) for r in requests]
+    # Requests keep tensors alive; a replayable call must not, so drop them after the first run.
+
+  def run(self):
+    torch = _native.torch_mod()
+    lib = _native.lib()
+    if self.first:
+      outs = [r.act for r in self.requests]
+      self.first = False
+      self.requests = None
+    else:
+      outs = [torch.empty(shape, dtype=torch.float32, device="cuda") for shape in self.shapes]
+      for items, idxs, _ in self.groups:
+        for j, i in enumerate(idxs):
+          items[j].activations = outs[i].data_ptr()
+    stream = _native.current_stream_ptr()
+    for items, idxs, nbytes in self.groups:
+      ws = _native.workspace(nbytes, "lookup")
+      _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
+    return outs
+
+
+def run_forward_group(requests):
+  """Runs every request; requests whose rows fall in one shape class share a grouped launch."""
+  return ForwardGroupCall(requests).run()
+
+
+def run_forward(rp, ids, sids, gains, table, **kw):
+  return run_forward_group([ForwardRequest(rp, ids, sids, gains, table, **kw)])[0]
 
 
 _OPT_KIND = {"sgd": 0, "adagrad": 1, "adam": 2}
 
 
-def run_grad(kind, rp, ids, sids, gains, table, slots, act_grad, hyper, *, min_value=None, max_value=None,
-             num_sc_per_device=None, global_device_count=None, local_device_count=None):
+class GradRequest:
+  """One stacked table of a grouped backward call."""
+
+  def __init__(self, kind, rp, ids, sids, gains, table, slots, act_grad, hyper, *, min_value=None, max_value=None,
+               num_sc_per_device=None, global_device_count=None, local_device_count=None):
+    torch = _native.require_cuda()
+    self.rp, self.ids, self.sids, self.gains = _device_operands(rp, ids, sids, gains)
+    self.table = _native.as_device(table, torch.float32, "embedding_table")
+    self.slots = [_native.as_device(s, torch.float32, "slot variable") for s in slots]
+    self.act_grad = _native.as_device(act_grad, torch.float32, "activations_grad")
+    l = int(local_device_count) if local_device_count else 1
+    self.geo = Geometry(self.rp, self.ids, self.table, self.act_grad.shape[0] // l, num_sc_per_device,
+                        global_device_count, local_device_count)
+    if self.act_grad.shape[0] != self.geo.batch:
+      raise ValueError(f"activations_grad has {self.act_grad.shape[0]} rows, expected {self.geo.batch}")
+    self.csr = self.geo.csr(self.rp, self.ids, self.sids, self.gains)
+    opt = _native.Optimizer()
+    opt.optimizer = _OPT_KIND[kind]
+    for i in range(4):
+      opt.hyper[i] = float(hyper[i]) if i < len(hyper) else 0.0
+    opt.clip_min = float("nan") if min_value is None else float(min_value)
+    opt.clip_max = float("nan") if max_value is None else float(max_value)
+    self.opt = opt
+    self.t_ptrs = self.geo.shard_pointers(self.table)
+    self.s_ptrs = [self.geo.shard_pointers(s) for s in self.slots]
+
+  def results(self):
+    return (self.table, *self.slots)
+
+
+class GradGroupCall:
+  """Ready-to-launch descriptors of a grouped backward call (addresses and sizes only)."""
+
+  def __init__(self, requests):
+    lib = _native.lib()
+    self.requests = requests
+    self.groups = []
+    by_class: dict = {}
+    for i, r in enumerate(requests):
+      by_class.setdefault((shape_class(r.geo.dim), r.opt.optimizer), []).append(i)
+    for idxs in by_class.values():
+      items = (_native.GradItem * len(idxs))()
+      for j, i in enumerate(idxs):
+        r = requests[i]
+        items[j].csr = r.csr
+        items[j].activation_grad = r.act_grad.data_ptr()
+        items[j].shard_tables = r.t_ptrs
+        if len(r.s_ptrs) > 0:
+          items[j].shard_slot0 = r.s_ptrs[0]
+        if len(r.s_ptrs) > 1:
+          items[j].shard_slot1 = r.s_ptrs[1]
+        items[j].optimizer = r.opt
+      nbytes = lib.sc_sparse_dense_matmul_grad_grouped_workspace_bytes(items, len(idxs))
+      if nbytes == 0:
+        _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), None, 0, None))
+      self.groups.append((items, idxs, nbytes))
+    self.keep = [(r.t_ptrs, r.s_ptrs) for r in requests]
+    self._results = [r.results() for r in requests]
+    self.first = True
+
+  def run(self):
+    lib = _native.lib()
+    stream = _native.current_stream_ptr()
+    for items, idxs, nbytes in self.groups:
+      ws = _native.workspace(nbytes, "lookup")
+      _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
+    if self.first:
+      self.first = False
+      self.requests = None
+      res, self._results = self._results, None
+      return res
+    return None
+
+
+def run_grad_group(requests):
+  return GradGroupCall(requests).run()
+
+
+def run_grad(kind, rp, ids, sids, gains, table, slots, act_grad, hyper, **kw):
   """Fused gradient + optimizer update; returns (table, *slots), updated in place."""
-  torch = _native.require_cuda()
-  lib = _native.lib()
-  rp, ids, sids, gains = _device_operands(rp, ids, sids, gains)
-  table = _native.as_device(table, torch.float32, "embedding_table")
-  slots = [_native.as_device(s, torch.float32, "slot variable") for s in slots]
-  act_grad = _native.as_device(act_grad, torch.float32, "activations_grad")
-  batch = act_grad.shape[0]
-  geo_l = int(local_device_count) if local_device_count else 1
-  geo = Geometry(rp, ids, table, batch // geo_l, num_sc_per_device, global_device_count, local_device_count)
-  csr = geo.csr(rp, ids, sids, gains)
-  opt = _native.Optimizer()
-  opt.optimizer = _OPT_KIND[kind]
-  for i in range(4):
-    opt.hyper[i] = float(hyper[i]) if i < len(hyper) else 0.0
-  opt.clip_min = float("nan") if min_value is None else float(min_value)
-  opt.clip_max = float("nan") if max_value is None else float(max_value)
-  nbytes = lib.sc_sparse_dense_matmul_grad_workspace_bytes(ctypes.byref(csr))
-  ws = _native.workspace(nbytes, "lookup")
-  t_ptrs = geo.shard_pointers(table)
-  s_ptrs = [geo.shard_pointers(s) for s in slots] + [None, None]
-  _native.check(lib.sc_sparse_dense_matmul_grad(ctypes.byref(csr), act_grad.data_ptr(), t_ptrs, s_ptrs[0], s_ptrs[1],
-                                                ctypes.byref(opt), ws.data_ptr(), ws.numel(),
-                                                _native.current_stream_ptr()))
-  return (table, *slots)
+  return run_grad_group([GradRequest(kind, rp, ids, sids, gains, table, slots, act_grad, hyper, **kw)])[0]
 
 
 def scalar_f32(x) -> float:

@@ -14,7 +14,7 @@ from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops
 from jax_tpu_embedding.sparsecore.lib.core.primitives import utils
 
 
-def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
+def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
           num_minibatches_per_physical_sparse_core, embedding_table, *, device_batch_size: int,
           max_ids_per_partition: int, max_unique_ids_per_partition: int, sharding_strategy: int = 1,
           quantization_config: tuple[float, float, int] | None = None, enable_minibatching: bool = False,
@@ -35,11 +35,11 @@ def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_g
     # Activation quantization is a TPU-side numeric option; values are returned unquantized.
   if enable_minibatching:
     raise NotImplementedError("minibatching exists to fit TPU on-chip memory and is not part of the B200 path")
-  return _ops.run_forward(
+  return _ops.ForwardRequest(
       lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains, embedding_table,
       device_batch_size=device_batch_size, num_sc_per_device=num_sc_per_device,
       global_device_count=global_device_count, local_device_count=local_device_count,
       max_ids_per_sample=max_ids_per_sample)
 
 
-tpu_sparse_dense_matmul_csr_primitive = _ops.Primitive("sparse_dense_matmul_csr", _impl)
+tpu_sparse_dense_matmul_csr_primitive = _ops.Primitive("sparse_dense_matmul_csr", _prepare, _ops.run_forward_group)

@@ -14,7 +14,7 @@ from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops
 from jax_tpu_embedding.sparsecore.lib.core.primitives import utils
 
 
-def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
+def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
           num_minibatches_per_physical_sparse_core, embedding_table, momentum, velocity, activations_grad, alpha_t,
           beta_1, beta_2, epsilon_hat, *_, max_ids_per_partition: int, max_unique_ids_per_partition: int,
           computation_name: str = "adam_optimizer_update", sharding_strategy: int = 1,
@@ -42,7 +42,7 @@ def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_g
   if enable_minibatching:
     raise NotImplementedError("minibatching exists to fit TPU on-chip memory and is not part of the B200 path")
   hyper = tuple(_ops.scalar_f32(h) for h in (alpha_t, beta_1, beta_2, epsilon_hat))
-  return _ops.run_grad(
+  return _ops.GradRequest(
       "adam", lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains, embedding_table,
       (momentum, velocity), activations_grad, hyper, min_value=min_value, max_value=max_value,
       num_sc_per_device=num_sc_per_device, global_device_count=global_device_count,
@@ -50,4 +50,4 @@ def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_g
 
 
 tpu_sparse_dense_matmul_grad_with_adam_primitive = _ops.Primitive(
-    "sparse_dense_matmul_grad_with_adam_primitive", _impl, multiple_results=True)
+    "sparse_dense_matmul_grad_with_adam_primitive", _prepare, _ops.run_grad_group, multiple_results=True)

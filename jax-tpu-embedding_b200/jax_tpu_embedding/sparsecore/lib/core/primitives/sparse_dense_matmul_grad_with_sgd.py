@@ -12,7 +12,7 @@ from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops
 from jax_tpu_embedding.sparsecore.lib.core.primitives import utils
 
 
-def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
+def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
           num_minibatches_per_physical_sparse_core, embedding_table, activations_grad, learning_rate, *_,
           max_ids_per_partition: int, max_unique_ids_per_partition: int,
           computation_name: str = "sgd_optimizer_update", sharding_strategy: int = 1,
@@ -26,12 +26,12 @@ def _impl(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_g
       max_unique_ids_per_partition, computation_name, sharding_strategy, min_value, max_value)
   if enable_minibatching:
     raise NotImplementedError("minibatching exists to fit TPU on-chip memory and is not part of the B200 path")
-  (table,) = _ops.run_grad(
+  return _ops.GradRequest(
       "sgd", lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains, embedding_table, (),
       activations_grad, (_ops.scalar_f32(learning_rate),), min_value=min_value, max_value=max_value,
       num_sc_per_device=num_sc_per_device, global_device_count=global_device_count,
       local_device_count=local_device_count)
-  return table
 
 
-tpu_sparse_dense_matmul_grad_with_sgd_primitive = _ops.Primitive("sparse_dense_matmul_grad_with_sgd", _impl)
+tpu_sparse_dense_matmul_grad_with_sgd_primitive = _ops.Primitive(
+    "sparse_dense_matmul_grad_with_sgd", _prepare, _ops.run_grad_group, unwrap=lambda r: r[0])

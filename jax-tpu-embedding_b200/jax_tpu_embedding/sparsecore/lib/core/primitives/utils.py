@@ -13,6 +13,9 @@ from typing import Any
 import numpy as np
 
 
+_DTYPE_CACHE: dict = {}
+
+
 def _np_dtype(x) -> np.dtype:
   """dtype of a numpy array, numpy/python scalar or torch tensor as a numpy dtype."""
   dt = getattr(x, "dtype", None)
@@ -24,9 +27,14 @@ def _np_dtype(x) -> np.dtype:
     if isinstance(x, float):
       return np.dtype(np.float32)
     return np.asarray(x).dtype
-  if type(dt).__module__.startswith("torch"):
-    return np.dtype(str(dt).replace("torch.", ""))
-  return np.dtype(dt)
+  cached = _DTYPE_CACHE.get(dt)
+  if cached is None:
+    if type(dt).__module__.startswith("torch"):
+      cached = np.dtype(str(dt).replace("torch.", ""))
+    else:
+      cached = np.dtype(dt)
+    _DTYPE_CACHE[dt] = cached
+  return cached
 
 
 def _shape(x) -> tuple[int, ...]:

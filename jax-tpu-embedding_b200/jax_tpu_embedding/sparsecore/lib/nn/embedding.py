@@ -28,6 +28,7 @@ import numpy as np
 from jax_tpu_embedding.sparsecore import _native
 from jax_tpu_embedding.sparsecore import _tree
 from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing
+from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops
 from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_csr
 from jax_tpu_embedding.sparsecore.lib.nn import embedding_spec
 from jax_tpu_embedding.sparsecore.lib.nn import table_stacking
@@ -396,41 +397,113 @@ def _max_ids_per_sample(feature_specs, stack_name: str) -> int:
   return 1
 
 
+class _SpecInfo:
+  """Per feature-spec-tree facts that do not change between steps (cached by object identity)."""
+
+  def __init__(self, feature_specs):
+    self.flat = _leaves(feature_specs)
+    self.stacked = get_stacked_table_specs(feature_specs)
+    self.members: dict[str, list] = collections.defaultdict(list)
+    for f in self.flat:
+      self.members[f.table_spec.stacked_table_spec.stack_name].append(f)
+    self.max_ids_per_sample = {}
+    self.trivial = {}  # stack holds one feature that is the whole stacked activation
+    for name, feats in self.members.items():
+      single_valent = all(len(tuple(f.input_shape)) >= 2 and tuple(f.input_shape)[-1] == 1 for f in feats)
+      self.max_ids_per_sample[name] = 1 if single_valent else 0
+      f = feats[0]
+      self.trivial[name] = (
+          len(feats) == 1 and f.id_transformation.row_offset == 0 and len(f.output_shape) == 2
+          and f.output_shape[-1] == f.table_spec.embedding_dim
+          and f.table_spec.embedding_dim == self.stacked[name].stack_embedding_dim
+          and f.output_shape[0] == self.stacked[name].total_sample_count)
+    self.all_trivial = all(self.trivial.values())
+    self.keep = feature_specs  # keeps the ids in the cache key alive
+
+
+_SPEC_INFO: dict = {}
+
+
+def _spec_info(feature_specs) -> _SpecInfo:
+  flat = _leaves(feature_specs)
+  key = tuple((id(f), id(f.table_spec._stacked_table_spec), id(f._id_transformation)) for f in flat)  # pylint: disable=protected-access
+  info = _SPEC_INFO.get(key)
+  if info is None:
+    if len(_SPEC_INFO) > 64:
+      _SPEC_INFO.clear()
+    info = _SPEC_INFO[key] = _SpecInfo(feature_specs)
+  return info
+
+
+def _is_cuda_tensor(x) -> bool:
+  return type(x).__module__.startswith("torch") and x.is_cuda and x.is_contiguous()
+
+
+_CALL_CACHE: dict = {}
+
+
+def _cache_put(key, value):
+  if len(_CALL_CACHE) > 32:
+    _CALL_CACHE.clear()
+  _CALL_CACHE[key] = value
+
+
 def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_specs, *, global_device_count: int,
                             sharding_strategy: str = "MOD", num_sc_per_device: int | None = None,
                             enable_minibatching: bool = False, perform_unstacking: bool = True,
                             use_activation_unstack_primitive: bool = False):
-  """Embedding lookup: one gather-combine per stacked table, then per-feature views."""
+  """Embedding lookup: one gather-combine per stacked table, then per-feature views.
+
+  All stacked tables are served by one grouped launch sequence.  When the same device buffers
+  are passed again (same addresses, sizes and specs) the validated launch descriptors of the
+  previous call are reused, so a training loop pays the per-table Python work once.
+  """
   if isinstance(preprocessed_inputs, SparseDenseMatmulInput):
     warnings.warn("SparseDenseMatmulInput is deprecated. Please use PreprocessedInput instead.", DeprecationWarning)
     preprocessed_inputs = PreprocessedInput(preprocessed_inputs)
   rps, eids, sids, gains = preprocessed_inputs.sparse_dense_matmul_input
   num_sc_per_device = _get_num_sc_per_device(num_sc_per_device)
   assert rps.keys() == embedding_variables.keys()
-  stacked_table_specs = get_stacked_table_specs(feature_specs)
+  info = _spec_info(feature_specs)
+  stacked_table_specs = info.stacked
   assert rps.keys() == stacked_table_specs.keys()
   strategy = int(sharding_strategy_to_enum(sharding_strategy))
 
-  activations = {}
-  local = 1
-  for name, stacked in stacked_table_specs.items():
-    local = _local_devices(rps[name], global_device_count, num_sc_per_device)
-    q = stacked.quantization_config
-    activations[name] = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
-        _flat(rps[name]), _flat(eids[name]), _flat(sids[name]), _flat(gains[name]), np.int32(1),
-        embedding_variables[name].table,
-        device_batch_size=stacked.total_sample_count // global_device_count,
-        max_ids_per_partition=stacked.max_ids_per_partition,
-        max_unique_ids_per_partition=stacked.max_unique_ids_per_partition,
-        sharding_strategy=strategy,
-        quantization_config=q.as_tuple() if q else None,
-        enable_minibatching=enable_minibatching,
-        num_sc_per_device=num_sc_per_device,
-        global_device_count=global_device_count,
-        local_device_count=local,
-        max_ids_per_sample=_max_ids_per_sample(feature_specs, name),
-    )
+  key = None
+  operands = [(rps[n], eids[n], sids[n], gains[n], embedding_variables[n].table) for n in stacked_table_specs]
+  if all(_is_cuda_tensor(x) for ops in operands for x in ops):
+    key = ("fwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching,
+           tuple((x.data_ptr(), tuple(x.shape), x.dtype) for ops in operands for x in ops))
+  cached = _CALL_CACHE.get(key) if key is not None else None
+  if cached is None:
+    requests, local = [], 1
+    for name, stacked in stacked_table_specs.items():
+      local = _local_devices(rps[name], global_device_count, num_sc_per_device)
+      q = stacked.quantization_config
+      requests.append(sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.prepare(
+          _flat(rps[name]), _flat(eids[name]), _flat(sids[name]), _flat(gains[name]), np.int32(1),
+          embedding_variables[name].table,
+          device_batch_size=stacked.total_sample_count // global_device_count,
+          max_ids_per_partition=stacked.max_ids_per_partition,
+          max_unique_ids_per_partition=stacked.max_unique_ids_per_partition,
+          sharding_strategy=strategy,
+          quantization_config=q.as_tuple() if q else None,
+          enable_minibatching=enable_minibatching,
+          num_sc_per_device=num_sc_per_device,
+          global_device_count=global_device_count,
+          local_device_count=local,
+          max_ids_per_sample=info.max_ids_per_sample[name],
+      ))
+    cached = (_ops.ForwardGroupCall(requests), local)
+    if key is not None:
+      _cache_put(key, cached)
+  call, local = cached
+  # One grouped launch sequence for all stacked tables (the reference issues one call per table).
+  activations = dict(zip(stacked_table_specs.keys(), call.run()))
   if perform_unstacking:
+    if info.all_trivial and local == 1:
+      return _tree.unflatten(feature_specs, [activations[f.table_spec.stacked_table_spec.stack_name]
+                                             for f in info.flat], is_leaf=_is_feature_leaf)
     activations = unstack_embedding_activations(
         activations, feature_specs, global_device_count, num_sc_per_device,
         use_activation_unstack_primitive=use_activation_unstack_primitive, local_device_count=local)
@@ -494,47 +567,72 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
     preprocessed_inputs = PreprocessedInput(preprocessed_inputs)
   rps, eids, sids, gains = preprocessed_inputs.sparse_dense_matmul_input
   assert rps.keys() == embedding_variables.keys()
-  stacked_table_specs = get_stacked_table_specs(feature_specs)
+  info = _spec_info(feature_specs)
+  stacked_table_specs = info.stacked
   assert rps.keys() == stacked_table_specs.keys()
   num_sc_per_device = _get_num_sc_per_device(num_sc_per_device)
   if global_device_count is None:
-    from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops  # pylint: disable=g-import-not-at-top
-
     global_device_count = _ops._world_size()  # pylint: disable=protected-access
   first = next(iter(rps))
   local = _local_devices(rps[first], global_device_count, num_sc_per_device)
 
   if perform_stacking:
     _assert_same_structure(feature_specs, activation_gradients, "feature_specs", "activation_gradients")
-    gradients = stack_embedding_gradients(activation_gradients, feature_specs, num_sc_per_device, global_device_count,
-                                          use_gradient_stacking_primitive, local_device_count=local)
+    grad_leaves = _leaves(activation_gradients)
+    if info.all_trivial and local == 1 and all(_is_cuda_tensor(g) and g.dim() == 2 for g in grad_leaves):
+      gradients = {f.table_spec.stacked_table_spec.stack_name: g for f, g in zip(info.flat, grad_leaves)}
+    else:
+      gradients = stack_embedding_gradients(activation_gradients, feature_specs, num_sc_per_device,
+                                            global_device_count, use_gradient_stacking_primitive,
+                                            local_device_count=local)
   else:
     assert isinstance(activation_gradients, Mapping)
     gradients = activation_gradients
   assert rps.keys() == gradients.keys()
   strategy = int(sharding_strategy_to_enum(sharding_strategy))
 
+  hypers = {n: tuple(float(h) for h in st.optimizer.get_hyperparameters(step)) for n, st in stacked_table_specs.items()}
+  limits = None if embedding_var_limits is None else tuple(
+      tuple(embedding_var_limits[n]) for n in stacked_table_specs)
+  key = None
+  operands = [(rps[n], eids[n], sids[n], gains[n], embedding_variables[n].table, *embedding_variables[n].slot,
+               gradients[n]) for n in stacked_table_specs]
+  if all(_is_cuda_tensor(x) for ops in operands for x in ops):
+    key = ("bwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, label, limits,
+           tuple(hypers.values()), tuple((x.data_ptr(), tuple(x.shape), x.dtype) for ops in operands for x in ops))
+  call = _CALL_CACHE.get(key) if key is not None else None
+  if call is None:
+    requests = []
+    for name, stacked in stacked_table_specs.items():
+      variables = embedding_variables[name]
+      hyper = stacked.optimizer.get_hyperparameters(step)
+      symbol = "{}-{}{}".format(stacked.optimizer.short_name(), stacked.stack_name, label)
+      extra = {}
+      if embedding_var_limits is not None:
+        extra["min_value"], extra["max_value"] = embedding_var_limits[name]
+      requests.append(stacked.optimizer.get_optimizer_primitive().prepare(
+          _flat(rps[name]), _flat(eids[name]), _flat(sids[name]), _flat(gains[name]), np.int32(1), variables.table,
+          *variables.slot, gradients[name], *hyper,
+          max_ids_per_partition=stacked.max_ids_per_partition,
+          max_unique_ids_per_partition=stacked.max_unique_ids_per_partition,
+          computation_name=symbol, sharding_strategy=strategy, enable_minibatching=enable_minibatching,
+          num_sc_per_device=num_sc_per_device, global_device_count=global_device_count, local_device_count=local,
+          **extra))
+    call = _ops.GradGroupCall(requests)
+    if key is not None:
+      _cache_put(key, call)
+  first_results = call.run()
+  # Tables and slot variables were updated in place; hand the same tensors back.
   updated = {}
-  for name, stacked in stacked_table_specs.items():
+  for index, name in enumerate(stacked_table_specs):
     variables = embedding_variables[name]
-    hyper = stacked.optimizer.get_hyperparameters(step)
-    symbol = "{}-{}{}".format(stacked.optimizer.short_name(), stacked.stack_name, label)
-    extra = {}
-    if embedding_var_limits is not None:
-      extra["min_value"], extra["max_value"] = embedding_var_limits[name]
-    flat_vars = [variables.table, *variables.slot]
-    results = stacked.optimizer.get_optimizer_primitive().bind(
-        _flat(rps[name]), _flat(eids[name]), _flat(sids[name]), _flat(gains[name]), np.int32(1), *flat_vars,
-        gradients[name], *hyper,
-        max_ids_per_partition=stacked.max_ids_per_partition,
-        max_unique_ids_per_partition=stacked.max_unique_ids_per_partition,
-        computation_name=symbol, sharding_strategy=strategy, enable_minibatching=enable_minibatching,
-        num_sc_per_device=num_sc_per_device, global_device_count=global_device_count, local_device_count=local,
-        **extra)
-    results = list(results) if isinstance(results, (tuple, list)) else [results]
-    slot_type = type(variables.slot)
-    slots = slot_type(*results[1:]) if hasattr(slot_type, "_fields") else tuple(results[1:])
-    updated[name] = EmbeddingVariables(table=results[0], slot=slots)
+    if _is_cuda_tensor(variables.table) and all(_is_cuda_tensor(x) for x in variables.slot):
+      updated[name] = variables
+    else:
+      results = first_results[index]
+      slot_type = type(variables.slot)
+      slots = slot_type(*results[1:]) if hasattr(slot_type, "_fields") else tuple(results[1:])
+      updated[name] = EmbeddingVariables(table=results[0], slot=slots)
   return updated
 
 
@@ -572,8 +670,6 @@ def init_embedding_variables(rng, table_specs, global_sharding: DeviceLayout | i
   torch = _native.torch_mod()
   s = _get_num_sc_per_device(num_sparsecore_per_device)
   if global_sharding is None:
-    from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops  # pylint: disable=g-import-not-at-top
-
     world = _ops._world_size()  # pylint: disable=protected-access
     layout = DeviceLayout(world, 1 if world > 1 else None,
                           torch.distributed.get_rank() if world > 1 else 0)
