@@ -373,10 +373,12 @@ def main():
   ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   if args.profile_range:
     torch.cuda.profiler.start()
+  launches0 = _native.lib().sc_launch_count()
   ev0.record()
   for _ in range(args.steps):
     lookup_update()
   ev1.record()
+  gpu_launches = int(_native.lib().sc_launch_count() - launches0)
   barrier()
   if args.profile_range:
     torch.cuda.profiler.stop()
@@ -444,14 +446,12 @@ def main():
       dev_feats = []
       for p in pinned:
         if isinstance(p, torch.Tensor):
-          dev_feats.append(_DenseOnDevice(p.cuda(non_blocking=True)))
+          dev_feats.append(p.cuda(non_blocking=True))
         else:
           dev_feats.append(embedding.RaggedInput(p.values.cuda(non_blocking=True), p.row_splits,
                                                  None if p.weights is None else p.weights.cuda(non_blocking=True)))
-      dev_w = None if pinned_w is None else [_DenseOnDevice(w.cuda(non_blocking=True)) for w in pinned_w]
-      feats_in = [d.as_ragged(dev_w[i] if dev_w else None) if isinstance(d, _DenseOnDevice) else d
-                  for i, d in enumerate(dev_feats)]
-      p2, _ = embedding.preprocess_sparse_dense_matmul_input(feats_in, None, specs, 1, 1, num_sc_per_device=1)
+      dev_w = None if pinned_w is None else [w.cuda(non_blocking=True) for w in pinned_w]
+      p2, _ = embedding.preprocess_sparse_dense_matmul_input(dev_feats, dev_w, specs, 1, 1, num_sc_per_device=1)
       acts = embedding.tpu_sparse_dense_matmul(p2, variables, specs, global_device_count=1, num_sc_per_device=1)
       checksum = torch.stack([a.sum() for a in acts]).sum()
       embedding.tpu_sparse_dense_matmul_grad(grads, p2, variables, specs, global_device_count=1, num_sc_per_device=1,
@@ -482,7 +482,6 @@ def main():
                      f"C preprocessing {r['preprocess_ms']:.0f} ms)"}
 
   if rank == 0:
-    launches_per_table_fwd, launches_per_table_bwd = 10, 2
     line = {
         "metric": "samples/s fwd+Adagrad bwd", "value": samples_per_s, "unit": "samples/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
@@ -495,27 +494,12 @@ def main():
                                  "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                                  "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak}},
         "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
-        "gpu_launches": args.steps * len(stacked) * (launches_per_table_fwd + launches_per_table_bwd),
+        "gpu_launches": gpu_launches,
         "table_bytes": int(table_bytes),
     }
     print(json.dumps(line))
   if world > 1:
     torch.distributed.destroy_process_group()
-
-
-class _DenseOnDevice:
-  """A dense [B, v] int32 feature already on the GPU, viewed as a RaggedInput without a host copy."""
-
-  def __init__(self, tensor):
-    self.tensor = tensor
-
-  def as_ragged(self, weights=None):
-    from jax_tpu_embedding.sparsecore.lib.nn import embedding
-
-    b, v = self.tensor.shape
-    splits = np.arange(b + 1, dtype=np.int64) * v
-    return embedding.RaggedInput(self.tensor.reshape(-1), splits,
-                                 None if weights is None else weights.tensor.reshape(-1))
 
 
 if __name__ == "__main__":

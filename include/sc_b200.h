@@ -44,6 +44,8 @@ enum sc_combiner { SC_COMBINER_SUM = 0, SC_COMBINER_MEAN = 1, SC_COMBINER_SQRTN 
 int32_t sc_version(void);
 const char* sc_status_name(int32_t status);
 int32_t sc_last_error(char* buffer, int32_t buffer_bytes);
+/* Number of CUDA kernels this library has launched in the process so far. */
+int64_t sc_launch_count(void);
 
 /* ---------------------------------------------------------------- buffer sizing
  * Replaces ComputeCooBufferSizePerDevice / GetRowPointersSizePerDevice
@@ -74,6 +76,8 @@ typedef struct {
   int32_t row_offset; /* FeatureIdTransformation.row_offset (global samples before this feature) */
   int32_t col_offset; /* row_offset_in_shard * num_scs of the feature's table */
   int32_t col_shift;  /* shard rotation of the feature's table */
+  int32_t valency;    /* > 0: every row has exactly `valency` ids and row_offsets is not read for it */
+  int32_t id_begin;   /* with valency > 0: index of the feature's first id inside `ids` */
 } sc_feature_desc_t;
 
 typedef struct {
@@ -98,6 +102,29 @@ int32_t sc_preprocess_table(const int32_t* ids_device, const int32_t* row_offset
                             const sc_preprocess_options_t* options, int32_t* row_pointers_device,
                             int32_t* embedding_ids_device, int32_t* sample_ids_device, float* gains_device,
                             int32_t* stats_device, void* workspace_device, size_t workspace_bytes, sc_stream_t stream);
+
+/* Grouped variant: all stacked tables of a model (and all local devices) in one call; every
+ * kernel is launched once for the whole group.  The group's sort key must fit 32 bits:
+ * bits(table index) + max over tables of bits(num_sc_per_device * stack_vocab_size). */
+typedef struct {
+  const int32_t* ids;          /* device */
+  const int32_t* row_offsets;  /* device, may be NULL when every feature has a fixed valency */
+  const float* weights;        /* device or NULL */
+  int64_t nnz;
+  int64_t total_rows;
+  const sc_feature_desc_t* features; /* host */
+  int32_t num_features;
+  sc_preprocess_options_t options;
+  int32_t* row_pointers;       /* device outputs */
+  int32_t* embedding_ids;
+  int32_t* sample_ids;
+  float* gains;
+  int32_t* stats;
+} sc_preprocess_item_t;
+
+size_t sc_preprocess_grouped_workspace_bytes(const sc_preprocess_item_t* items, int32_t count);
+int32_t sc_preprocess_grouped(const sc_preprocess_item_t* items, int32_t count, void* workspace_device,
+                              size_t workspace_bytes, sc_stream_t stream);
 
 /* ---------------------------------------------------------------- lookup / update
  * One device buffer of CSR-wrapped COO input plus the geometry of the stacked table. */

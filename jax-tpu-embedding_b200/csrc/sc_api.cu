@@ -1,6 +1,8 @@
 // Library-wide entry points: version, status names, last-error text and the host-side
 // buffer sizing arithmetic.
 #include <stdarg.h>
+
+#include <atomic>
 #include <string.h>
 
 #include "sc_common.cuh"
@@ -15,6 +17,10 @@ void set_error(const char* fmt, ...) {
   vsnprintf(g_error, sizeof g_error, fmt, ap);
   va_end(ap);
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
 int sm_count() {
   static int cached[64] = {0};
@@ -31,6 +37,9 @@ int sm_count() {
 }  // namespace sc
 
 extern "C" int32_t sc_version(void) { return 100; }
+
+namespace sc { long long launches(); }
+extern "C" int64_t sc_launch_count(void) { return (int64_t)sc::launches(); }
 
 extern "C" const char* sc_status_name(int32_t status) {
   switch (status) {

@@ -27,6 +27,7 @@ void set_error(const char* fmt, ...);
 
 #define SC_LAUNCH_OK(name)                                                                        \
   do {                                                                                            \
+    ::sc::count_launch();                                                                         \
     cudaError_t err__ = cudaGetLastError();                                                       \
     if (err__ != cudaSuccess) SC_FAIL(SC_CUDA_ERROR, "launch %s: %s", name, cudaGetErrorString(err__)); \
   } while (0)
@@ -59,6 +60,9 @@ class Workspace {
   size_t bytes_;
   size_t used_ = 0;
 };
+
+// Counts kernel launches issued by this library (read with sc_launch_count).
+void count_launch(int n = 1);
 
 // Number of SMs of the current device (cached per device).
 int sm_count();

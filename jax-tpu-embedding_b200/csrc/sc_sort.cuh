@@ -108,10 +108,12 @@ inline cudaError_t exclusive_scan(const T* in, T* out, size_t n, T* temp, T* tot
   const size_t tiles = (size_t)ceil_div((int64_t)n, kScanTile);
   if (tiles == 1) {
     scan_tile_kernel<T><<<1, kScanThreads, 0, stream>>>(in, out, n, nullptr, total_out);
+    count_launch();
     return cudaGetLastError();
   }
   T* sums = temp;
   scan_reduce_kernel<T><<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, sums, n);
+  count_launch(2);  // this kernel and the tile scan below
   cudaError_t err = exclusive_scan<T>(sums, sums, tiles, temp + align_up(tiles, 64), total_out, stream);
   if (err != cudaSuccess) return err;
   scan_tile_kernel<T><<<(unsigned)tiles, kScanThreads, 0, stream>>>(in, out, n, sums, nullptr);
@@ -240,6 +242,7 @@ inline cudaError_t radix_sort_pairs(SortBuffers& b, size_t n, int bits, bool iot
     const int pass_bits = min(kRadixBits, bits - shift);
     const uint32_t mask = (1u << pass_bits) - 1u;
     radix_hist_kernel<<<tiles, kSortThreads, 0, stream>>>(b.keys[cur], b.hist, n, shift, mask, tiles);
+    count_launch(2);  // histogram and scatter of this pass
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     err = exclusive_scan<uint32_t>(b.hist, b.hist, (size_t)kRadix * tiles, b.scan_temp, nullptr, stream);

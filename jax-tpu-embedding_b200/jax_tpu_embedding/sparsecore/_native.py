@@ -31,13 +31,19 @@ c_i32, c_i64, c_f32, c_vp, c_sz = (ctypes.c_int32, ctypes.c_int64, ctypes.c_floa
 
 class FeatureDesc(ctypes.Structure):
   _fields_ = [("row_begin", c_i32), ("rows", c_i32), ("row_offset", c_i32), ("col_offset", c_i32),
-              ("col_shift", c_i32)]
+              ("col_shift", c_i32), ("valency", c_i32), ("id_begin", c_i32)]
 
 
 class PreprocessOptions(ctypes.Structure):
   _fields_ = [("global_device_count", c_i32), ("num_sc_per_device", c_i32), ("combiner", c_i32),
               ("max_ids_per_partition", c_i32), ("max_unique_ids_per_partition", c_i32),
               ("allow_id_dropping", c_i32), ("coo_buffer_size_per_device", c_i32), ("stack_vocab_size", c_i32)]
+
+
+class PreprocessItem(ctypes.Structure):
+  _fields_ = [("ids", c_vp), ("row_offsets", c_vp), ("weights", c_vp), ("nnz", c_i64), ("total_rows", c_i64),
+              ("features", ctypes.POINTER(FeatureDesc)), ("num_features", c_i32), ("options", PreprocessOptions),
+              ("row_pointers", c_vp), ("embedding_ids", c_vp), ("sample_ids", c_vp), ("gains", c_vp), ("stats", c_vp)]
 
 
 class Csr(ctypes.Structure):
@@ -82,6 +88,7 @@ def lib() -> ctypes.CDLL:
           "The SparseCore operators have no CPU fallback.")
     l = ctypes.CDLL(LIB_PATH)
     l.sc_version.restype = c_i32
+    l.sc_launch_count.restype = c_i64
     l.sc_status_name.restype = ctypes.c_char_p
     l.sc_status_name.argtypes = [c_i32]
     l.sc_last_error.restype = c_i32
@@ -99,6 +106,10 @@ def lib() -> ctypes.CDLL:
     l.sc_preprocess_table.restype = c_i32
     l.sc_preprocess_table.argtypes = [c_vp, c_vp, c_vp, c_i64, c_i64, ctypes.POINTER(FeatureDesc), c_i32,
                                       ctypes.POINTER(PreprocessOptions), c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_sz, c_vp]
+    l.sc_preprocess_grouped_workspace_bytes.restype = c_sz
+    l.sc_preprocess_grouped_workspace_bytes.argtypes = [ctypes.POINTER(PreprocessItem), c_i32]
+    l.sc_preprocess_grouped.restype = c_i32
+    l.sc_preprocess_grouped.argtypes = [ctypes.POINTER(PreprocessItem), c_i32, c_vp, c_sz, c_vp]
     l.sc_sparse_dense_matmul_fwd_workspace_bytes.restype = c_sz
     l.sc_sparse_dense_matmul_fwd_workspace_bytes.argtypes = [ctypes.POINTER(Csr)]
     l.sc_sparse_dense_matmul_fwd.restype = c_i32

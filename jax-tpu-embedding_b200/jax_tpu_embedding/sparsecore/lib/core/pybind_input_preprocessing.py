@@ -137,54 +137,103 @@ def _feature_rows(feature) -> int:
   return feature.shape[0]
 
 
-def _slice_to_csr(feature, weights, lo: int, hi: int):
-  """Rows [lo, hi) of one feature as (ids, lengths-or-offsets..., weights) host arrays."""
-  if isinstance(feature, RaggedInput):
-    splits = feature.row_splits
-    b, e = int(splits[lo]), int(splits[hi])
-    w = feature.weights if feature.weights is not None else weights
-    return feature.values[b:e], splits[lo:hi + 1] - splits[lo], (None if w is None else w[b:e])
-  arr = np.asarray(feature)
-  if arr.dtype != object and arr.ndim == 2:
-    rows = arr[lo:hi]
-    ids = np.ascontiguousarray(rows, dtype=np.int32).reshape(-1)
-    offsets = np.arange(hi - lo + 1, dtype=np.int64) * arr.shape[1]
-    w = None
-    if weights is not None:
-      w = np.ascontiguousarray(np.asarray(weights)[lo:hi], dtype=np.float32).reshape(-1)
-    return ids, offsets, w
-  if arr.ndim != 1:
-    raise ValueError("Only 1D and 2D numpy arrays supported as inputs.")
-  rows = [np.asarray(r, dtype=np.int32).reshape(-1) for r in arr[lo:hi]]
-  lens = np.fromiter((len(r) for r in rows), dtype=np.int64, count=len(rows))
-  offsets = np.zeros(len(rows) + 1, dtype=np.int64)
-  np.cumsum(lens, out=offsets[1:])
-  ids = np.concatenate(rows) if rows else np.zeros(0, np.int32)
-  w = None
-  if weights is not None:
-    wr = [np.asarray(r, dtype=np.float32).reshape(-1) for r in np.asarray(weights, dtype=object)[lo:hi]]
-    w = np.concatenate(wr) if wr else np.zeros(0, np.float32)
-    if len(w) != len(ids):
-      raise ValueError("Dimension mismatch for features and weights")
-  return ids, offsets, w
-
-
-def _concat(parts, dtype):
-  torch = _native.torch_mod()
-  if any(_is_torch(p) for p in parts):
-    tdt = {np.int32: torch.int32, np.float32: torch.float32}[dtype]
-    ts = [p.to(device="cuda", dtype=tdt) if _is_torch(p) else torch.from_numpy(np.ascontiguousarray(p, dtype=dtype)).cuda()
-          for p in parts]
-    return ts[0] if len(ts) == 1 else torch.cat(ts)
-  arrs = [np.ascontiguousarray(p, dtype=dtype) for p in parts]
-  return arrs[0] if len(arrs) == 1 else np.concatenate(arrs)
-
-
 def _to_cuda(x, tdt):
   torch = _native.torch_mod()
   if _is_torch(x):
-    return x.to(device="cuda", dtype=tdt).contiguous()
-  return torch.from_numpy(np.ascontiguousarray(x)).to(device="cuda", dtype=tdt, non_blocking=True)
+    if x.is_cuda and x.dtype == tdt and x.is_contiguous():
+      return x
+    return x.to(device="cuda", dtype=tdt, non_blocking=True).contiguous()
+  npdt = {torch.int32: np.int32, torch.float32: np.float32}[tdt]
+  return torch.from_numpy(np.ascontiguousarray(x, dtype=npdt)).to(device="cuda", non_blocking=True)
+
+
+def _cat(parts, tdt):
+  torch = _native.torch_mod()
+  parts = [_to_cuda(p, tdt) for p in parts]
+  return parts[0] if len(parts) == 1 else torch.cat(parts)
+
+
+class _DeviceBatch:
+  """The rows of one stacked table that one device processes, as device arrays + descriptors."""
+
+  def __init__(self, members, features, feature_weights, device_index: int, local_device_count: int):
+    torch = _native.torch_mod()
+    ids_parts, off_parts, w_parts, descs = [], [], [], []
+    id_base, row_base = 0, 0
+    any_ragged, any_weights = False, False
+    for idx, spec in members:
+      feature = features[idx]
+      weights = None if feature_weights is None else feature_weights[idx]
+      rows_total = _feature_rows(feature)
+      per_dev = rows_total // local_device_count
+      lo, hi = device_index * per_dev, (device_index + 1) * per_dev
+      transform = _transform(spec)
+      if isinstance(feature, RaggedInput):
+        splits = feature.row_splits
+        b, e = int(splits[lo]), int(splits[hi])
+        ids_parts.append(feature.values[b:e])
+        off = splits[lo:hi] - splits[lo] + id_base
+        off_parts.append(off)
+        w = feature.weights if feature.weights is not None else weights
+        w_parts.append(None if w is None else w[b:e])
+        descs.append(_native.FeatureDesc(row_base, per_dev, *transform, 0, 0))
+        n_ids = e - b
+        any_ragged = True
+      elif _is_torch(feature) or (isinstance(feature, np.ndarray) and feature.dtype != object):
+        if feature.ndim != 2:
+          raise ValueError("Only 1D and 2D numpy arrays supported as inputs.")
+        valency = int(feature.shape[1])
+        ids_parts.append(feature[lo:hi].reshape(-1))
+        off_parts.append(("dense", per_dev, valency, id_base))
+        w_parts.append(None if weights is None else weights[lo:hi].reshape(-1))
+        descs.append(_native.FeatureDesc(row_base, per_dev, *transform, valency, id_base))
+        n_ids = per_dev * valency
+        if valency == 0:
+          any_ragged = True
+      else:
+        arr = np.asarray(feature)
+        if arr.ndim != 1:
+          raise ValueError("Only 1D and 2D numpy arrays supported as inputs.")
+        rows = [np.asarray(r, dtype=np.int32).reshape(-1) for r in arr[lo:hi]]
+        lens = np.fromiter((len(r) for r in rows), dtype=np.int64, count=len(rows))
+        off = np.zeros(len(rows), dtype=np.int64)
+        if len(rows) > 1:
+          np.cumsum(lens[:-1], out=off[1:])
+        n_ids = int(lens.sum())
+        ids_parts.append(np.concatenate(rows) if n_ids else np.zeros(0, np.int32))
+        off_parts.append(off + id_base)
+        if weights is None:
+          w_parts.append(None)
+        else:
+          wr = [np.asarray(r, dtype=np.float32).reshape(-1) for r in np.asarray(weights, dtype=object)[lo:hi]]
+          w = np.concatenate(wr) if wr else np.zeros(0, np.float32)
+          if len(w) != n_ids:
+            raise ValueError("Dimension mismatch for features and weights")
+          w_parts.append(w)
+        descs.append(_native.FeatureDesc(row_base, per_dev, *transform, 0, 0))
+        any_ragged = True
+      any_weights = any_weights or w_parts[-1] is not None
+      id_base += n_ids
+      row_base += per_dev
+    self.nnz, self.total_rows = id_base, row_base
+    self.descs = (_native.FeatureDesc * len(descs))(*descs)
+    self.ids = _cat(ids_parts, torch.int32) if id_base else torch.zeros(1, dtype=torch.int32, device="cuda")
+    self.offsets = None
+    if any_ragged:
+      full = []
+      for o in off_parts:
+        if isinstance(o, tuple):
+          _, rows, valency, base = o
+          full.append(np.arange(rows, dtype=np.int64) * valency + base)
+        else:
+          full.append(o)
+      full.append(np.asarray([id_base], np.int64))
+      self.offsets = _cat(full, torch.int32)
+    self.weights = None
+    if any_weights:
+      ws = [w if w is not None else np.ones(int(p.numel() if _is_torch(p) else np.size(p)), np.float32)
+            for w, p in zip(w_parts, ids_parts)]
+      self.weights = _cat(ws, torch.float32)
 
 
 # ------------------------------------------------------------------------------ device call
@@ -212,7 +261,7 @@ def preprocess_stack_on_device(ids, row_offsets, weights, feature_descs, *, glob
   descs = (_native.FeatureDesc * nfeat)()
   row = 0
   for i, (rows, row_offset, col_offset, col_shift) in enumerate(feature_descs):
-    descs[i] = _native.FeatureDesc(row, int(rows), int(row_offset), int(col_offset), int(col_shift))
+    descs[i] = _native.FeatureDesc(row, int(rows), int(row_offset), int(col_offset), int(col_shift), 0, 0)
     row += int(rows)
   total_rows = row
   nnz = int(ids.numel())
@@ -301,63 +350,82 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
     raise ValueError("features and feature_specs must have the same length")
 
   torch = _native.require_cuda()
+  lib = _native.lib()
   l, s = local_device_count, num_sc_per_device
   out_rp, out_ids, out_sids, out_gains = {}, {}, {}, {}
   stats = SparseDenseMatmulInputStats()
-  pending = []
-  for stack_name, members in _group_by_stack(feature_specs).items():
+  stacks = list(_group_by_stack(feature_specs).items())
+  rp_size = max(p, 8) * s
+  stats_size = 2 * p + s + 3
+  coos = []
+  for _, members in stacks:
     stacked = members[0][1].table_spec.stacked_table_spec
-    coo = _coo_buffer_size(stacked.max_ids_per_partition, global_device_count, s,
-                           stacked.suggested_coo_buffer_size_per_device)
-    rp_size = max(p, 8) * s
-    dev_out = (torch.empty((l, rp_size), dtype=torch.int32, device="cuda"),
-               torch.empty((l, coo), dtype=torch.int32, device="cuda"),
-               torch.empty((l, coo), dtype=torch.int32, device="cuda"),
-               torch.empty((l, coo), dtype=torch.float32, device="cuda"))
-    stats_dev = []
+    coos.append(_coo_buffer_size(stacked.max_ids_per_partition, global_device_count, s,
+                                 stacked.suggested_coo_buffer_size_per_device))
+  # One int32 buffer holds [row pointers | embedding ids | sample ids] of every stack and device,
+  # one float32 buffer the gains, one int32 buffer the statistics.
+  int_total = sum(l * (rp_size + 2 * c) for c in coos)
+  ints = torch.empty(int_total, dtype=torch.int32, device="cuda")
+  floats = torch.empty(sum(l * c for c in coos), dtype=torch.float32, device="cuda")
+  stats_dev = torch.empty((len(stacks), l, stats_size), dtype=torch.int32, device="cuda")
+  items = (_native.PreprocessItem * (len(stacks) * l))()
+  keep, views = [], []
+  ipos = fpos = 0
+  for si, ((stack_name, members), coo) in enumerate(zip(stacks, coos)):
+    stacked = members[0][1].table_spec.stacked_table_spec
+    rp_v = ints[ipos:ipos + l * rp_size].view(l, rp_size); ipos += l * rp_size
+    id_v = ints[ipos:ipos + l * coo].view(l, coo); ipos += l * coo
+    sid_v = ints[ipos:ipos + l * coo].view(l, coo); ipos += l * coo
+    gain_v = floats[fpos:fpos + l * coo].view(l, coo); fpos += l * coo
+    views.append((rp_v, id_v, sid_v, gain_v))
+    opt = _native.PreprocessOptions(int(global_device_count), int(s), _native.COMBINERS.get(stacked.combiner, 0),
+                                    int(stacked.max_ids_per_partition), int(stacked.max_unique_ids_per_partition),
+                                    int(bool(allow_id_dropping)), int(coo), int(stacked.stack_vocab_size))
     for d in range(l):
-      ids_parts, off_parts, w_parts, descs = [], [], [], []
-      base = 0
-      for idx, spec in members:
-        rows_total = _feature_rows(features[idx])
-        per_dev = rows_total // l
-        w_in = None if feature_weights is None else feature_weights[idx]
-        ids_f, off_f, w_f = _slice_to_csr(features[idx], w_in, d * per_dev, (d + 1) * per_dev)
-        ids_parts.append(ids_f)
-        off_parts.append(off_f[:-1] + base)
-        base += int(off_f[-1])
-        if w_f is not None:
-          w_parts.append(w_f)
-        elif feature_weights is not None:
-          w_parts.append(np.ones(len(ids_f), np.float32))
-        descs.append((per_dev,) + _transform(spec))
-      tail = torch.tensor([base]) if any(_is_torch(o) for o in off_parts) else np.asarray([base], np.int64)
-      off_parts.append(tail)
-      ids_t = _to_cuda(_concat(ids_parts, np.int32), torch.int32)
-      if any(_is_torch(o) for o in off_parts):
-        off_t = torch.cat([o.to(device="cuda", dtype=torch.int32) if _is_torch(o)
-                           else torch.from_numpy(np.asarray(o)).to(device="cuda", dtype=torch.int32) for o in off_parts])
-      else:
-        off_t = _to_cuda(np.concatenate(off_parts), torch.int32)
-      w_t = _to_cuda(_concat(w_parts, np.float32), torch.float32) if w_parts else None
-      outs = tuple(t[d] for t in dev_out)
-      *_, st = preprocess_stack_on_device(
-          ids_t, off_t, w_t, descs, global_device_count=global_device_count, num_sc_per_device=s,
-          combiner=stacked.combiner, max_ids_per_partition=stacked.max_ids_per_partition,
-          max_unique_ids_per_partition=stacked.max_unique_ids_per_partition, allow_id_dropping=allow_id_dropping,
-          coo_buffer_size_per_device=coo, stack_vocab_size=stacked.stack_vocab_size, outputs=outs)
-      stats_dev.append(st)
-    pending.append((stack_name, stacked, dev_out, torch.stack(stats_dev)))
+      batch = _DeviceBatch(members, features, feature_weights, d, l)
+      keep.append(batch)
+      it = items[si * l + d]
+      it.ids = batch.ids.data_ptr()
+      it.row_offsets = None if batch.offsets is None else batch.offsets.data_ptr()
+      it.weights = None if batch.weights is None else batch.weights.data_ptr()
+      it.nnz, it.total_rows = batch.nnz, batch.total_rows
+      it.features = batch.descs
+      it.num_features = len(batch.descs)
+      it.options = opt
+      it.row_pointers = rp_v[d].data_ptr()
+      it.embedding_ids = id_v[d].data_ptr()
+      it.sample_ids = sid_v[d].data_ptr()
+      it.gains = gain_v[d].data_ptr()
+      it.stats = stats_dev[si, d].data_ptr()
+  # Groups are bounded by the 32-bit sort key: split greedily when a group does not fit.
+  start, count = 0, len(items)
+  stream = _native.current_stream_ptr()
+  while start < count:
+    n = count - start
+    while True:
+      sub = ctypes.cast(ctypes.byref(items, start * ctypes.sizeof(_native.PreprocessItem)),
+                        ctypes.POINTER(_native.PreprocessItem))
+      nbytes = lib.sc_preprocess_grouped_workspace_bytes(sub, n)
+      if nbytes or n == 1:
+        break
+      n = (n + 1) // 2
+    if nbytes == 0:
+      _native.check(lib.sc_preprocess_grouped(sub, n, None, 0, None))
+    ws = _native.workspace(nbytes, "preprocess")
+    _native.check(lib.sc_preprocess_grouped(sub, n, ws.data_ptr(), ws.numel(), stream))
+    start += n
 
-  for stack_name, stacked, dev_out, stats_dev in pending:
-    host = stats_dev.cpu().numpy()  # synchronises with the stream
+  host = stats_dev.cpu().numpy()  # the only synchronisation of the call
+  del keep
+  for si, ((stack_name, members), dev_out) in enumerate(zip(stacks, views)):
+    stacked = members[0][1].table_spec.stacked_table_spec
     for d in range(l):
-      _raise_for_status(host[d], p, s, stack_name, stacked.max_ids_per_partition,
+      _raise_for_status(host[si, d], p, s, stack_name, stacked.max_ids_per_partition,
                         stacked.max_unique_ids_per_partition)
-    stats.max_ids_per_partition[stack_name] = host[:, :p].reshape(-1).copy()
-    stats.max_unique_ids_per_partition[stack_name] = host[:, p:2 * p].reshape(-1).copy()
-    stats.required_buffer_sizes[stack_name] = host[:, 2 * p:2 * p + s].reshape(-1).copy()
-    stats.dropped_id_count[stack_name] = int(host[:, 2 * p + s].sum())
+    stats.max_ids_per_partition[stack_name] = host[si, :, :p].reshape(-1).copy()
+    stats.max_unique_ids_per_partition[stack_name] = host[si, :, p:2 * p].reshape(-1).copy()
+    stats.required_buffer_sizes[stack_name] = host[si, :, 2 * p:2 * p + s].reshape(-1).copy()
+    stats.dropped_id_count[stack_name] = int(host[si, :, 2 * p + s].sum())
     arrays = dev_out if has_leading_dimension else tuple(t.reshape(-1) for t in dev_out)
     if not device_output:
       arrays = tuple(t.cpu().numpy() for t in arrays)
