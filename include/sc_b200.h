@@ -194,6 +194,29 @@ size_t sc_sparse_dense_matmul_grad_grouped_workspace_bytes(const sc_grad_item_t*
 int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* items, int32_t count, void* workspace_device,
                                             size_t workspace_bytes, sc_stream_t stream);
 
+/* Fused backward + optimizer update for callers that cannot allocate device memory at all:
+ * an embedding server whose device memory was carved up completely at start-up, a plugin invoked
+ * from inside another runtime's execution callback where cudaMalloc is forbidden, or a
+ * latency-critical loop that must never wait on the driver's allocator lock - places where even
+ * asking a framework for a workspace tensor may end in cudaMalloc.  (No counterpart in the
+ * reference project: there the XLA runtime owns all buffers.)
+ *
+ * Same arithmetic and kernels as sc_sparse_dense_matmul_grad, but the scratch lives in a
+ * SC_STATIC_SCRATCH_BYTES array built into the library image, so the call performs no
+ * cudaMalloc / cudaFree and takes no workspace.  Limits: one shard and one SparseCore per buffer
+ * (num_scs == num_sc_per_device == 1) and
+ *   512 + 2 * ceil(coo_buffer_size / 32) * dim * 4  <=  SC_STATIC_SCRATCH_BYTES,
+ * e.g. 65536 slots at dim 128; larger inputs are rejected with SC_WORKSPACE_TOO_SMALL.
+ * The first call on each device resolves the address of the array (cudaGetSymbolAddress); make
+ * that first call before any stream capture begins.  All calls on a device share the one array:
+ * the call overwrites every scratch word it later reads, so nothing needs clearing, but two
+ * calls that overlap on the GPU (different streams) race and must be serialised by the caller. */
+#define SC_STATIC_SCRATCH_BYTES (2 * 1024 * 1024 + 4096)
+int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const float* activation_grad_device,
+                                           float* const* shard_tables_host, float* const* shard_slot0_host,
+                                           float* const* shard_slot1_host, const sc_optimizer_t* optimizer,
+                                           sc_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -992,3 +992,79 @@ extern "C" int32_t sc_sparse_dense_matmul_grad(const sc_csr_t* csr, const float*
   sc_grad_item_t item = {*csr, activation_grad, shard_tables, shard_slot0, shard_slot1, *optimizer};
   return sc_sparse_dense_matmul_grad_grouped(&item, 1, workspace, workspace_bytes, stream);
 }
+
+// ---- update without any allocation -----------------------------------------------------------
+// Scratch of sc_sparse_dense_matmul_grad_static: one descriptor block followed by the per-chunk
+// partial sums.  Every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[SC_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of g_static_scratch per device ordinal, resolved on first use.
+void* g_static_scratch_ptr[64] = {nullptr};
+}  // namespace
+
+extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const float* activation_grad,
+                                                      float* const* shard_tables, float* const* shard_slot0,
+                                                      float* const* shard_slot1, const sc_optimizer_t* optimizer,
+                                                      sc_stream_t stream) {
+  if (!csr || !optimizer) SC_FAIL(SC_INVALID_ARGUMENT, "null descriptor");
+  CsrView v;
+  int st = make_view(csr, &v);
+  if (st != SC_OK) return st;
+  if (v.S != 1 || v.P != 1)
+    SC_FAIL(SC_UNSUPPORTED, "the allocation-free update handles one shard and one SparseCore per buffer (got %d, %d)", v.P, v.S);
+  const int kind = optimizer->optimizer;
+  if (kind < 0 || kind > 2) SC_FAIL(SC_INVALID_ARGUMENT, "unknown optimizer");
+  if (!activation_grad || !shard_tables || !shard_tables[0]) SC_FAIL(SC_INVALID_ARGUMENT, "null gradient or table pointer");
+  if (kind >= 1 && (!shard_slot0 || !shard_slot0[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 0");
+  if (kind >= 2 && (!shard_slot1 || !shard_slot1[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
+  if (!isnan(optimizer->clip_min) && !isnan(optimizer->clip_max) && optimizer->clip_min > optimizer->clip_max)
+    SC_FAIL(SC_INVALID_ARGUMENT, "min_value must be less than or equal to max_value");
+  int w, k;
+  if (!pick_shape(v.dim, &w, &k)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
+
+  // Layout inside the static array: [TableDesc | 3 shard pointers | partial sums].
+  const size_t image = align_up(sizeof(TableDesc), 256) + align_up(3 * sizeof(float*), 256);
+  const uint32_t chunks = (uint32_t)ceil_div(v.coo, 32);
+  const size_t need = image + (size_t)2 * chunks * (size_t)v.dim * sizeof(float);
+  if (need > (size_t)SC_STATIC_SCRATCH_BYTES)
+    SC_FAIL(SC_WORKSPACE_TOO_SMALL,
+            "the allocation-free update needs %zu scratch bytes for coo_buffer_size %d and dim %d but the built-in scratch "
+            "holds %d; use sc_sparse_dense_matmul_grad with a caller workspace instead", need, v.coo, v.dim,
+            (int)SC_STATIC_SCRATCH_BYTES);
+
+  int dev = 0;
+  SC_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) SC_FAIL(SC_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    // In host code the array name is only a handle; the kernels need its device address.
+    void* ptr = nullptr;
+    SC_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  char* base = static_cast<char*>(g_static_scratch_ptr[dev]);
+  float** pool_dev = reinterpret_cast<float**>(base + align_up(sizeof(TableDesc), 256));
+  float* partial = reinterpret_cast<float*>(base + image);
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+
+  struct { TableDesc td; } host;
+  memset(&host, 0, sizeof host);
+  host.td.v = v;
+  host.td.grad = activation_grad;
+  host.td.opt.kind = kind;
+  host.td.opt.h0 = optimizer->hyper[0]; host.td.opt.h1 = optimizer->hyper[1];
+  host.td.opt.h2 = optimizer->hyper[2]; host.td.opt.h3 = optimizer->hyper[3];
+  host.td.opt.lo = optimizer->clip_min; host.td.opt.hi = optimizer->clip_max;
+  host.td.table = pool_dev;
+  host.td.slot0 = kind >= 1 ? pool_dev + 1 : nullptr;
+  host.td.slot1 = kind >= 2 ? pool_dev + 2 : nullptr;
+  host.td.total_rows = (uint32_t)v.rows_per_shard;
+  float* pool_host[3] = {shard_tables[0], kind >= 1 ? shard_slot0[0] : nullptr, kind >= 2 ? shard_slot1[0] : nullptr};
+  // Both sources are pageable stack memory: the copies are staged before the calls return.
+  SC_CUDA_OK(cudaMemcpyAsync(base, &host.td, sizeof(TableDesc), cudaMemcpyHostToDevice, cs));
+  SC_CUDA_OK(cudaMemcpyAsync(pool_dev, pool_host, sizeof pool_host, cudaMemcpyHostToDevice, cs));
+  const TableDesc* tabs = reinterpret_cast<const TableDesc*>(base);
+#define SC_STATIC_CALL(W, K) launch_bwd<W, K>(tabs, 1, chunks, partial, kind, cs)
+  SC_SHAPE_SWITCH(w, k, SC_STATIC_CALL);
+#undef SC_STATIC_CALL
+}

@@ -127,6 +127,9 @@ def lib() -> ctypes.CDLL:
     l.sc_sparse_dense_matmul_grad_grouped_workspace_bytes.argtypes = [ctypes.POINTER(GradItem), c_i32]
     l.sc_sparse_dense_matmul_grad_grouped.restype = c_i32
     l.sc_sparse_dense_matmul_grad_grouped.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
+    l.sc_sparse_dense_matmul_grad_static.restype = c_i32
+    l.sc_sparse_dense_matmul_grad_static.argtypes = [ctypes.POINTER(Csr), c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
+                                                     ctypes.POINTER(c_vp), ctypes.POINTER(Optimizer), c_vp]
     _lib = l
   return _lib
 
