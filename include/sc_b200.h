@@ -178,6 +178,15 @@ typedef struct {
   float* activations;               /* device, [device_batch_size, dim] */
 } sc_fwd_item_t;
 
+/* Buffers of one source device as seen from the owner of a shard (peer-mapped device pointers). */
+typedef struct {
+  const int32_t* row_pointers;
+  const int32_t* embedding_ids;
+  const int32_t* sample_ids;
+  const float* gains;
+  const float* activation_grad;
+} sc_pull_source_t;
+
 typedef struct {
   sc_csr_t csr;
   const float* activation_grad;     /* device, [device_batch_size, dim] */
@@ -185,14 +194,41 @@ typedef struct {
   float* const* shard_slot0;
   float* const* shard_slot1;
   sc_optimizer_t optimizer;
+  /* Row-sharded tables with one process per GPU ("pull" mode; replaces the cross-chip exchange
+   * that the TPU custom call performs implicitly, sc/docs/parameters.rst:20-24).  When `sources`
+   * is not NULL this device owns shard `shard` (its table is shard_tables[0]) and reduces the
+   * entries that each of the `num_sources` == num_scs devices holds for that shard, reading the
+   * peers' CSR buffers and gradient rows over NVLink; `csr` then describes the geometry of ONE
+   * source buffer and `partition_capacity` bounds the entries per (source, shard), normally
+   * max_ids_per_partition rounded up to 8.  The caller makes every source buffer complete and
+   * visible (a stream-ordered barrier across the devices) before this call. */
+  const sc_pull_source_t* sources;  /* host array [num_sources] or NULL */
+  int32_t num_sources;
+  int32_t shard;
+  int32_t partition_capacity;
 } sc_grad_item_t;
 
 size_t sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(const sc_fwd_item_t* items, int32_t count);
 int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items, int32_t count, void* workspace_device,
                                            size_t workspace_bytes, sc_stream_t stream);
+/* Pull mode only: copies this device's CSR buffers and activation gradients into its own exchange
+ * buffers (sources[shard]); follow with a barrier across the devices, then the grouped update. */
+int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, sc_stream_t stream);
 size_t sc_sparse_dense_matmul_grad_grouped_workspace_bytes(const sc_grad_item_t* items, int32_t count);
 int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* items, int32_t count, void* workspace_device,
                                             size_t workspace_bytes, sc_stream_t stream);
+
+/* ---------------------------------------------------------------- peer-visible memory
+ * Row-sharded tables with one process per GPU: every process allocates its table shards and its
+ * exchange buffers with sc_peer_alloc, exports a 64-byte CUDA IPC handle and imports the handles
+ * of its peers (exchanged by the host program); the kernels then read remote memory with plain
+ * loads over NVLink.  Replaces the implicit cross-chip addressing of the TPU custom calls
+ * (sc/docs/parameters.rst:20-24).  These are the only entry points that allocate. */
+int32_t sc_peer_alloc(size_t bytes, void** device_pointer_out);
+int32_t sc_peer_free(void* device_pointer);
+int32_t sc_ipc_export(void* device_pointer, char* handle64_out);
+int32_t sc_ipc_import(const char* handle64, void** peer_pointer_out);
+int32_t sc_ipc_release(void* peer_pointer);
 
 /* Fused backward + optimizer update for callers that cannot allocate device memory at all:
  * an embedding server whose device memory was carved up completely at start-up, a plugin invoked

@@ -94,3 +94,42 @@ extern "C" int32_t sc_compute_row_pointers_size_per_device(int32_t global_device
   const int32_t num_scs = global_device_count * num_sc_per_device;
   return (num_scs > sc::kAlign ? num_scs : sc::kAlign) * num_sc_per_device;
 }
+
+// ---- peer-visible device memory (row-sharded tables, one process per GPU) ---------------------
+// The reference needs no such calls: the TPU runtime addresses other chips' shards inside the
+// custom call (sc/docs/parameters.rst:20-24).  Here every process allocates its shards and
+// exchange buffers with sc_peer_alloc, exports a CUDA IPC handle and imports its peers' handles;
+// the lookup / update kernels then read remote rows with ordinary loads over NVLink.
+
+extern "C" int32_t sc_peer_alloc(size_t bytes, void** out) {
+  if (!out || bytes == 0) SC_FAIL(SC_INVALID_ARGUMENT, "sc_peer_alloc: bad arguments");
+  SC_CUDA_OK(cudaMalloc(out, bytes));
+  return SC_OK;
+}
+
+extern "C" int32_t sc_peer_free(void* ptr) {
+  SC_CUDA_OK(cudaFree(ptr));
+  return SC_OK;
+}
+
+extern "C" int32_t sc_ipc_export(void* ptr, char* handle64) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!ptr || !handle64) SC_FAIL(SC_INVALID_ARGUMENT, "sc_ipc_export: bad arguments");
+  cudaIpcMemHandle_t h;
+  SC_CUDA_OK(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle64, &h, sizeof h);
+  return SC_OK;
+}
+
+extern "C" int32_t sc_ipc_import(const char* handle64, void** out) {
+  if (!out || !handle64) SC_FAIL(SC_INVALID_ARGUMENT, "sc_ipc_import: bad arguments");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof h);
+  SC_CUDA_OK(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+  return SC_OK;
+}
+
+extern "C" int32_t sc_ipc_release(void* ptr) {
+  SC_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return SC_OK;
+}

@@ -59,6 +59,15 @@ struct OptParams {
   float lo, hi;  // NaN = unbounded
 };
 
+// Buffers of one source device as seen from the owner of a shard (peer-mapped pointers).
+struct PullSrc {
+  const int32_t* row_pointers;
+  const int32_t* ids;
+  const int32_t* sids;
+  const float* gains;
+  const float* grad;
+};
+
 // One stacked table of a grouped launch.
 struct TableDesc {
   CsrView v;
@@ -73,10 +82,24 @@ struct TableDesc {
   uint32_t chunk_base;  // first global 32-entry chunk (backward)
   // Backward entry list: direct (entry e = slot e, row = ids[e]) for one SparseCore and one
   // shard; otherwise entries sorted by global row (rows[e]) with their source slot (slots[e]).
+  // All indirect tables of a call share ONE sorted list: rows[] holds row_base + global row,
+  // slots[] holds ent_base + entry index, and range[0..1] delimits this table's part of the list.
   const uint32_t* rows;
   const uint32_t* slots;
+  const uint32_t* range;
+  uint32_t row_base;
+  uint32_t ent_base;
+  uint32_t n_ent;       // size of this table's entry index space (0 for direct tables)
   int32_t indirect;
   uint32_t total_rows;  // P * rows_per_shard
+  // Pull mode (row-sharded tables, one process per GPU): this device owns shard `pull_shard` and
+  // reduces the entries that EVERY device holds for that shard, reading them and the gradient
+  // rows from the peers' memory.  Entry index = source * pull_cap + position inside the partition.
+  const PullSrc* pull;
+  int32_t* pull_begin;  // first slot of the shard's partition in every source buffer
+  int32_t pull_cap;
+  int32_t pull_shard;
+  int32_t num_sources;
 };
 
 // Index of the table whose [base, next base) range contains x.
@@ -277,15 +300,12 @@ __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g,
 }
 
 __device__ __forceinline__ int entry_count(const TableDesc& td) {
-  return td.indirect ? td.v.coo : min(td.v.row_pointers[0], td.v.coo_per_sc);
+  return td.indirect ? (int)(td.range[1] - td.range[0]) : min(td.v.row_pointers[0], td.v.coo_per_sc);
 }
 
 __device__ __forceinline__ uint32_t entry_row(const TableDesc& td, int e, int n) {
   if (e < 0 || e >= n) return kNoRow;
-  if (td.indirect) {
-    const uint32_t r = td.rows[e];
-    return r < td.total_rows ? r : kNoRow;
-  }
+  if (td.indirect) return td.rows[td.range[0] + (uint32_t)e] - td.row_base;  // every listed entry is valid
   const int id = td.v.ids[e];
   return (id >= 0 && (int64_t)id < td.v.rows_per_shard) ? (uint32_t)id : kNoRow;
 }
@@ -452,14 +472,23 @@ __global__ void __launch_bounds__(kBlock, K == 1 ? 3 : 1) bwd_main_kernel(const 
   if (lane == 0) prev_row = entry_row(td, e0 - 1, n);
   const uint32_t next_row = entry_row(td, e0 + 32, n);  // row after the chunk
   const bool valid = my_row != kNoRow;
-  int my_act = -1;
+  const float* my_src = nullptr;  // gradient row of this lane's entry
   float my_gain = 0.f;
   if (valid) {
-    const int q = td.indirect ? (int)(td.slots[e]) : e;
-    const int s = q / v.coo_per_sc;
-    const int sid = v.sids[q];
-    my_gain = v.gains[q];
-    my_act = (sid >= 0 && sid < v.bsc) ? s * v.bsc + sid : -1;
+    const int q = td.indirect ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
+    if (td.pull != nullptr) {
+      const int s = q / td.pull_cap;
+      const PullSrc& src = td.pull[s];
+      const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
+      const int sid = src.sids[slot];
+      my_gain = src.gains[slot];
+      if (sid >= 0 && sid < v.bdev) my_src = src.grad + (int64_t)sid * dim;
+    } else {
+      const int s = q / v.coo_per_sc;
+      const int sid = v.sids[q];
+      my_gain = v.gains[q];
+      if (sid >= 0 && sid < v.bsc) my_src = grad + (int64_t)(s * v.bsc + sid) * dim;
+    }
   }
   const uint32_t heads = __ballot_sync(0xffffffffu, valid && my_row != prev_row);
   const uint32_t valids = __ballot_sync(0xffffffffu, valid);
@@ -481,12 +510,12 @@ __global__ void __launch_bounds__(kBlock, K == 1 ? 3 : 1) bwd_main_kernel(const 
     return r;
   };
   auto load_grad = [&](int j, VT (&g)[K]) {
-    const int act = __shfl_sync(0xffffffffu, my_act, j);
-    const VT* src = reinterpret_cast<const VT*>(grad + (int64_t)max(act, 0) * dim);
+    const VT* src = reinterpret_cast<const VT*>(
+        (const float*)__shfl_sync(0xffffffffu, (unsigned long long)my_src, j));
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int c = lane + k * 32;
-      g[k] = (act >= 0 && c < vec_per_row) ? __ldg(src + c) : Vec<W>::zero();
+      g[k] = (src != nullptr && c < vec_per_row) ? src[c] : Vec<W>::zero();
     }
   };
 
@@ -612,18 +641,54 @@ __global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __re
   }
 }
 
-// key = global row (shard * rows_per_shard + id) of the slot, total_rows for empty slots.
-__global__ void bwd_keys_kernel(CsrView v, uint32_t total_rows, uint32_t* __restrict__ keys) {
-  const int q = blockIdx.x * blockDim.x + threadIdx.x;
-  if (q >= v.coo) return;
-  const int s = q / v.coo_per_sc, local = q - s * v.coo_per_sc;
-  uint32_t key = total_rows;
-  const int g = slot_shard(v, s, local);
-  if (g >= 0) {
-    const int id = v.ids[q];
-    if (id >= 0 && (int64_t)id < v.rows_per_shard) key = (uint32_t)((int64_t)g * v.rows_per_shard + id);
+// Entry index space of all indirect tables -> sort key (row_base + global row; `invalid` for
+// indices that hold no entry).  Virtual-device tables: entry index = slot of the concatenated
+// buffer.  Pull tables: entry index = source * cap + position inside the source's partition.
+__global__ void bwd_keys_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_ent, uint32_t invalid,
+                                uint32_t* __restrict__ keys) {
+  const uint32_t ge = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ge >= total_ent) return;
+  // Tables with an empty entry space share their base with the next one: pick the last match.
+  const int t = find_table(count, ge, [&](int i) { return tabs[i].ent_base; });
+  const TableDesc& td = tabs[t];
+  const CsrView& v = td.v;
+  const int q = (int)(ge - td.ent_base);
+  uint32_t key = invalid;
+  if (td.pull != nullptr) {
+    const int s = q / td.pull_cap, j = q - s * td.pull_cap;
+    const PullSrc& src = td.pull[s];
+    const int g = td.pull_shard;
+    const int begin = g == 0 ? 0 : ((src.row_pointers[g - 1] + kAlign - 1) & ~(kAlign - 1));
+    const int end = src.row_pointers[g];
+    if (j == 0) td.pull_begin[s] = begin;
+    if (begin + j < end) {
+      const int id = src.ids[begin + j];
+      if (id >= 0 && (int64_t)id < v.rows_per_shard) key = td.row_base + (uint32_t)id;
+    }
+  } else {
+    const int s = q / v.coo_per_sc, local = q - s * v.coo_per_sc;
+    const int g = slot_shard(v, s, local);
+    if (g >= 0) {
+      const int id = v.ids[q];
+      if (id >= 0 && (int64_t)id < v.rows_per_shard) key = td.row_base + (uint32_t)((int64_t)g * v.rows_per_shard + id);
+    }
   }
-  keys[q] = key;
+  keys[ge] = key;
+}
+
+// ranges[t] = first sorted position whose key is >= row_base of table t; ranges[count] = number of
+// valid entries.  Table t's entries are [ranges[t], ranges[t + 1]).
+__global__ void bwd_ranges_kernel(const TableDesc* __restrict__ tabs, int count, const uint32_t* __restrict__ keys, uint32_t n,
+                                  uint32_t invalid, uint32_t* __restrict__ ranges) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t > count) return;
+  const uint32_t target = t < count ? tabs[t].row_base : invalid;
+  uint32_t lo = 0, hi = n;
+  while (lo < hi) {
+    const uint32_t mid = (lo + hi) >> 1;
+    if (keys[mid] < target) lo = mid + 1; else hi = mid;
+  }
+  ranges[t] = lo;
 }
 
 // ------------------------------------------------------------------------ host side
@@ -778,9 +843,9 @@ bool carve_fwd(Workspace& ws, const FwdPlan& p, int count, FwdScratch* s) {
 struct BwdPlan {
   std::vector<CsrView> views;
   std::vector<int> indirect;
-  uint64_t total_chunks = 0;
-  size_t max_indirect_slots = 0;
-  int total_shards = 0;
+  std::vector<uint32_t> n_ent;  // entry index space per table (0 for direct tables)
+  uint64_t total_chunks = 0, total_ent = 0, total_rows = 0;
+  int total_shards = 0, total_sources = 0;
   int w = 0, k = 0, max_dim = 0, max_slots = 0;
 };
 
@@ -788,45 +853,72 @@ int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
   if (!items || count <= 0) SC_FAIL(SC_INVALID_ARGUMENT, "empty backward group");
   p->views.resize(count);
   p->indirect.resize(count);
+  p->n_ent.resize(count);
   for (int i = 0; i < count; ++i) {
     int st = make_view(&items[i].csr, &p->views[i]);
     if (st != SC_OK) return st;
-    const CsrView& v = p->views[i];
+    CsrView& v = p->views[i];
     int w, k;
     if (!pick_shape(v.dim, &w, &k)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
     if (i == 0) { p->w = w; p->k = k; }
     if (w != p->w || k != p->k) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the row length class (dim %d vs %d)",
                                        v.dim, p->views[0].dim);
-    p->indirect[i] = !(v.S == 1 && v.P == 1);
-    if (p->indirect[i]) p->max_indirect_slots += (size_t)v.coo;
-    p->total_chunks += (uint64_t)ceil_div(v.coo, 32);
+    const bool pull = items[i].sources != nullptr;
+    if (pull) {
+      if (v.S != 1) SC_FAIL(SC_INVALID_ARGUMENT, "pull mode needs one SparseCore per device");
+      if (items[i].num_sources != v.P) SC_FAIL(SC_INVALID_ARGUMENT, "pull mode needs one source per shard (%d vs %d)", items[i].num_sources, v.P);
+      if (items[i].shard < 0 || items[i].shard >= v.P) SC_FAIL(SC_INVALID_ARGUMENT, "shard %d out of range", items[i].shard);
+      if (items[i].partition_capacity <= 0 || items[i].partition_capacity > v.coo)
+        SC_FAIL(SC_INVALID_ARGUMENT, "partition_capacity must be in (0, coo_buffer_size]");
+      for (int sidx = 0; sidx < v.P; ++sidx) {
+        const sc_pull_source_t& src = items[i].sources[sidx];
+        if (!src.row_pointers || !src.embedding_ids || !src.sample_ids || !src.gains || !src.activation_grad)
+          SC_FAIL(SC_INVALID_ARGUMENT, "source %d has a null buffer", sidx);
+      }
+      p->n_ent[i] = (uint32_t)((int64_t)v.P * items[i].partition_capacity);
+      p->total_sources += v.P;
+    } else {
+      p->n_ent[i] = (v.S == 1 && v.P == 1) ? 0u : (uint32_t)v.coo;
+    }
+    p->indirect[i] = p->n_ent[i] != 0;
+    if (p->indirect[i]) {
+      p->total_ent += p->n_ent[i];
+      p->total_rows += pull ? (uint64_t)v.rows_per_shard : (uint64_t)v.P * (uint64_t)v.rows_per_shard;
+    }
+    const int64_t space = p->indirect[i] ? (int64_t)p->n_ent[i] : (int64_t)v.coo;
+    p->total_chunks += (uint64_t)ceil_div(space, 32);
     p->total_shards += v.P;
     p->max_dim = v.dim > p->max_dim ? v.dim : p->max_dim;
     const sc_optimizer_t& o = items[i].optimizer;
     if (o.optimizer < 0 || o.optimizer > 2) SC_FAIL(SC_INVALID_ARGUMENT, "unknown optimizer");
     if (i == 0) p->max_slots = o.optimizer;
     if (o.optimizer != p->max_slots) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the optimizer kind");
-    if (!items[i].activation_grad || !items[i].shard_tables) SC_FAIL(SC_INVALID_ARGUMENT, "null gradient or table pointer");
+    if ((!pull && !items[i].activation_grad) || !items[i].shard_tables) SC_FAIL(SC_INVALID_ARGUMENT, "null gradient or table pointer");
     if (o.optimizer >= 1 && !items[i].shard_slot0) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 0");
     if (o.optimizer >= 2 && !items[i].shard_slot1) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
     if (!isnan(o.clip_min) && !isnan(o.clip_max) && o.clip_min > o.clip_max)
       SC_FAIL(SC_INVALID_ARGUMENT, "min_value must be less than or equal to max_value");
   }
-  if (p->total_chunks >= 0x7fffffffull) SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
+  if (p->total_chunks >= 0x7fffffffull || p->total_ent >= 0xffffffffull || p->total_rows >= 0xfffffffeull)
+    SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
   return SC_OK;
 }
 
 struct BwdScratch {
   char* image;
-  std::vector<SortBuffers> sorts;  // one per indirect table
+  SortBuffers sort;  // one sorted list for all indirect tables
+  uint32_t* ranges;
+  PullSrc* pull;
+  int32_t* pull_begin;
   float* partial;
 };
 
 bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
   s->image = ws.take<char>(image_bytes(count, p.total_shards));
-  s->sorts.resize(count);
-  for (int i = 0; i < count; ++i)
-    if (p.indirect[i]) carve_sort(ws, (size_t)p.views[i].coo, &s->sorts[i]);
+  if (p.total_ent > 0) carve_sort(ws, (size_t)p.total_ent, &s->sort);
+  s->ranges = ws.take<uint32_t>((size_t)count + 1);
+  s->pull = ws.take<PullSrc>((size_t)p.total_sources + 1);
+  s->pull_begin = ws.take<int32_t>((size_t)p.total_sources + 1);
   s->partial = ws.take<float>((size_t)2 * (size_t)p.total_chunks * (size_t)p.max_dim);
   return ws.ok();
 }
@@ -910,9 +1002,12 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
 
   GroupImage img;
   std::vector<int> pool_index;
-  uint32_t chunk_base = 0;
+  std::vector<PullSrc> pull_host;
+  uint32_t chunk_base = 0, ent_base = 0, row_base = 0;
+  int source_base = 0;
   for (int i = 0; i < count; ++i) {
     const sc_optimizer_t& o = items[i].optimizer;
+    const bool pull = items[i].sources != nullptr;
     TableDesc td;
     memset(&td, 0, sizeof td);
     td.v = p.views[i];
@@ -921,37 +1016,99 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     td.opt.h0 = o.hyper[0]; td.opt.h1 = o.hyper[1]; td.opt.h2 = o.hyper[2]; td.opt.h3 = o.hyper[3];
     td.opt.lo = o.clip_min; td.opt.hi = o.clip_max;
     td.chunk_base = chunk_base;
-    chunk_base += (uint32_t)ceil_div(td.v.coo, 32);
     td.indirect = p.indirect[i];
-    td.total_rows = (uint32_t)((int64_t)td.v.P * td.v.rows_per_shard);
+    td.n_ent = p.n_ent[i];
+    td.ent_base = ent_base;
+    td.row_base = row_base;
+    td.range = s.ranges + i;
+    const int table_shards = pull ? 1 : td.v.P;  // a pull table updates only the shard it owns
+    td.total_rows = (uint32_t)((int64_t)table_shards * td.v.rows_per_shard);
+    chunk_base += (uint32_t)ceil_div(td.indirect ? (int64_t)td.n_ent : (int64_t)td.v.coo, 32);
+    if (td.indirect) {
+      ent_base += td.n_ent;
+      row_base += td.total_rows;
+    }
+    if (pull) {
+      td.pull = s.pull + source_base;
+      td.pull_begin = s.pull_begin + source_base;
+      td.pull_cap = items[i].partition_capacity;
+      td.pull_shard = items[i].shard;
+      td.num_sources = items[i].num_sources;
+      for (int sidx = 0; sidx < items[i].num_sources; ++sidx) {
+        const sc_pull_source_t& src = items[i].sources[sidx];
+        pull_host.push_back(PullSrc{src.row_pointers, src.embedding_ids, src.sample_ids, src.gains, src.activation_grad});
+      }
+      source_base += items[i].num_sources;
+      td.v.P = 1;  // row -> pointer arithmetic of the update sees the owned shard only
+    }
     float* const* srcs[3] = {items[i].shard_tables, o.optimizer >= 1 ? items[i].shard_slot0 : nullptr,
                              o.optimizer >= 2 ? items[i].shard_slot1 : nullptr};
     for (int a = 0; a < 3; ++a) {
       if (!srcs[a]) { pool_index.push_back(-1); continue; }
       pool_index.push_back((int)img.pool.size());
-      for (int g = 0; g < td.v.P; ++g) {
+      for (int g = 0; g < table_shards; ++g) {
         if (!srcs[a][g]) SC_FAIL(SC_INVALID_ARGUMENT, "shard %d misses a table or slot pointer", g);
         img.pool.push_back(srcs[a][g]);
       }
     }
-    if (td.indirect) {
-      // Entries of several SparseCores / shards: order them by global row first (stable, so
-      // contributions to one row keep the order SparseCore, sample).
-      bwd_keys_kernel<<<(unsigned)ceil_div(td.v.coo, kBlock), kBlock, 0, cs>>>(td.v, td.total_rows, s.sorts[i].keys[0]);
-      SC_LAUNCH_OK("bwd_keys_kernel");
-      int res = 0;
-      SC_CUDA_OK(radix_sort_pairs(s.sorts[i], (size_t)td.v.coo, bit_width_u32(td.total_rows), true, &res, cs));
-      td.rows = s.sorts[i].keys[res];
-      td.slots = s.sorts[i].vals[res];
-    }
     img.tabs.push_back(td);
   }
+  const uint32_t total_ent = (uint32_t)p.total_ent, invalid = (uint32_t)p.total_rows;
+  if (total_ent > 0) {
+    // The sorted list lives in one of the two sort buffers; which one is known before launching.
+    const int passes = (bit_width_u32(invalid) + kRadixBits - 1) / kRadixBits;
+    const int res_index = passes & 1;
+    for (auto& td : img.tabs) {
+      td.rows = s.sort.keys[res_index];
+      td.slots = s.sort.vals[res_index];
+    }
+  }
+  if (!pull_host.empty())
+    SC_CUDA_OK(cudaMemcpyAsync(s.pull, pull_host.data(), pull_host.size() * sizeof(PullSrc), cudaMemcpyHostToDevice, cs));
   SC_CUDA_OK(upload(img, s.image, pool_index, cs));
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
+  if (total_ent > 0) {
+    // Entries of several SparseCores / shards / devices: order them by global row first (stable,
+    // so contributions to one row keep the order source, sample), one sort for all tables.
+    bwd_keys_kernel<<<(unsigned)ceil_div(total_ent, kBlock), kBlock, 0, cs>>>(tabs, count, total_ent, invalid, s.sort.keys[0]);
+    SC_LAUNCH_OK("bwd_keys_kernel");
+    int res = 0;
+    SC_CUDA_OK(radix_sort_pairs(s.sort, (size_t)total_ent, bit_width_u32(invalid), true, &res, cs));
+    const int passes = (bit_width_u32(invalid) + kRadixBits - 1) / kRadixBits;
+    if (res != (passes & 1)) SC_FAIL(SC_CUDA_ERROR, "internal: unexpected sort buffer parity");
+    bwd_ranges_kernel<<<(unsigned)ceil_div(count + 1, kBlock), kBlock, 0, cs>>>(tabs, count, s.sort.keys[res], total_ent, invalid,
+                                                                              s.ranges);
+    SC_LAUNCH_OK("bwd_ranges_kernel");
+  }
   const uint32_t total_chunks = (uint32_t)p.total_chunks;
 #define SC_BWD_CALL(W, K) launch_bwd<W, K>(tabs, count, total_chunks, s.partial, p.max_slots, cs)
   SC_SHAPE_SWITCH(p.w, p.k, SC_BWD_CALL);
 #undef SC_BWD_CALL
+}
+
+// Copies this device's CSR buffers and activation gradients of every pull-mode item into the
+// device's own peer-visible exchange buffers (sources[shard]).  The caller separates this call
+// from the update with a barrier across the devices.
+extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, sc_stream_t stream) {
+  if (!items || count <= 0) SC_FAIL(SC_INVALID_ARGUMENT, "empty backward group");
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < count; ++i) {
+    const sc_grad_item_t& it = items[i];
+    if (!it.sources) continue;
+    CsrView v;
+    int st = make_view(&it.csr, &v);
+    if (st != SC_OK) return st;
+    if (it.shard < 0 || it.shard >= it.num_sources || !it.activation_grad) SC_FAIL(SC_INVALID_ARGUMENT, "bad pull item");
+    const sc_pull_source_t& own = it.sources[it.shard];
+    const size_t rp_bytes = sizeof(int32_t) * (size_t)v.R * v.S, coo_bytes = sizeof(int32_t) * (size_t)v.coo;
+    SC_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(own.row_pointers), v.row_pointers, rp_bytes, cudaMemcpyDeviceToDevice, cs));
+    SC_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(own.embedding_ids), v.ids, coo_bytes, cudaMemcpyDeviceToDevice, cs));
+    SC_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(own.sample_ids), v.sids, coo_bytes, cudaMemcpyDeviceToDevice, cs));
+    SC_CUDA_OK(cudaMemcpyAsync(const_cast<float*>(own.gains), v.gains, coo_bytes, cudaMemcpyDeviceToDevice, cs));
+    SC_CUDA_OK(cudaMemcpyAsync(const_cast<float*>(own.activation_grad), it.activation_grad,
+                               sizeof(float) * (size_t)v.bdev * v.dim, cudaMemcpyDeviceToDevice, cs));
+  }
+  return SC_OK;
 }
 
 // ---- single-table entry points: groups of one ---------------------------------------------

@@ -61,9 +61,16 @@ class FwdItem(ctypes.Structure):
   _fields_ = [("csr", Csr), ("shard_tables", ctypes.POINTER(c_vp)), ("activations", c_vp)]
 
 
+class PullSource(ctypes.Structure):
+  _fields_ = [("row_pointers", c_vp), ("embedding_ids", c_vp), ("sample_ids", c_vp), ("gains", c_vp),
+              ("activation_grad", c_vp)]
+
+
 class GradItem(ctypes.Structure):
   _fields_ = [("csr", Csr), ("activation_grad", c_vp), ("shard_tables", ctypes.POINTER(c_vp)),
-              ("shard_slot0", ctypes.POINTER(c_vp)), ("shard_slot1", ctypes.POINTER(c_vp)), ("optimizer", Optimizer)]
+              ("shard_slot0", ctypes.POINTER(c_vp)), ("shard_slot1", ctypes.POINTER(c_vp)), ("optimizer", Optimizer),
+              ("sources", ctypes.POINTER(PullSource)), ("num_sources", c_i32), ("shard", c_i32),
+              ("partition_capacity", c_i32)]
 
 
 _lib = None
@@ -127,6 +134,18 @@ def lib() -> ctypes.CDLL:
     l.sc_sparse_dense_matmul_grad_grouped_workspace_bytes.argtypes = [ctypes.POINTER(GradItem), c_i32]
     l.sc_sparse_dense_matmul_grad_grouped.restype = c_i32
     l.sc_sparse_dense_matmul_grad_grouped.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
+    l.sc_sparse_dense_matmul_grad_stage.restype = c_i32
+    l.sc_sparse_dense_matmul_grad_stage.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp]
+    l.sc_peer_alloc.restype = c_i32
+    l.sc_peer_alloc.argtypes = [c_sz, ctypes.POINTER(c_vp)]
+    l.sc_peer_free.restype = c_i32
+    l.sc_peer_free.argtypes = [c_vp]
+    l.sc_ipc_export.restype = c_i32
+    l.sc_ipc_export.argtypes = [c_vp, ctypes.c_char_p]
+    l.sc_ipc_import.restype = c_i32
+    l.sc_ipc_import.argtypes = [ctypes.c_char_p, ctypes.POINTER(c_vp)]
+    l.sc_ipc_release.restype = c_i32
+    l.sc_ipc_release.argtypes = [c_vp]
     l.sc_sparse_dense_matmul_grad_static.restype = c_i32
     l.sc_sparse_dense_matmul_grad_static.argtypes = [ctypes.POINTER(Csr), c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp),
                                                      ctypes.POINTER(c_vp), ctypes.POINTER(Optimizer), c_vp]

@@ -79,6 +79,13 @@ class Geometry:
     rows = table.shape[0]
     if rows % (l * s):
       raise ValueError(f"embedding_table has {rows} rows, not divisible by {l * s} local shards")
+    if l != c:
+      from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
+
+      if l != 1 or not distributed.is_active() or distributed.world_size() != c:
+        raise ValueError(
+            f"operands carry {l} of {c} devices: either pass the buffers of all devices (virtual devices on one "
+            "GPU) or run one process per GPU with sparsecore.distributed.init()")
     self.s, self.c, self.l, self.p = s, c, l, p
     self.s_eff = l * s
     self.coo = coo
@@ -167,6 +174,7 @@ class ForwardGroupCall:
       self.groups.append((items, idxs, nbytes))
     self.shapes = [tuple(r.act.shape) for r in requests]
     self.first = True
+    self.sharded = any(r.geo.l != r.geo.c for r in requests)
     self.keep = [(r.ptrs,) for r in requests]
     # Requests keep tensors alive; a replayable call must not, so drop them after the first run.
 
@@ -183,6 +191,11 @@ class ForwardGroupCall:
         for j, i in enumerate(idxs):
           items[j].activations = outs[i].data_ptr()
     stream = _native.current_stream_ptr()
+    if self.sharded:
+      # Every peer must have finished updating its shard before remote rows are read.
+      from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
+
+      distributed.stream_barrier()
     for items, idxs, nbytes in self.groups:
       ws = _native.workspace(nbytes, "lookup")
       _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
@@ -205,7 +218,8 @@ class GradRequest:
   """One stacked table of a grouped backward call."""
 
   def __init__(self, kind, rp, ids, sids, gains, table, slots, act_grad, hyper, *, min_value=None, max_value=None,
-               num_sc_per_device=None, global_device_count=None, local_device_count=None):
+               num_sc_per_device=None, global_device_count=None, local_device_count=None, partition_capacity=None,
+               exchange_key=None):
     torch = _native.require_cuda()
     self.rp, self.ids, self.sids, self.gains = _device_operands(rp, ids, sids, gains)
     self.table = _native.as_device(table, torch.float32, "embedding_table")
@@ -224,8 +238,24 @@ class GradRequest:
     opt.clip_min = float("nan") if min_value is None else float(min_value)
     opt.clip_max = float("nan") if max_value is None else float(max_value)
     self.opt = opt
-    self.t_ptrs = self.geo.shard_pointers(self.table)
-    self.s_ptrs = [self.geo.shard_pointers(s) for s in self.slots]
+    self.pull = None
+    if self.geo.l != self.geo.c:
+      # Row-sharded table, one process per GPU: this process owns one shard and pulls the entries
+      # every process holds for it (see sparsecore.distributed).
+      from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
+
+      if self.geo.s != 1:
+        raise ValueError("row-sharded tables with one process per GPU need num_sc_per_device == 1")
+      self.pull = distributed.exchange_buffers(exchange_key or "default", self.rp.numel(), self.geo.coo,
+                                               self.geo.batch, self.geo.dim)
+      cap = self.geo.coo if not partition_capacity else min(self.geo.coo, (int(partition_capacity) + 7) // 8 * 8)
+      self.partition_capacity = cap
+      self.shard = distributed.rank()
+      self.t_ptrs = (_native.c_vp * 1)(self.table.data_ptr())
+      self.s_ptrs = [(_native.c_vp * 1)(s.data_ptr()) for s in self.slots]
+    else:
+      self.t_ptrs = self.geo.shard_pointers(self.table)
+      self.s_ptrs = [self.geo.shard_pointers(s) for s in self.slots]
 
   def results(self):
     return (self.table, *self.slots)
@@ -253,17 +283,30 @@ class GradGroupCall:
         if len(r.s_ptrs) > 1:
           items[j].shard_slot1 = r.s_ptrs[1]
         items[j].optimizer = r.opt
+        if r.pull is not None:
+          items[j].sources = r.pull["sources"]
+          items[j].num_sources = r.geo.c
+          items[j].shard = r.shard
+          items[j].partition_capacity = r.partition_capacity
       nbytes = lib.sc_sparse_dense_matmul_grad_grouped_workspace_bytes(items, len(idxs))
       if nbytes == 0:
         _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), None, 0, None))
       self.groups.append((items, idxs, nbytes))
-    self.keep = [(r.t_ptrs, r.s_ptrs) for r in requests]
+    self.keep = [(r.t_ptrs, r.s_ptrs, r.pull) for r in requests]
+    self.sharded = any(r.pull is not None for r in requests)
     self._results = [r.results() for r in requests]
     self.first = True
 
   def run(self):
     lib = _native.lib()
     stream = _native.current_stream_ptr()
+    if self.sharded:
+      from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
+
+      distributed.stream_barrier()  # peers are done reading the exchange buffers of the previous call
+      for items, idxs, _ in self.groups:
+        _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), stream))
+      distributed.stream_barrier()  # every peer's exchange buffers are complete
     for items, idxs, nbytes in self.groups:
       ws = _native.workspace(nbytes, "lookup")
       _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))

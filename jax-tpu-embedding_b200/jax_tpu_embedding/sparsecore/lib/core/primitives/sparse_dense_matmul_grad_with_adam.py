@@ -46,7 +46,8 @@ def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lh
       "adam", lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains, embedding_table,
       (momentum, velocity), activations_grad, hyper, min_value=min_value, max_value=max_value,
       num_sc_per_device=num_sc_per_device, global_device_count=global_device_count,
-      local_device_count=local_device_count)
+      local_device_count=local_device_count, partition_capacity=max_ids_per_partition,
+      exchange_key=computation_name)
 
 
 tpu_sparse_dense_matmul_grad_with_adam_primitive = _ops.Primitive(

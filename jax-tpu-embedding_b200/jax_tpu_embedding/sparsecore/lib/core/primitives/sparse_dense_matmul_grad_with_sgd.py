@@ -30,7 +30,8 @@ def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lh
       "sgd", lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains, embedding_table, (),
       activations_grad, (_ops.scalar_f32(learning_rate),), min_value=min_value, max_value=max_value,
       num_sc_per_device=num_sc_per_device, global_device_count=global_device_count,
-      local_device_count=local_device_count)
+      local_device_count=local_device_count, partition_capacity=max_ids_per_partition,
+      exchange_key=computation_name)
 
 
 tpu_sparse_dense_matmul_grad_with_sgd_primitive = _ops.Primitive(

@@ -678,6 +678,11 @@ def init_embedding_variables(rng, table_specs, global_sharding: DeviceLayout | i
   else:
     layout = global_sharding
   c, l = layout.global_device_count, layout.resolved_local()
+  if allocator is None and l != c:
+    from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
+
+    if distributed.is_active():
+      allocator = distributed.alloc  # shards must be visible to the other GPUs
   if device is None:
     device = "cuda" if torch.cuda.is_available() else "cpu"
   seed = int(rng.initial_seed()) if isinstance(rng, torch.Generator) else int(rng)
