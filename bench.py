@@ -1,6 +1,6 @@
 """Benchmark of the SparseCore hot path on B200: forward + fused Adagrad backward.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c5|c1] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5|c1] [--impl reference]
 
 Prints ONE JSON line.  `value` is samples/s of lookup + update with the preprocessed batch
 resident in HBM; `e2e` adds the host->device copy of the raw ids, GPU preprocessing and a
@@ -59,6 +59,9 @@ def workload(name, scale=1.0):
                 tables=[dict(vocab=int(1e7 * scale), dim=64,
                              feats=[dict(kind="ragged", poisson=20, lo=1, hi=64, dist="zipf", a=1.1)])
                         for _ in range(8)])
+  if name == "c4":  # per-GPU batch 16384: at 8 GPUs this is the 131072-sample, 1e8-row configuration
+    return dict(seed=404, batch=16384, combiner="mean", optimizer="adagrad", weights=False, stack=False,
+                tables=[dict(vocab=int(1e8 * scale), dim=128, feats=[dict(kind="ragged", lo=1, hi=32, dist="zipf", a=1.05)])])
   if name == "c5":
     return dict(seed=505, batch=32768, combiner="mean", optimizer="adam", weights=False, stack=True,
                 tables=[dict(vocab=int(1e5 * scale), dim=32, feats=[dict(kind="ragged", lo=1, hi=16, dist="uniform")])
@@ -66,7 +69,7 @@ def workload(name, scale=1.0):
   raise ValueError(name)
 
 
-def build_specs(wl, global_device_count=1, num_sc=1):
+def build_specs(wl, global_device_count=1, num_sc=1, global_batch=None):
   from jax_tpu_embedding.sparsecore.lib.nn import embedding, embedding_spec, initializers, table_stacking
 
   if wl["optimizer"] == "sgd":
@@ -81,9 +84,10 @@ def build_specs(wl, global_device_count=1, num_sc=1):
                                   initializer=initializers.normal(0.01), optimizer=opt, combiner=wl["combiner"],
                                   max_ids_per_partition=1 << 24, max_unique_ids_per_partition=1 << 24)
     for fi, f in enumerate(t["feats"]):
-      shape = [wl["batch"], f["valency"]] if f["kind"] == "dense" else [wl["batch"]]
+      gb = global_batch or wl["batch"]
+      shape = [gb, f["valency"]] if f["kind"] == "dense" else [gb]
       specs.append(embedding_spec.FeatureSpec(name=f"f{ti:03d}_{fi}", table_spec=ts, input_shape=shape,
-                                              output_shape=[wl["batch"], t["dim"]]))
+                                              output_shape=[gb, t["dim"]]))
   if wl["stack"]:
     big = lambda n, b: 1 << 24
     table_stacking.stack_tables(specs, [f"t{i:03d}" for i in range(len(wl["tables"]))], global_device_count, num_sc,
@@ -94,17 +98,17 @@ def build_specs(wl, global_device_count=1, num_sc=1):
   return specs
 
 
-def build_inputs(wl, specs):
-  """Raw host inputs: one leaf per feature (dense int32 [B, v] or RaggedInput), optional weights."""
+def build_inputs(wl, specs, rank=0):
+  """Raw host inputs of one rank: one leaf per feature (dense int32 [B, v] or RaggedInput), optional weights."""
   from jax_tpu_embedding.sparsecore.lib.nn import embedding
 
   feats, weights = [], []
   fi = 0
   for ti, t in enumerate(wl["tables"]):
     for f in t["feats"]:
-      rng = np.random.default_rng([wl["seed"], 2, fi])
-      lrng = np.random.default_rng([wl["seed"], 3, fi])
-      wrng = np.random.default_rng([wl["seed"], 4, fi])
+      rng = np.random.default_rng([wl["seed"], 2, fi, rank])
+      lrng = np.random.default_rng([wl["seed"], 3, fi, rank])
+      wrng = np.random.default_rng([wl["seed"], 4, fi, rank])
       b = wl["batch"]
       draw = (lambda n: zipf_ids(rng, t["vocab"], n, f["a"])) if f["dist"] == "zipf" else (
           lambda n: rng.integers(0, t["vocab"], size=n).astype(np.int32))
@@ -188,14 +192,18 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
-def table_stats(pre, specs, name):
+def table_stats(pre, specs, name, world=1):
   """nnz (entries after dedup) and unique rows of one stacked table, from the CSR on device."""
   import torch
 
-  rp = pre.lhs_row_pointers[name]
+  rp = pre.lhs_row_pointers[name].cpu().numpy()
   ids = pre.lhs_embedding_ids[name]
-  n = int(rp[0].item())
-  u = int(torch.unique_consecutive(ids[:n]).numel())
+  n = u = 0
+  for g in range(world):
+    begin = 0 if g == 0 else (int(rp[g - 1]) + 7) // 8 * 8
+    end = int(rp[g])
+    n += end - begin
+    u += int(torch.unique_consecutive(ids[begin:end]).numel())
   return n, u
 
 
@@ -336,28 +344,51 @@ def main():
   local_rank = int(os.environ.get("LOCAL_RANK", "0"))
   torch.cuda.set_device(local_rank)
   if world > 1:
-    torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    from jax_tpu_embedding.sparsecore import distributed
 
-  specs = build_specs(wl)
-  feats, weights = build_inputs(wl, specs)
+    torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    distributed.init()
+    config["sharding"] = (f"every stacked table row-sharded mod {world} over {world} GPUs (one process per GPU); forward "
+                          "gathers remote rows over NVLink, backward pulls entries and gradient rows from the peers")
+
+  # Weak scaling: every GPU brings its own batch of wl['batch'] samples; tables are shared.
+  specs = build_specs(wl, global_device_count=world, global_batch=wl["batch"] * world)
+  feats, weights = build_inputs(wl, specs, rank)
   stacked = embedding.get_stacked_table_specs(specs)
   table_specs = list({f.table_spec.name: f.table_spec for f in specs}.values())
-  variables = embedding.init_embedding_variables(1234 + rank, table_specs, 1, num_sparsecore_per_device=1)
+  layout = embedding.DeviceLayout(world, 1 if world > 1 else None, rank)
+  variables = embedding.init_embedding_variables(1234 + rank, table_specs, layout, num_sparsecore_per_device=1)
   table_bytes = sum(v.table.numel() * 4 * (1 + len(v.slot)) for v in variables.values())
 
   # FDO pass (the reference's own recipe): observe limits once, then size the buffers exactly.
-  pre, stats = embedding.preprocess_sparse_dense_matmul_input(feats, weights, specs, 1, 1, num_sc_per_device=1,
+  pre, stats = embedding.preprocess_sparse_dense_matmul_input(feats, weights, specs, 1, world, num_sc_per_device=1,
                                                               allow_id_dropping=True)
+  if world > 1:  # all ranks must agree on limits and buffer sizes
+    for d in (stats.max_ids_per_partition, stats.max_unique_ids_per_partition, stats.required_buffer_size_per_sc):
+      for k in sorted(d):
+        t = torch.from_numpy(np.ascontiguousarray(d[k])).cuda()
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        d[k] = t.cpu().numpy()
   embedding.update_preprocessing_parameters(specs, stats, 1)
-  pre, stats = embedding.preprocess_sparse_dense_matmul_input(feats, weights, specs, 1, 1, num_sc_per_device=1)
+  pre, stats = embedding.preprocess_sparse_dense_matmul_input(feats, weights, specs, 1, world, num_sc_per_device=1)
   stacked = embedding.get_stacked_table_specs(specs)
   gen = torch.Generator(device="cuda").manual_seed(5 + rank)
-  grads = [torch.randn(tuple(f.output_shape), generator=gen, device="cuda") * 1e-2 for f in specs]
+  grads = [torch.randn((wl["batch"], f.output_shape[-1]), generator=gen, device="cuda") * 1e-2 for f in specs]
+  if world > 1 and len(specs) == len(stacked):
+    # The dense part of a model writes its activation gradients straight into the peer-visible
+    # exchange buffers, which saves the staging copy inside the update.
+    for i, f in enumerate(specs):
+      st = f.table_spec.stacked_table_spec
+      key = f"{st.optimizer.short_name()}-{st.stack_name}"
+      buf = distributed.gradient_buffer(key, pre.lhs_row_pointers[st.stack_name].numel(),
+                                        pre.lhs_embedding_ids[st.stack_name].numel(), wl["batch"], st.stack_embedding_dim)
+      buf.copy_(grads[i])
+      grads[i] = buf
 
   def lookup_update():
-    acts = embedding.tpu_sparse_dense_matmul(pre, variables, specs, global_device_count=1, num_sc_per_device=1)
-    embedding.tpu_sparse_dense_matmul_grad(grads, pre, variables, specs, global_device_count=1, num_sc_per_device=1,
-                                           step=0)
+    acts = embedding.tpu_sparse_dense_matmul(pre, variables, specs, global_device_count=world, num_sc_per_device=1)
+    embedding.tpu_sparse_dense_matmul_grad(grads, pre, variables, specs, global_device_count=world,
+                                           num_sc_per_device=1, step=0)
     return acts
 
   def barrier():
@@ -395,18 +426,18 @@ def main():
   algo_bytes, bwd_ms = 0, 0.0
   per = {}
   for name, spec in stacked.items():
-    n, u = table_stats(pre, specs, name)
-    d, bdev = spec.stack_embedding_dim, spec.total_sample_count
+    n, u = table_stats(pre, specs, name, world)
+    d, bdev = spec.stack_embedding_dim, spec.total_sample_count // world
     slots = spec.optimizer.slot_variables_count()
     per[name] = (n, u)
     algo_bytes += bdev * 4 * d + n * 12 + 8 * 4 + u * 4 * d * (1 + slots) * 2
-  stacked_grads = embedding.stack_embedding_gradients(grads, specs, 1, 1)
+  stacked_grads = embedding.stack_embedding_gradients(grads, specs, 1, world)
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   torch.cuda.synchronize()
   reps = max(3, min(args.steps, 10))
   e0.record()
   for _ in range(reps):
-    embedding.tpu_sparse_dense_matmul_grad(stacked_grads, pre, variables, specs, global_device_count=1,
+    embedding.tpu_sparse_dense_matmul_grad(stacked_grads, pre, variables, specs, global_device_count=world,
                                            num_sc_per_device=1, step=0, perform_stacking=False)
   e1.record()
   torch.cuda.synchronize()
@@ -417,11 +448,11 @@ def main():
   # quantities as the algorithmic figure, so it is scaled to this launch.
   traffic_ratio = 1.03
   achieved = algo_bytes / (bwd_ms * 1e-3) / 1e9
-  fwd_bytes = sum(per[n][1] * 4 * s.stack_embedding_dim + per[n][0] * 12 + 32 + s.total_sample_count * 4 * s.stack_embedding_dim
-                  for n, s in stacked.items())
+  fwd_bytes = sum(per[n][1] * 4 * s.stack_embedding_dim + per[n][0] * 12 + 32
+                  + s.total_sample_count // world * 4 * s.stack_embedding_dim for n, s in stacked.items())
   e0.record()
   for _ in range(reps):
-    embedding.tpu_sparse_dense_matmul(pre, variables, specs, global_device_count=1, num_sc_per_device=1,
+    embedding.tpu_sparse_dense_matmul(pre, variables, specs, global_device_count=world, num_sc_per_device=1,
                                       perform_unstacking=False)
   e1.record()
   torch.cuda.synchronize()
@@ -455,11 +486,11 @@ def main():
           dev_feats.append(embedding.RaggedInput(p.values.cuda(non_blocking=True), p.row_splits,
                                                  None if p.weights is None else p.weights.cuda(non_blocking=True)))
       dev_w = None if pinned_w is None else [w.cuda(non_blocking=True) for w in pinned_w]
-      p2, _ = embedding.preprocess_sparse_dense_matmul_input(dev_feats, dev_w, specs, 1, 1, num_sc_per_device=1)
-      acts = embedding.tpu_sparse_dense_matmul(p2, variables, specs, global_device_count=1, num_sc_per_device=1)
+      p2, _ = embedding.preprocess_sparse_dense_matmul_input(dev_feats, dev_w, specs, 1, world, num_sc_per_device=1)
+      acts = embedding.tpu_sparse_dense_matmul(p2, variables, specs, global_device_count=world, num_sc_per_device=1)
       checksum = torch.stack([a.sum() for a in acts]).sum()
-      embedding.tpu_sparse_dense_matmul_grad(grads, p2, variables, specs, global_device_count=1, num_sc_per_device=1,
-                                             step=0)
+      embedding.tpu_sparse_dense_matmul_grad(grads, p2, variables, specs, global_device_count=world,
+                                             num_sc_per_device=1, step=0)
       return float(checksum.item())
 
     for _ in range(2):
@@ -498,6 +529,12 @@ def main():
                      "forward": {"algorithmic_bytes": int(fwd_bytes), "ms": fwd_ms,
                                  "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                                  "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak}},
+        "nvlink": None if world == 1 else {
+            "forward_bytes_per_gpu": int(nnz_in * (world - 1) / world * 4 * wl["tables"][0]["dim"]),
+            "backward_bytes_per_gpu": int(nnz_in * (world - 1) / world * (4 * wl["tables"][0]["dim"] + 12)),
+            "bound_ms": nnz_in * (world - 1) / world * (8 * wl["tables"][0]["dim"] + 12) / 770e9 * 1e3,
+            "note": "remote rows (forward) and remote gradient rows + entries (backward) at the measured 770 GB/s "
+                    "per direction; the step cannot be faster than max(HBM time, this)"},
         "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
         "gpu_launches": gpu_launches,
         "table_bytes": int(table_bytes),

@@ -212,8 +212,11 @@ size_t sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(const sc_fwd_item_t* i
 int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items, int32_t count, void* workspace_device,
                                            size_t workspace_bytes, sc_stream_t stream);
 /* Pull mode only: copies this device's CSR buffers and activation gradients into its own exchange
- * buffers (sources[shard]); follow with a barrier across the devices, then the grouped update. */
-int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, sc_stream_t stream);
+ * buffers (sources[shard]) with one kernel launch, skipping buffers that already live there; the
+ * workspace of the grouped update is large enough.  Follow with a barrier across the devices,
+ * then the grouped update. */
+int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, void* workspace_device,
+                                          size_t workspace_bytes, sc_stream_t stream);
 size_t sc_sparse_dense_matmul_grad_grouped_workspace_bytes(const sc_grad_item_t* items, int32_t count);
 int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* items, int32_t count, void* workspace_device,
                                             size_t workspace_bytes, sc_stream_t stream);

@@ -1086,12 +1086,39 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
 #undef SC_BWD_CALL
 }
 
+// One (source, destination, bytes) triple of the grouped staging copy; all multiples of 4 bytes.
+struct CopyJob {
+  const uint32_t* src;
+  uint32_t* dst;
+  uint64_t words;
+};
+
+// blockIdx.y = job; the blocks of a row stride over the job's words (16-byte vectors when aligned).
+__global__ void stage_copy_kernel(const CopyJob* __restrict__ jobs) {
+  const CopyJob j = jobs[blockIdx.y];
+  const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((((uintptr_t)j.src | (uintptr_t)j.dst) & 15) == 0) {
+    const uint64_t vecs = j.words / 4;
+    const uint4* s4 = reinterpret_cast<const uint4*>(j.src);
+    uint4* d4 = reinterpret_cast<uint4*>(j.dst);
+    for (uint64_t i = tid; i < vecs; i += stride) d4[i] = s4[i];
+    for (uint64_t i = vecs * 4 + tid; i < j.words; i += stride) j.dst[i] = j.src[i];
+  } else {
+    for (uint64_t i = tid; i < j.words; i += stride) j.dst[i] = j.src[i];
+  }
+}
+
 // Copies this device's CSR buffers and activation gradients of every pull-mode item into the
-// device's own peer-visible exchange buffers (sources[shard]).  The caller separates this call
-// from the update with a barrier across the devices.
-extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, sc_stream_t stream) {
+// device's own peer-visible exchange buffers (sources[shard]) with ONE kernel launch; buffers
+// that already live there (same address) are skipped.  `workspace` holds the job list
+// (sc_sparse_dense_matmul_grad_grouped_workspace_bytes covers it).  The caller separates this
+// call from the update with a barrier across the devices.
+extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, void* workspace,
+                                                     size_t workspace_bytes, sc_stream_t stream) {
   if (!items || count <= 0) SC_FAIL(SC_INVALID_ARGUMENT, "empty backward group");
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  std::vector<CopyJob> jobs;
   for (int i = 0; i < count; ++i) {
     const sc_grad_item_t& it = items[i];
     if (!it.sources) continue;
@@ -1100,14 +1127,23 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items
     if (st != SC_OK) return st;
     if (it.shard < 0 || it.shard >= it.num_sources || !it.activation_grad) SC_FAIL(SC_INVALID_ARGUMENT, "bad pull item");
     const sc_pull_source_t& own = it.sources[it.shard];
-    const size_t rp_bytes = sizeof(int32_t) * (size_t)v.R * v.S, coo_bytes = sizeof(int32_t) * (size_t)v.coo;
-    SC_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(own.row_pointers), v.row_pointers, rp_bytes, cudaMemcpyDeviceToDevice, cs));
-    SC_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(own.embedding_ids), v.ids, coo_bytes, cudaMemcpyDeviceToDevice, cs));
-    SC_CUDA_OK(cudaMemcpyAsync(const_cast<int32_t*>(own.sample_ids), v.sids, coo_bytes, cudaMemcpyDeviceToDevice, cs));
-    SC_CUDA_OK(cudaMemcpyAsync(const_cast<float*>(own.gains), v.gains, coo_bytes, cudaMemcpyDeviceToDevice, cs));
-    SC_CUDA_OK(cudaMemcpyAsync(const_cast<float*>(own.activation_grad), it.activation_grad,
-                               sizeof(float) * (size_t)v.bdev * v.dim, cudaMemcpyDeviceToDevice, cs));
+    const void* srcs[5] = {v.row_pointers, v.ids, v.sids, v.gains, it.activation_grad};
+    const void* dsts[5] = {own.row_pointers, own.embedding_ids, own.sample_ids, own.gains, own.activation_grad};
+    const uint64_t words[5] = {(uint64_t)v.R * v.S, (uint64_t)v.coo, (uint64_t)v.coo, (uint64_t)v.coo,
+                               (uint64_t)v.bdev * v.dim};
+    for (int a = 0; a < 5; ++a) {
+      if (srcs[a] == dsts[a] || words[a] == 0) continue;
+      jobs.push_back(CopyJob{static_cast<const uint32_t*>(srcs[a]),
+                             const_cast<uint32_t*>(static_cast<const uint32_t*>(dsts[a])), words[a]});
+    }
   }
+  if (jobs.empty()) return SC_OK;
+  const size_t bytes = jobs.size() * sizeof(CopyJob);
+  if (!workspace || workspace_bytes < bytes) SC_FAIL(SC_WORKSPACE_TOO_SMALL, "staging needs %zu workspace bytes", bytes);
+  SC_CUDA_OK(cudaMemcpyAsync(workspace, jobs.data(), bytes, cudaMemcpyHostToDevice, cs));
+  dim3 grid(32, (unsigned)jobs.size());
+  stage_copy_kernel<<<grid, kBlock, 0, cs>>>(static_cast<const CopyJob*>(workspace));
+  SC_LAUNCH_OK("stage_copy_kernel");
   return SC_OK;
 }
 

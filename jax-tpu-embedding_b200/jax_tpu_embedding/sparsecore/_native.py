@@ -135,7 +135,7 @@ def lib() -> ctypes.CDLL:
     l.sc_sparse_dense_matmul_grad_grouped.restype = c_i32
     l.sc_sparse_dense_matmul_grad_grouped.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
     l.sc_sparse_dense_matmul_grad_stage.restype = c_i32
-    l.sc_sparse_dense_matmul_grad_stage.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp]
+    l.sc_sparse_dense_matmul_grad_stage.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
     l.sc_peer_alloc.restype = c_i32
     l.sc_peer_alloc.argtypes = [c_sz, ctypes.POINTER(c_vp)]
     l.sc_peer_free.restype = c_i32

@@ -158,3 +158,14 @@ def exchange_buffers(key, rp_size: int, coo: int, batch: int, dim: int):
                                              ptrs["grad"][r])
     _ctx.exchange[full_key] = buf
   return buf
+
+
+def gradient_buffer(exchange_key: str, rp_size: int, coo: int, batch: int, dim: int):
+  """The peer-visible [batch, dim] buffer the backward reads activation gradients from.
+
+  A model that writes its activation gradients of a stacked table directly into this tensor and
+  passes it to `tpu_sparse_dense_matmul_grad(..., perform_stacking=False)` saves the staging copy
+  of the gradients (batch * dim * 8 bytes of HBM traffic per step).  `exchange_key` is
+  "<optimizer short name>-<stack name><label>", the name of the update computation.
+  """
+  return exchange_buffers(exchange_key, rp_size, coo, batch, dim)["grad"]

@@ -304,8 +304,9 @@ class GradGroupCall:
       from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
 
       distributed.stream_barrier()  # peers are done reading the exchange buffers of the previous call
-      for items, idxs, _ in self.groups:
-        _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), stream))
+      for items, idxs, nbytes in self.groups:
+        ws = _native.workspace(nbytes, "lookup")
+        _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
       distributed.stream_barrier()  # every peer's exchange buffers are complete
     for items, idxs, nbytes in self.groups:
       ws = _native.workspace(nbytes, "lookup")
