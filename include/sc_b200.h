@@ -244,7 +244,7 @@ int32_t sc_ipc_release(void* peer_pointer);
  * SC_STATIC_SCRATCH_BYTES array built into the library image, so the call performs no
  * cudaMalloc / cudaFree and takes no workspace.  Limits: one shard and one SparseCore per buffer
  * (num_scs == num_sc_per_device == 1) and
- *   512 + 2 * ceil(coo_buffer_size / 32) * dim * 4  <=  SC_STATIC_SCRATCH_BYTES,
+ *   512 + ceil(coo_buffer_size / 32) * (8 * dim + 1)  <=  SC_STATIC_SCRATCH_BYTES,
  * e.g. 65536 slots at dim 128; larger inputs are rejected with SC_WORKSPACE_TOO_SMALL.
  * The first call on each device resolves the address of the array (cudaGetSymbolAddress); make
  * that first call before any stream capture begins.  All calls on a device share the one array:

@@ -31,6 +31,9 @@
 #include <vector>
 
 #include "sc_common.cuh"
+#include <stdlib.h>
+#include <string.h>
+
 #include "sc_sort.cuh"
 
 namespace sc {
@@ -189,87 +192,98 @@ __device__ __forceinline__ void resolve_entry(const TableDesc& td, const uint32_
   *off = (g >= 0 && id >= 0 && (int64_t)id < v.rows_per_shard) ? (int64_t)id * v.dim : -1;
 }
 
+// What a forward warp knows about one of its 32 activation rows.
+struct RowMeta {
+  int64_t off;       // first entry: float offset of the table row inside its shard, -1 if none
+  uint32_t begin, end;
+  int32_t table;
+  int32_t shard;
+  float gain;
+  int32_t pad;
+};
+
 // One warp per 32 consecutive global activation rows.  Lane l first resolves the range and the
-// first entry of row r0 + l, so the dependent index loads of 32 rows overlap; the warp then
-// walks the rows, K vectors of width W per lane covering one table row.
-template <int W, int K>
+// first entry of row r0 + l, so the dependent index loads of 32 rows overlap.  The warp is then
+// split into 32 / G groups of G lanes; each group owns every (32 / G)-th row and covers one table
+// row with K vectors of width W per lane, so 32 / G table rows (K loads per lane each) are in
+// flight per warp.  Every activation row is written exactly once.
+template <int W, int K, int G>
 __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act,
                                                             const uint32_t* __restrict__ offsets,
                                                             const uint32_t* __restrict__ slots) {
   using VT = typename Vec<W>::T;
-  const int lane = threadIdx.x & 31;
-  const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5)) * 32u;
+  constexpr int NG = 32 / G;
+  __shared__ RowMeta s_meta[kWarpsPerBlock][32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + wib) * 32u;
   if (r0 >= total_act) return;
-  const uint32_t my_r = r0 + lane;
-  uint32_t my_begin = 0, my_end = 0;
-  int my_t = 0;
-  int64_t first_off = -1;
-  float first_gain = 0.f;
-  int first_shard = 0;
-  if (my_r < total_act) {
-    my_begin = offsets[my_r];
-    my_end = offsets[my_r + 1];
-    my_t = find_table(count, my_r, [&](int i) { return tabs[i].act_base; });
-    if (my_end > my_begin) resolve_entry(tabs[my_t], slots, my_begin, &first_off, &first_gain, &first_shard);
-  }
-  const int rows_here = (int)min(32u, total_act - r0);
-  // First entry of row j, broadcast from lane j; its table row is loaded one row ahead.
-  auto first_load = [&](int j, VT (&x)[K], float* gain, bool* any) {
-    const int tj = __shfl_sync(0xffffffffu, my_t, j);
-    const int64_t off0 = __shfl_sync(0xffffffffu, first_off, j);
-    const int shard0 = __shfl_sync(0xffffffffu, first_shard, j);
-    *gain = __shfl_sync(0xffffffffu, first_gain, j);
-    *any = off0 >= 0;
-    const TableDesc& tdj = tabs[tj];
-    const int vec_per_row = tdj.v.dim / W;
-    const VT* src = reinterpret_cast<const VT*>(tdj.table[max(shard0, 0)] + max(off0, (int64_t)0));
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int c = lane + k * 32;
-      x[k] = (off0 >= 0 && c < vec_per_row) ? __ldg(src + c) : Vec<W>::zero();
+  {
+    RowMeta m;
+    m.off = -1; m.begin = m.end = 0; m.table = 0; m.shard = 0; m.gain = 0.f; m.pad = 0;
+    const uint32_t my_r = r0 + lane;
+    if (my_r < total_act) {
+      m.begin = offsets[my_r];
+      m.end = offsets[my_r + 1];
+      m.table = find_table(count, my_r, [&](int i) { return tabs[i].act_base; });
+      if (m.end > m.begin) resolve_entry(tabs[m.table], slots, m.begin, &m.off, &m.gain, &m.shard);
     }
-  };
-  VT x_nxt[K];
-  float gain_nxt;
-  bool any_nxt;
-  first_load(0, x_nxt, &gain_nxt, &any_nxt);
-  for (int j = 0; j < rows_here; ++j) {
-    const uint32_t begin = __shfl_sync(0xffffffffu, my_begin, j);
-    const uint32_t end = __shfl_sync(0xffffffffu, my_end, j);
-    const int t = __shfl_sync(0xffffffffu, my_t, j);
-    const TableDesc& td = tabs[t];
-    const int vec_per_row = td.v.dim / W;
+    s_meta[wib][lane] = m;
+  }
+  __syncwarp();
+  const int group = lane / G, gl = lane % G;
+  const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (group * G));
+  const int rows_here = (int)min(32u, total_act - r0);
+  int cached_t = -1, dim = 0, vec_per_row = 0;
+  float* const* table_ptrs = nullptr;
+  float* act = nullptr;
+  uint32_t act_base = 0;
+  for (int j = group; j < rows_here; j += NG) {
+    const RowMeta m = s_meta[wib][j];
+    if (m.table != cached_t) {
+      const TableDesc& td = tabs[m.table];
+      dim = td.v.dim;
+      vec_per_row = dim / W;
+      table_ptrs = td.table;
+      act = td.act;
+      act_base = td.act_base;
+      cached_t = m.table;
+    }
     VT acc[K];
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      acc[k] = Vec<W>::zero();
-      if (any_nxt) Vec<W>::axpy(acc[k], gain_nxt, x_nxt[k]);
+    for (int k = 0; k < K; ++k) acc[k] = Vec<W>::zero();
+    if (m.off >= 0) {
+      const VT* src = reinterpret_cast<const VT*>(table_ptrs[m.shard] + m.off);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = gl + k * G;
+        if (c < vec_per_row) Vec<W>::axpy(acc[k], m.gain, __ldg(src + c));
+      }
     }
-    if (j + 1 < rows_here) first_load(j + 1, x_nxt, &gain_nxt, &any_nxt);
-    for (uint32_t base = begin + 1; base < end; base += 32) {
-      const uint32_t e = base + lane;
+    for (uint32_t base = m.begin + 1; base < m.end; base += G) {
+      // Each lane of the group resolves one entry; the group then walks them in order.
+      const uint32_t e = base + gl;
       int64_t e_off = -1;
       float e_gain = 0.f;
       int e_shard = 0;
-      if (e < end) resolve_entry(td, slots, e, &e_off, &e_gain, &e_shard);
-      const int cnt = (int)min(32u, end - base);
+      if (e < m.end) resolve_entry(tabs[m.table], slots, e, &e_off, &e_gain, &e_shard);
+      const int cnt = (int)min((uint32_t)G, m.end - base);
       for (int i = 0; i < cnt; ++i) {
-        const int64_t off = __shfl_sync(0xffffffffu, e_off, i);
-        const float gain = __shfl_sync(0xffffffffu, e_gain, i);
-        const int g = __shfl_sync(0xffffffffu, e_shard, i);
+        const int64_t off = __shfl_sync(gmask, e_off, i, G);
+        const float gain = __shfl_sync(gmask, e_gain, i, G);
+        const int g = __shfl_sync(gmask, e_shard, i, G);
         if (off < 0) continue;
-        const VT* src = reinterpret_cast<const VT*>(td.table[g] + off);
+        const VT* src = reinterpret_cast<const VT*>(table_ptrs[g] + off);
 #pragma unroll
         for (int k = 0; k < K; ++k) {
-          const int c = lane + k * 32;
+          const int c = gl + k * G;
           if (c < vec_per_row) Vec<W>::axpy(acc[k], gain, __ldg(src + c));
         }
       }
     }
-    VT* dst = reinterpret_cast<VT*>(td.act + (int64_t)(r0 + j - td.act_base) * td.v.dim);
+    VT* dst = reinterpret_cast<VT*>(act + (int64_t)(r0 + j - act_base) * dim);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
-      const int c = lane + k * 32;
+      const int c = gl + k * G;
       if (c < vec_per_row) dst[c] = acc[k];
     }
   }
@@ -399,72 +413,45 @@ __device__ __forceinline__ void store_row(const RowCtx& ctx, int64_t grow, int l
   }
 }
 
-// Variants specialised on the number of slot variables (0 sgd, 1 adagrad, 2 adam) so that the
-// unused slot rows occupy no registers.
-template <int W, int K, int NS>
-__device__ __forceinline__ void load_row_ns(const RowCtx& ctx, int64_t grow, int lane, typename Vec<W>::T (&w)[K],
-                                            typename Vec<W>::T (&x0)[NS >= 1 ? K : 1],
-                                            typename Vec<W>::T (&x1)[NS >= 2 ? K : 1]) {
-  using VT = typename Vec<W>::T;
-  float *pw, *pa, *pb;
-  row_pointers_of(ctx, grow, &pw, &pa, &pb);
-  const int vec_per_row = ctx.dim / W;
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const int c = lane + k * 32;
-    const bool in = c < vec_per_row;
-    w[k] = in ? reinterpret_cast<const VT*>(pw)[c] : Vec<W>::zero();
-    if (NS >= 1) x0[k] = in ? reinterpret_cast<const VT*>(pa)[c] : Vec<W>::zero();
-    if (NS >= 2) x1[k] = in ? reinterpret_cast<const VT*>(pb)[c] : Vec<W>::zero();
-  }
-}
+// Flags a chunk leaves for the fix-up kernel.
+constexpr uint8_t kChunkHeadContinues = 1;  // a run that starts in this chunk goes on in the next one
+constexpr uint8_t kChunkAllContinues = 2;   // the whole chunk continues an earlier run and does not end it
 
-template <int W, int K, int NS>
-__device__ __forceinline__ void store_row_ns(const RowCtx& ctx, int64_t grow, int lane, const typename Vec<W>::T (&gsum)[K],
-                                             typename Vec<W>::T (&w)[K], typename Vec<W>::T (&x0)[NS >= 1 ? K : 1],
-                                             typename Vec<W>::T (&x1)[NS >= 2 ? K : 1]) {
-  using VT = typename Vec<W>::T;
-  float *pw, *pa, *pb;
-  row_pointers_of(ctx, grow, &pw, &pa, &pb);
-  const int vec_per_row = ctx.dim / W;
-#pragma unroll
-  for (int k = 0; k < K; ++k) {
-    const int c = lane + k * 32;
-    if (c >= vec_per_row) continue;
-    float* wf = reinterpret_cast<float*>(&w[k]);
-    float* af = NS >= 1 ? reinterpret_cast<float*>(&x0[NS >= 1 ? k : 0]) : nullptr;
-    float* bf = NS >= 2 ? reinterpret_cast<float*>(&x1[NS >= 2 ? k : 0]) : nullptr;
-    const float* gf = reinterpret_cast<const float*>(&gsum[k]);
-    float dead0 = 0.f, dead1 = 0.f;
-#pragma unroll
-    for (int i = 0; i < W; ++i) wf[i] = apply_opt(ctx.o, wf[i], gf[i], NS >= 1 ? af[i] : dead0, NS >= 2 ? bf[i] : dead1);
-    reinterpret_cast<VT*>(pw)[c] = w[k];
-    if (NS >= 1) reinterpret_cast<VT*>(pa)[c] = x0[NS >= 1 ? k : 0];
-    if (NS >= 2) reinterpret_cast<VT*>(pb)[c] = x1[NS >= 2 ? k : 0];
-  }
-}
+// What a backward warp knows about one of its 32 entries.
+struct EntMeta {
+  const float* src;  // gradient row of the entry (nullptr: contributes nothing)
+  uint32_t row;      // kNoRow for lanes past the end of the list
+  float gain;
+};
 
 // Warp per 32 consecutive entries of one table.  partial[(2 * global_chunk + k) * dim ...]:
 // k = 0 holds the sum of a run that started in an earlier chunk, k = 1 of a run that continues
-// into the next chunk.  The loads of run i + 1 (first gradient row, table row, slot rows) are
-// issued before run i is finished, so a warp keeps two rows in flight.
-template <int W, int K, int NS>
-__global__ void __launch_bounds__(kBlock, K == 1 ? 3 : 1) bwd_main_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
-                                                          float* __restrict__ partial) {
+// into the next chunk.  After the lane-parallel metadata phase the warp splits into 32 / G groups
+// of G lanes; each group owns every (32 / G)-th run of the chunk, issues the loads of the run's
+// table row and slot rows (NS of them) before it sums the gradient rows, and finishes with a
+// single store per array.  NS is the number of slot variables (0 sgd, 1 adagrad, 2 adam).
+template <int W, int K, int G, int NS>
+__global__ void __launch_bounds__(kBlock) bwd_main_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
+                                                          float* __restrict__ partial, uint8_t* __restrict__ chunk_flags) {
   using VT = typename Vec<W>::T;
-  const int lane = threadIdx.x & 31;
-  const uint32_t gchunk = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  constexpr int NG = 32 / G;
+  __shared__ EntMeta s_ent[kWarpsPerBlock][32];
+  __shared__ uint8_t s_start[kWarpsPerBlock][33];  // lane at which the r-th run of the chunk starts
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t gchunk = blockIdx.x * kWarpsPerBlock + wib;
   if (gchunk >= total_chunks) return;
   const int t = find_table(count, gchunk, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
   const CsrView& v = td.v;
   const int n = entry_count(td);
   const int e0 = (int)(gchunk - td.chunk_base) * 32;
-  if (e0 >= n) return;
+  if (e0 >= n) {
+    if (lane == 0) chunk_flags[gchunk] = 0;
+    return;
+  }
   const RowCtx ctx = make_ctx(td);
   const int dim = ctx.dim;
   const int vec_per_row = dim / W;
-  const float* __restrict__ grad = td.grad;
 
   const int e = e0 + lane;
   const uint32_t my_row = entry_row(td, e, n);
@@ -472,7 +459,189 @@ __global__ void __launch_bounds__(kBlock, K == 1 ? 3 : 1) bwd_main_kernel(const 
   if (lane == 0) prev_row = entry_row(td, e0 - 1, n);
   const uint32_t next_row = entry_row(td, e0 + 32, n);  // row after the chunk
   const bool valid = my_row != kNoRow;
-  const float* my_src = nullptr;  // gradient row of this lane's entry
+  {
+    EntMeta m;
+    m.src = nullptr; m.row = my_row; m.gain = 0.f;
+    if (valid) {
+      const int q = td.indirect ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
+      if (td.pull != nullptr) {
+        const int s = q / td.pull_cap;
+        const PullSrc& src = td.pull[s];
+        const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
+        const int sid = src.sids[slot];
+        m.gain = src.gains[slot];
+        if (sid >= 0 && sid < v.bdev) m.src = src.grad + (int64_t)sid * dim;
+      } else {
+        const int s = q / v.coo_per_sc;
+        const int sid = v.sids[q];
+        m.gain = v.gains[q];
+        if (sid >= 0 && sid < v.bsc) m.src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
+      }
+    }
+    s_ent[wib][lane] = m;
+  }
+  const uint32_t heads = __ballot_sync(0xffffffffu, valid && my_row != prev_row);
+  const uint32_t valids = __ballot_sync(0xffffffffu, valid);
+  // Runs start at lane 0 (a continuation when lane 0 is valid but not a head) and at every head.
+  const uint32_t starts = heads | (valids & 1u);
+  const int nruns = __popc(starts);
+  if (lane == 31) {
+    // What the fix-up kernel needs to know about the run that reaches the end of the chunk.
+    uint8_t flag = 0;
+    if (valid && next_row == my_row) flag = ((heads >> (31 - __clz(starts))) & 1u) ? kChunkHeadContinues : kChunkAllContinues;
+    chunk_flags[gchunk] = flag;
+  }
+  if ((starts >> lane) & 1u) s_start[wib][__popc(starts & ((1u << lane) - 1u))] = (uint8_t)lane;
+  if (lane == 0) s_start[wib][nruns] = 32;
+  __syncwarp();
+
+  const int group = lane / G, gl = lane % G;
+  constexpr int K0 = NS >= 1 ? K : 1, K1 = NS >= 2 ? K : 1;  // unused slot arrays shrink to one dead element
+  for (int r = group; r < nruns; r += NG) {
+    const int a = s_start[wib][r], b = s_start[wib][r + 1];
+    const uint32_t row = s_ent[wib][a].row;
+    int last = a;
+    while (last + 1 < b && s_ent[wib][last + 1].row == row) ++last;  // stops at lanes past the list
+    const bool is_head = (heads >> a) & 1u;
+    const bool whole = is_head && !(last == 31 && next_row == row);
+    float *pw = nullptr, *pa = nullptr, *pb = nullptr;
+    VT w[K], x0[K0], x1[K1];
+    if (whole) {
+      row_pointers_of(ctx, (int64_t)row, &pw, &pa, &pb);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = gl + k * G;
+        const bool in = c < vec_per_row;
+        w[k] = in ? reinterpret_cast<const VT*>(pw)[c] : Vec<W>::zero();
+        if (NS >= 1) x0[NS >= 1 ? k : 0] = in ? reinterpret_cast<const VT*>(pa)[c] : Vec<W>::zero();
+        if (NS >= 2) x1[NS >= 2 ? k : 0] = in ? reinterpret_cast<const VT*>(pb)[c] : Vec<W>::zero();
+      }
+    }
+    VT acc[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) acc[k] = Vec<W>::zero();
+    for (int j = a; j <= last; ++j) {
+      const EntMeta m = s_ent[wib][j];
+      if (m.src == nullptr) continue;
+      const VT* src = reinterpret_cast<const VT*>(m.src);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = gl + k * G;
+        if (c < vec_per_row) Vec<W>::axpy(acc[k], m.gain, src[c]);
+      }
+    }
+    if (whole) {
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = gl + k * G;
+        if (c >= vec_per_row) continue;
+        float* wf = reinterpret_cast<float*>(&w[k]);
+        float* af = NS >= 1 ? reinterpret_cast<float*>(&x0[NS >= 1 ? k : 0]) : nullptr;
+        float* bf = NS >= 2 ? reinterpret_cast<float*>(&x1[NS >= 2 ? k : 0]) : nullptr;
+        const float* gf = reinterpret_cast<const float*>(&acc[k]);
+        float dead0 = 0.f, dead1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < W; ++i) wf[i] = apply_opt(ctx.o, wf[i], gf[i], NS >= 1 ? af[i] : dead0, NS >= 2 ? bf[i] : dead1);
+        reinterpret_cast<VT*>(pw)[c] = w[k];
+        if (NS >= 1) reinterpret_cast<VT*>(pa)[c] = x0[NS >= 1 ? k : 0];
+        if (NS >= 2) reinterpret_cast<VT*>(pb)[c] = x1[NS >= 2 ? k : 0];
+      }
+    } else {
+      VT* dst = reinterpret_cast<VT*>(partial + ((int64_t)2 * gchunk + (is_head ? 1 : 0)) * dim);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = gl + k * G;
+        if (c < vec_per_row) dst[c] = acc[k];
+      }
+    }
+  }
+}
+
+// ---- cp.async pipeline variant of the update kernel
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(__cvta_generic_to_global(src)) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kPipeBlock = 128;
+constexpr int kPipeWarps = kPipeBlock / 32;
+constexpr int kPipeAhead = 2;  // batches in flight while one is consumed
+// Rows copied per batch for K float4 vectors per lane (about 2 KiB), and rows in a warp's ring.
+__host__ __device__ constexpr int pipe_batch_rows(int K) { return K == 1 ? 4 : K == 2 ? 2 : 1; }
+// While batch b is consumed, batches b + 1 .. b + kPipeAhead are in flight and an entry that
+// ends in batch b may still need up to 1 + NS rows of earlier batches.
+__host__ __device__ constexpr int pipe_ring_rows(int K, int NS) { return (kPipeAhead + 1) * pipe_batch_rows(K) + 1 + NS; }
+
+__device__ __forceinline__ float fast_axpy(float a, float g, float x) { return __fmaf_rn(g, x, a); }
+
+// Optimizer step of the pipelined kernel: fused multiply-adds and the hardware reciprocal square
+// root (2 ulp) instead of IEEE sqrt + divide; within 1e-6 relative of apply_opt.
+__device__ __forceinline__ float apply_opt_fast(const OptParams& o, float w, float g, float& s0, float& s1) {
+  float nw;
+  if (o.kind == 0) {
+    nw = __fmaf_rn(-o.h0, g, w);
+  } else if (o.kind == 1) {
+    s0 = __fmaf_rn(g, g, s0);
+    nw = __fmaf_rn(-(o.h0 * g), rsqrtf(s0), w);
+  } else {
+    s0 = __fmaf_rn(1.0f - o.h1, g - s0, s0);
+    s1 = __fmaf_rn(1.0f - o.h2, g * g - s1, s1);
+    nw = w - __fdividef(o.h0 * s0, sqrtf(s1) + o.h3);
+  }
+  return clip(nw, o.lo, o.hi);
+}
+
+// Same contract as bwd_main_kernel, for rows of `dim` floats with dim % 4 == 0 and 16-byte aligned
+// tables, slot variables and gradients.  A warp owns 32 consecutive entries.  Lane j describes
+// entry j: its gradient row and, when a run that this warp owns entirely ends at j, the table
+// row and the NS slot rows to update.  The addresses of all those rows are laid out, in entry
+// order, in a per-warp list in shared memory.  The warp then streams the list through a ring of
+// row slots with cp.async (16 bytes per lane, nothing held in registers while in flight): B rows
+// per commit group, kPipeAhead groups in flight, and consumes every entry as soon as its last
+// row has landed -- K float4 per lane from shared memory.  The pipeline is therefore as deep for
+// a chunk of 32 single-entry rows as for one long run, and the in-flight bytes per warp do not
+// depend on the optimizer.
+template <int K, int NS>
+__global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
+                                                             float* __restrict__ partial, uint8_t* __restrict__ chunk_flags,
+                                                             int ring_floats) {
+  constexpr int B = pipe_batch_rows(K);
+  constexpr int R = pipe_ring_rows(K, NS);
+  constexpr int kMaxRows = 32 * (2 + NS);
+  extern __shared__ __align__(128) unsigned char pipe_smem[];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t gchunk = blockIdx.x * kPipeWarps + wib;
+  if (gchunk >= total_chunks) return;
+  const int t = find_table(count, gchunk, [&](int i) { return tabs[i].chunk_base; });
+  const TableDesc& td = tabs[t];
+  const CsrView& v = td.v;
+  const int n = entry_count(td);
+  const int e0 = (int)(gchunk - td.chunk_base) * 32;
+  if (e0 >= n) {
+    if (lane == 0) chunk_flags[gchunk] = 0;
+    return;
+  }
+  const RowCtx ctx = make_ctx(td);
+  const int dim = ctx.dim;
+  const int vec_per_row = dim >> 2;
+  // Shared memory: [rings of all warps | row lists of all warps | gains of all warps].
+  const float* ring = reinterpret_cast<const float*>(pipe_smem) + (size_t)wib * ring_floats;
+  const float** rowlist = reinterpret_cast<const float**>(pipe_smem + (size_t)kPipeWarps * ring_floats * 4) + wib * kMaxRows;
+  float* gains = reinterpret_cast<float*>(pipe_smem + (size_t)kPipeWarps * (ring_floats * 4 + kMaxRows * 8)) + wib * 32;
+  const uint32_t ring_base = smem_addr(ring);
+  const uint32_t rowbytes = (uint32_t)dim * 4u;
+
+  const int e = e0 + lane;
+  const uint32_t my_row = entry_row(td, e, n);
+  uint32_t prev_row = __shfl_up_sync(0xffffffffu, my_row, 1);
+  if (lane == 0) prev_row = entry_row(td, e0 - 1, n);
+  const uint32_t next_row = entry_row(td, e0 + 32, n);  // row after the chunk
+  const bool valid = my_row != kNoRow;
+  const float* my_src = nullptr;
   float my_gain = 0.f;
   if (valid) {
     const int q = td.indirect ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
@@ -487,107 +656,170 @@ __global__ void __launch_bounds__(kBlock, K == 1 ? 3 : 1) bwd_main_kernel(const 
       const int s = q / v.coo_per_sc;
       const int sid = v.sids[q];
       my_gain = v.gains[q];
-      if (sid >= 0 && sid < v.bsc) my_src = grad + (int64_t)(s * v.bsc + sid) * dim;
+      if (sid >= 0 && sid < v.bsc) my_src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
     }
   }
+  const uint32_t lt = (1u << lane) - 1u;
   const uint32_t heads = __ballot_sync(0xffffffffu, valid && my_row != prev_row);
   const uint32_t valids = __ballot_sync(0xffffffffu, valid);
-  // Runs start at lane 0 (a continuation when lane 0 is valid but not a head) and at every head.
-  uint32_t starts = heads | (valids & 1u);
-  if (starts == 0) return;
+  if (valids == 0) {
+    if (lane == 0) chunk_flags[gchunk] = 0;
+    return;
+  }
+  const uint32_t starts = heads | (valids & 1u);
+  // The run of lane j starts at the highest start bit at or below j.
+  const int run_start = 31 - __clz(starts & (lt | (1u << lane)));
+  const bool head_run = valid && ((heads >> run_start) & 1u);
+  const bool is_end = valid && (lane == 31 || (((starts | ~valids) >> (lane + 1)) & 1u));
+  const bool goes_on = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
+  const bool w_end = is_end && head_run && !goes_on;                // apply the optimizer here
+  const bool has_src = valid && my_src != nullptr;
+  const uint32_t srcmask = __ballot_sync(0xffffffffu, has_src);
+  const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
+  const uint32_t endmask = __ballot_sync(0xffffffffu, is_end);
+  const uint32_t headrunmask = __ballot_sync(0xffffffffu, head_run);
+  const int jmax = 32 - __clz(valids);
+  if (lane == 31)
+    chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
+  {
+    int o = __popc(srcmask & lt) + (1 + NS) * __popc(wendmask & lt);
+    if (has_src) rowlist[o++] = my_src;
+    if (w_end) {
+      float *pw, *pa, *pb;
+      row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
+      rowlist[o++] = pw;
+      if (NS >= 1) rowlist[o++] = pa;
+      if (NS >= 2) rowlist[o++] = pb;
+    }
+    gains[lane] = my_gain;
+  }
+  const int total = __popc(srcmask) + (1 + NS) * __popc(wendmask);  // rows to stream
+  __syncwarp();
 
-  // Describes the run that starts at lane `a`: its row, last lane, and whether this warp owns
-  // the whole row (then the optimizer is applied here, otherwise a partial sum is stored).
-  struct Run { int a, last; uint32_t row; bool is_head, whole; };
-  auto describe = [&](int a) {
-    Run r;
-    r.a = a;
-    r.row = __shfl_sync(0xffffffffu, my_row, a);
-    const uint32_t same = __ballot_sync(0xffffffffu, my_row == r.row) & (0xffffffffu << a);
-    r.last = 31 - __clz(same);
-    r.is_head = (heads >> a) & 1u;
-    r.whole = r.is_head && !(r.last == 31 && next_row == r.row);
-    return r;
-  };
-  auto load_grad = [&](int j, VT (&g)[K]) {
-    const VT* src = reinterpret_cast<const VT*>(
-        (const float*)__shfl_sync(0xffffffffu, (unsigned long long)my_src, j));
+  // Copies rows [b * B, b * B + B) of the list into their ring slots; always one commit group.
+  auto issue_batch = [&](int b) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const int c = lane + k * 32;
-      g[k] = (src != nullptr && c < vec_per_row) ? src[c] : Vec<W>::zero();
+    for (int i = 0; i < B; ++i) {
+      const int r = b * B + i;
+      if (r < total) {
+        const float* src = rowlist[r];
+        const uint32_t dst = ring_base + (uint32_t)(r % R) * rowbytes;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          const int c = lane + k * 32;
+          if (c < vec_per_row) cp_async16(dst + (uint32_t)c * 16u, src + c * 4);
+        }
+      }
     }
+    cp_async_commit();
   };
 
-  constexpr int K0 = NS >= 1 ? K : 1, K1 = NS >= 2 ? K : 1;  // unused slot arrays shrink to one dead element
-  VT g_nxt[K], w_nxt[K], x0_nxt[K0], x1_nxt[K1];
-  Run nxt = describe(__ffs(starts) - 1);
-  starts &= starts - 1;
-  load_grad(nxt.a, g_nxt);
-  if (nxt.whole) load_row_ns<W, K, NS>(ctx, (int64_t)nxt.row, lane, w_nxt, x0_nxt, x1_nxt);
-  bool more = true;
-  while (more) {
-    const Run cur = nxt;
-    VT g_cur[K], w_cur[K], x0_cur[K0], x1_cur[K1];
+  float4 acc[K];
+  // Consumes entry j, whose rows start at list position `off`.
+  auto consume = [&](int j, int off) {
+    const uint32_t bit = 1u << j;
+    if (starts & bit) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) { g_cur[k] = g_nxt[k]; w_cur[k] = w_nxt[k]; }
-#pragma unroll
-    for (int k = 0; k < K0; ++k) x0_cur[k] = x0_nxt[k];
-#pragma unroll
-    for (int k = 0; k < K1; ++k) x1_cur[k] = x1_nxt[k];
-    more = starts != 0;
-    if (more) {
-      nxt = describe(__ffs(starts) - 1);
-      starts &= starts - 1;
-      load_grad(nxt.a, g_nxt);
-      if (nxt.whole) load_row_ns<W, K, NS>(ctx, (int64_t)nxt.row, lane, w_nxt, x0_nxt, x1_nxt);
+      for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    VT acc[K];
-    const float gain_a = __shfl_sync(0xffffffffu, my_gain, cur.a);
+    if (srcmask & bit) {
+      const float gain = gains[j];
+      const float4* g = reinterpret_cast<const float4*>(ring + (size_t)(off % R) * dim);
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      acc[k] = Vec<W>::zero();
-      Vec<W>::axpy(acc[k], gain_a, g_cur[k]);
+      for (int k = 0; k < K; ++k) {
+        const int c = lane + k * 32;
+        if (c < vec_per_row) {
+          const float4 x = g[c];
+          acc[k].x = fast_axpy(acc[k].x, gain, x.x); acc[k].y = fast_axpy(acc[k].y, gain, x.y);
+          acc[k].z = fast_axpy(acc[k].z, gain, x.z); acc[k].w = fast_axpy(acc[k].w, gain, x.w);
+        }
+      }
+      ++off;
     }
-    for (int j = cur.a + 1; j <= cur.last; ++j) {
-      VT g[K];
-      load_grad(j, g);
-      const float gain = __shfl_sync(0xffffffffu, my_gain, j);
+    if (!(endmask & bit)) return;
+    if (wendmask & bit) {
+      float* pw = const_cast<float*>(rowlist[off]);
+      float* pa = NS >= 1 ? const_cast<float*>(rowlist[off + (NS >= 1 ? 1 : 0)]) : nullptr;
+      float* pb = NS >= 2 ? const_cast<float*>(rowlist[off + (NS >= 2 ? 2 : 0)]) : nullptr;
+      const float4* sw = reinterpret_cast<const float4*>(ring + (size_t)(off % R) * dim);
+      const float4* sa = reinterpret_cast<const float4*>(ring + (size_t)((off + 1) % R) * dim);
+      const float4* sb = reinterpret_cast<const float4*>(ring + (size_t)((off + 2) % R) * dim);
 #pragma unroll
-      for (int k = 0; k < K; ++k) Vec<W>::axpy(acc[k], gain, g[k]);
-    }
-    if (cur.whole) {
-      store_row_ns<W, K, NS>(ctx, (int64_t)cur.row, lane, acc, w_cur, x0_cur, x1_cur);
+      for (int k = 0; k < K; ++k) {
+        const int c = lane + k * 32;
+        if (c >= vec_per_row) continue;
+        float4 w = sw[c];
+        float4 x0 = NS >= 1 ? sa[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 x1 = NS >= 2 ? sb[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float* wf = reinterpret_cast<float*>(&w);
+        float* af = reinterpret_cast<float*>(&x0);
+        float* bf = reinterpret_cast<float*>(&x1);
+        const float* gf = reinterpret_cast<const float*>(&acc[k]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast(ctx.o, wf[i], gf[i], af[i], bf[i]);
+        reinterpret_cast<float4*>(pw)[c] = w;
+        if (NS >= 1) reinterpret_cast<float4*>(pa)[c] = x0;
+        if (NS >= 2) reinterpret_cast<float4*>(pb)[c] = x1;
+      }
     } else {
-      VT* dst = reinterpret_cast<VT*>(partial + ((int64_t)2 * gchunk + (cur.is_head ? 1 : 0)) * dim);
+      float4* dst = reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((headrunmask & bit) ? 1 : 0)) * dim);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int c = lane + k * 32;
         if (c < vec_per_row) dst[c] = acc[k];
       }
     }
+  };
+  // Consumes, in order, every entry whose rows lie below list position `landed`.
+  int j = 0;
+  auto consume_upto = [&](int landed) {
+    while (j < jmax) {
+      const uint32_t bit = 1u << j;
+      if (valids & bit) {
+        const uint32_t below = bit - 1u;
+        const int off = __popc(srcmask & below) + (1 + NS) * __popc(wendmask & below);
+        const int cnt = (int)((srcmask >> j) & 1u) + (1 + NS) * (int)((wendmask >> j) & 1u);
+        if (off + cnt > landed) break;
+        consume(j, off);
+      }
+      ++j;
+    }
+  };
+
+  const int batches = (total + B - 1) / B;
+#pragma unroll
+  for (int b = 0; b < kPipeAhead; ++b) issue_batch(b);
+  for (int b = 0; b < batches; ++b) {
+    // The slots that batch b + kPipeAhead overwrites held rows of entries that were consumed in
+    // earlier iterations (see pipe_ring_rows).
+    issue_batch(b + kPipeAhead);
+    cp_async_wait<kPipeAhead>();  // this lane's copies of batch b have landed
+    __syncwarp();                 // ... and every other lane's
+    consume_upto(min(total, (b + 1) * B));
+    __syncwarp();                 // all lanes are done with the slots that the next batch recycles
   }
+  cp_async_wait<0>();
+  consume_upto(total);  // entries without rows at the end of the chunk
 }
 
-// Warp per chunk: if a run starts in this chunk and continues past it, add its partial
-// sums in chunk order and apply the optimizer once.
+// Warp per chunk that is flagged kChunkHeadContinues: adds the partial sums of the run that
+// starts in this chunk and goes on through the following ones, in chunk order, and applies the
+// optimizer once.
 template <int W, int K>
 __global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
-                                                           const float* __restrict__ partial) {
+                                                           const float* __restrict__ partial,
+                                                           const uint8_t* __restrict__ chunk_flags) {
   using VT = typename Vec<W>::T;
   const int lane = threadIdx.x & 31;
   const uint32_t gchunk = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (gchunk >= total_chunks) return;
+  if (!(chunk_flags[gchunk] & kChunkHeadContinues)) return;
   const int t = find_table(count, gchunk, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
   const int n = entry_count(td);
-  const int chunk = (int)(gchunk - td.chunk_base);
-  const int e0 = chunk * 32;
-  if (e0 + 32 >= n) return;  // nothing after this chunk
+  const int e0 = (int)(gchunk - td.chunk_base) * 32;
   const uint32_t row = entry_row(td, e0 + 31, n);
-  if (row == kNoRow || entry_row(td, e0 + 32, n) != row) return;  // last run ends here
-  // The run must start inside this chunk: either it does not cover lane 0, or lane 0 is its head.
-  if (entry_row(td, e0, n) == row && entry_row(td, e0 - 1, n) == row) return;
+  if (row == kNoRow) return;
   const int dim = td.v.dim;
   const int vec_per_row = dim / W;
   VT acc[K];
@@ -599,21 +831,23 @@ __global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __re
       acc[k] = c < vec_per_row ? src[c] : Vec<W>::zero();
     }
   }
-  // Entries are ordered by row, so the run ends at the first entry with a larger row.
-  int lo = e0 + 32, hi = n;
-  while (lo < hi) {
-    const int mid = (lo + hi) >> 1;
-    if (entry_row(td, mid, n) <= row) lo = mid + 1; else hi = mid;
+  // The run covers chunk gchunk + 1 and every following chunk flagged kChunkAllContinues, plus
+  // the one after those (where it ends).  The last chunk of a table never carries a flag.
+  uint32_t c_end = gchunk + 1;  // last chunk with a partial sum of this run
+  for (;;) {
+    const uint32_t c = c_end + lane;
+    const bool on = c < total_chunks && (chunk_flags[c] & kChunkAllContinues);
+    const uint32_t stop = __ballot_sync(0xffffffffu, !on);
+    if (stop != 0) { c_end += (uint32_t)__ffs(stop) - 1u; break; }
+    c_end += 32;
   }
-  const int c_end = (lo + 31) / 32;  // chunks chunk+1 .. c_end-1 hold continuation partials
-  const float* pbase = partial + (int64_t)2 * td.chunk_base * dim;
-  int c2 = chunk + 1;
+  uint32_t c2 = gchunk + 1;
   constexpr int U = K == 1 ? 16 : K == 2 ? 8 : K == 4 ? 4 : 2;  // partial rows in flight
-  for (; c2 + U <= c_end; c2 += U) {
+  for (; c2 + U <= c_end + 1; c2 += U) {
     VT p[U][K];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const VT* src = reinterpret_cast<const VT*>(pbase + (int64_t)2 * (c2 + u) * dim);
+      const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * (c2 + u) * dim);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int c = lane + k * 32;
@@ -625,8 +859,8 @@ __global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __re
 #pragma unroll
       for (int k = 0; k < K; ++k) Vec<W>::add(acc[k], p[u][k]);
   }
-  for (; c2 < c_end; ++c2) {
-    const VT* src = reinterpret_cast<const VT*>(pbase + (int64_t)2 * c2 * dim);
+  for (; c2 <= c_end; ++c2) {
+    const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * c2 * dim);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int c = lane + k * 32;
@@ -714,15 +948,6 @@ int make_view(const sc_csr_t* c, CsrView* v) {
   return SC_OK;
 }
 
-// Picks the vector width and per-lane vector count for a row length.
-bool pick_shape(int dim, int* w, int* k) {
-  *w = (dim % 4 == 0) ? 4 : 1;
-  const int vecs = dim / *w;
-  const int need = (vecs + 31) / 32;
-  *k = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : 0;
-  return *k != 0;
-}
-
 struct SortScratch {
   SortBuffers b;
 };
@@ -764,37 +989,121 @@ size_t image_bytes(int count, int total_shards) {
   return align_up((size_t)count * sizeof(TableDesc), 256) + (size_t)3 * total_shards * sizeof(float*);
 }
 
-template <int W, int K>
+// Lanes per row (G) and vectors per lane (K) for a row of `dim` floats; W is the vector width.
+bool pick_group_shape(int dim, int* w, int* k, int* g) {
+  *w = (dim % 4 == 0) ? 4 : 1;
+  const int vecs = dim / *w;
+  if (vecs <= 4) { *g = 4; *k = 1; }
+  else if (vecs <= 8) { *g = 8; *k = 1; }
+  else if (vecs <= 16) { *g = 8; *k = 2; }
+  else if (vecs <= 32) { *g = 8; *k = 4; }
+  else if (vecs <= 64) { *g = 16; *k = 4; }
+  else if (vecs <= 128) { *g = 32; *k = 4; }
+  else if (vecs <= 256) { *g = 32; *k = 8; }
+  else return false;
+  // Tuning knob: SC_GROUP_LANES=16|32 widens the groups of rows that would use 8 lanes.
+  static const int forced = [] { const char* e = getenv("SC_GROUP_LANES"); return e ? atoi(e) : 0; }();
+  if (*g == 8 && (forced == 16 || forced == 32)) {
+    const int lanes = forced;
+    *k = (vecs + lanes - 1) / lanes;
+    *k = *k <= 1 ? 1 : *k <= 2 ? 2 : 4;
+    *g = lanes;
+  }
+  return true;
+}
+
+template <int W, int K, int G>
 int launch_fwd(const TableDesc* tabs, int count, uint32_t total_act, const uint32_t* offsets, const uint32_t* slots,
                cudaStream_t st) {
   const unsigned warps = (unsigned)ceil_div(total_act, 32);
-  fwd_gather_kernel<W, K><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act, offsets, slots);
+  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act, offsets, slots);
   SC_LAUNCH_OK("fwd_gather_kernel");
   return SC_OK;
 }
 
-template <int W, int K>
-int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, int num_slots, cudaStream_t st) {
+template <int W, int K32>
+int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const float* partial, const uint8_t* flags,
+                 cudaStream_t st) {
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
-  if (num_slots == 0) bwd_main_kernel<W, K, 0><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial);
-  else if (num_slots == 1) bwd_main_kernel<W, K, 1><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial);
-  else bwd_main_kernel<W, K, 2><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial);
-  SC_LAUNCH_OK("bwd_main_kernel");
-  bwd_fixup_kernel<W, K><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial);
+  bwd_fixup_kernel<W, K32><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
   SC_LAUNCH_OK("bwd_fixup_kernel");
   return SC_OK;
 }
 
-#define SC_SHAPE_SWITCH(w, k, CALL)          \
-  do {                                       \
-    if (w == 4 && k == 1) return CALL(4, 1); \
-    if (w == 4 && k == 2) return CALL(4, 2); \
-    if (w == 4 && k == 4) return CALL(4, 4); \
-    if (w == 4 && k == 8) return CALL(4, 8); \
-    if (w == 1 && k == 1) return CALL(1, 1); \
-    if (w == 1 && k == 2) return CALL(1, 2); \
-    if (w == 1 && k == 4) return CALL(1, 4); \
-    return CALL(1, 8);                       \
+template <int K, int NS>
+int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags, int max_dim,
+                   cudaStream_t st) {
+  const int ring_floats = pipe_ring_rows(K, NS) * max_dim;
+  const size_t smem = (size_t)kPipeWarps * ((size_t)ring_floats * 4 + 32 * (2 + NS) * 8 + 32 * 4);
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  (int)cudaSharedmemCarveoutMaxShared));
+  const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
+  bwd_pipe_kernel<K, NS><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, partial, flags, ring_floats);
+  SC_LAUNCH_OK("bwd_pipe_kernel");
+  return SC_OK;
+}
+
+// Update with the cp.async pipeline kernel; K32 = float4 vectors per lane of a full warp.
+template <int K32>
+int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags, int num_slots,
+                    int max_dim, cudaStream_t st) {
+  int rc;
+  if (num_slots == 0) rc = launch_pipe_ns<K32, 0>(tabs, count, total_chunks, partial, flags, max_dim, st);
+  else if (num_slots == 1) rc = launch_pipe_ns<K32, 1>(tabs, count, total_chunks, partial, flags, max_dim, st);
+  else rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, partial, flags, max_dim, st);
+  if (rc != SC_OK) return rc;
+  return launch_fixup<4, K32>(tabs, count, total_chunks, partial, flags, st);
+}
+
+inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags,
+                             int num_slots, int max_dim, cudaStream_t st) {
+  const int vecs = (max_dim / 4 + 31) / 32;
+  if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
+  if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
+  if (vecs <= 4) return launch_bwd_pipe<4>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
+  return launch_bwd_pipe<8>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// The cp.async pipeline is the default; SC_BWD_KERNEL=groups selects the register-only kernel.
+inline bool pipe_enabled() {
+  static const bool on = [] { const char* e = getenv("SC_BWD_KERNEL"); return !(e && strcmp(e, "groups") == 0); }();
+  return on;
+}
+
+template <int W, int K, int G>
+int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags, int num_slots,
+               cudaStream_t st) {
+  const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
+  if (num_slots == 0) bwd_main_kernel<W, K, G, 0><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
+  else if (num_slots == 1) bwd_main_kernel<W, K, G, 1><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
+  else bwd_main_kernel<W, K, G, 2><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
+  SC_LAUNCH_OK("bwd_main_kernel");
+  // The fix-up kernel keeps the full warp per row: K32 vectors per lane.
+  constexpr int K32 = (K * G + 31) / 32;
+  return launch_fixup<W, K32>(tabs, count, total_chunks, partial, flags, st);
+}
+
+#define SC_SHAPE_SWITCH_W(W, k, g, CALL)             \
+  do {                                               \
+    if (g == 4) return CALL(W, 1, 4);                \
+    if (g == 8 && k == 1) return CALL(W, 1, 8);      \
+    if (g == 8 && k == 2) return CALL(W, 2, 8);      \
+    if (g == 8) return CALL(W, 4, 8);                \
+    if (g == 16 && k == 1) return CALL(W, 1, 16);    \
+    if (g == 16 && k == 2) return CALL(W, 2, 16);    \
+    if (g == 16) return CALL(W, 4, 16);              \
+    if (k == 1) return CALL(W, 1, 32);               \
+    if (k == 2) return CALL(W, 2, 32);               \
+    if (k == 4) return CALL(W, 4, 32);               \
+    return CALL(W, 8, 32);                           \
+  } while (0)
+#define SC_SHAPE_SWITCH(w, k, g, CALL)               \
+  do {                                               \
+    if (w == 4) SC_SHAPE_SWITCH_W(4, k, g, CALL);    \
+    SC_SHAPE_SWITCH_W(1, k, g, CALL);                \
   } while (0)
 
 // ---- forward group -----------------------------------------------------------------------
@@ -803,7 +1112,7 @@ struct FwdPlan {
   std::vector<CsrView> views;
   uint64_t total_slots = 0, total_act = 0;
   int total_shards = 0;
-  int w = 0, k = 0;
+  int w = 0, k = 0, g = 0;
 };
 
 int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
@@ -812,10 +1121,10 @@ int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
   for (int i = 0; i < count; ++i) {
     int st = make_view(&items[i].csr, &p->views[i]);
     if (st != SC_OK) return st;
-    int w, k;
-    if (!pick_shape(p->views[i].dim, &w, &k)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the gather kernel", p->views[i].dim);
-    if (i == 0) { p->w = w; p->k = k; }
-    if (w != p->w || k != p->k) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the row length class (dim %d vs %d)",
+    int w, k, g;
+    if (!pick_group_shape(p->views[i].dim, &w, &k, &g)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the gather kernel", p->views[i].dim);
+    if (i == 0) { p->w = w; p->k = k; p->g = g; }
+    if (w != p->w || k != p->k || g != p->g) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the row length class (dim %d vs %d)",
                                        p->views[i].dim, p->views[0].dim);
     p->total_slots += (uint64_t)p->views[i].coo;
     p->total_act += (uint64_t)p->views[i].bdev;
@@ -846,7 +1155,7 @@ struct BwdPlan {
   std::vector<uint32_t> n_ent;  // entry index space per table (0 for direct tables)
   uint64_t total_chunks = 0, total_ent = 0, total_rows = 0;
   int total_shards = 0, total_sources = 0;
-  int w = 0, k = 0, max_dim = 0, max_slots = 0;
+  int w = 0, k = 0, g = 0, max_dim = 0, max_slots = 0;
 };
 
 int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
@@ -858,10 +1167,10 @@ int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
     int st = make_view(&items[i].csr, &p->views[i]);
     if (st != SC_OK) return st;
     CsrView& v = p->views[i];
-    int w, k;
-    if (!pick_shape(v.dim, &w, &k)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
-    if (i == 0) { p->w = w; p->k = k; }
-    if (w != p->w || k != p->k) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the row length class (dim %d vs %d)",
+    int w, k, g;
+    if (!pick_group_shape(v.dim, &w, &k, &g)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
+    if (i == 0) { p->w = w; p->k = k; p->g = g; }
+    if (w != p->w || k != p->k || g != p->g) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the row length class (dim %d vs %d)",
                                        v.dim, p->views[0].dim);
     const bool pull = items[i].sources != nullptr;
     if (pull) {
@@ -911,6 +1220,7 @@ struct BwdScratch {
   PullSrc* pull;
   int32_t* pull_begin;
   float* partial;
+  uint8_t* flags;  // one byte per chunk, written by the update kernel for the fix-up kernel
 };
 
 bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
@@ -920,6 +1230,7 @@ bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
   s->pull = ws.take<PullSrc>((size_t)p.total_sources + 1);
   s->pull_begin = ws.take<int32_t>((size_t)p.total_sources + 1);
   s->partial = ws.take<float>((size_t)2 * (size_t)p.total_chunks * (size_t)p.max_dim);
+  s->flags = ws.take<uint8_t>((size_t)p.total_chunks + 1);
   return ws.ok();
 }
 
@@ -976,8 +1287,8 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   fwd_offsets_kernel<<<(unsigned)ceil_div((int64_t)total_slots + 1, kBlock), kBlock, 0, cs>>>(s.sort.keys[res], total_slots, total_act,
                                                                                            s.offsets);
   SC_LAUNCH_OK("fwd_offsets_kernel");
-#define SC_FWD_CALL(W, K) launch_fwd<W, K>(tabs, count, total_act, s.offsets, s.sort.vals[res], cs)
-  SC_SHAPE_SWITCH(p.w, p.k, SC_FWD_CALL);
+#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, s.offsets, s.sort.vals[res], cs)
+  SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL);
 #undef SC_FWD_CALL
 }
 
@@ -1005,9 +1316,11 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
   std::vector<PullSrc> pull_host;
   uint32_t chunk_base = 0, ent_base = 0, row_base = 0;
   int source_base = 0;
+  bool ring = p.w == 4 && pipe_enabled();  // 16-byte asynchronous copies need aligned rows
   for (int i = 0; i < count; ++i) {
     const sc_optimizer_t& o = items[i].optimizer;
     const bool pull = items[i].sources != nullptr;
+    ring = ring && aligned16(items[i].activation_grad);
     TableDesc td;
     memset(&td, 0, sizeof td);
     td.v = p.views[i];
@@ -1037,6 +1350,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
       for (int sidx = 0; sidx < items[i].num_sources; ++sidx) {
         const sc_pull_source_t& src = items[i].sources[sidx];
         pull_host.push_back(PullSrc{src.row_pointers, src.embedding_ids, src.sample_ids, src.gains, src.activation_grad});
+        ring = ring && aligned16(src.activation_grad);
       }
       source_base += items[i].num_sources;
       td.v.P = 1;  // row -> pointer arithmetic of the update sees the owned shard only
@@ -1048,6 +1362,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
       pool_index.push_back((int)img.pool.size());
       for (int g = 0; g < table_shards; ++g) {
         if (!srcs[a][g]) SC_FAIL(SC_INVALID_ARGUMENT, "shard %d misses a table or slot pointer", g);
+        ring = ring && aligned16(srcs[a][g]);
         img.pool.push_back(srcs[a][g]);
       }
     }
@@ -1081,8 +1396,9 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     SC_LAUNCH_OK("bwd_ranges_kernel");
   }
   const uint32_t total_chunks = (uint32_t)p.total_chunks;
-#define SC_BWD_CALL(W, K) launch_bwd<W, K>(tabs, count, total_chunks, s.partial, p.max_slots, cs)
-  SC_SHAPE_SWITCH(p.w, p.k, SC_BWD_CALL);
+  if (ring) return dispatch_bwd_pipe(tabs, count, total_chunks, s.partial, s.flags, p.max_slots, p.max_dim, cs);
+#define SC_BWD_CALL(W, K, G) launch_bwd<W, K, G>(tabs, count, total_chunks, s.partial, s.flags, p.max_slots, cs)
+  SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_BWD_CALL);
 #undef SC_BWD_CALL
 }
 
@@ -1213,13 +1529,14 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   if (kind >= 2 && (!shard_slot1 || !shard_slot1[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
   if (!isnan(optimizer->clip_min) && !isnan(optimizer->clip_max) && optimizer->clip_min > optimizer->clip_max)
     SC_FAIL(SC_INVALID_ARGUMENT, "min_value must be less than or equal to max_value");
-  int w, k;
-  if (!pick_shape(v.dim, &w, &k)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
+  int w, k, g;
+  if (!pick_group_shape(v.dim, &w, &k, &g)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
 
-  // Layout inside the static array: [TableDesc | 3 shard pointers | partial sums].
+  // Layout inside the static array: [TableDesc | 3 shard pointers | partial sums | chunk flags].
   const size_t image = align_up(sizeof(TableDesc), 256) + align_up(3 * sizeof(float*), 256);
   const uint32_t chunks = (uint32_t)ceil_div(v.coo, 32);
-  const size_t need = image + (size_t)2 * chunks * (size_t)v.dim * sizeof(float);
+  const size_t partial_bytes = (size_t)2 * chunks * (size_t)v.dim * sizeof(float);
+  const size_t need = image + partial_bytes + chunks;
   if (need > (size_t)SC_STATIC_SCRATCH_BYTES)
     SC_FAIL(SC_WORKSPACE_TOO_SMALL,
             "the allocation-free update needs %zu scratch bytes for coo_buffer_size %d and dim %d but the built-in scratch "
@@ -1238,6 +1555,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   char* base = static_cast<char*>(g_static_scratch_ptr[dev]);
   float** pool_dev = reinterpret_cast<float**>(base + align_up(sizeof(TableDesc), 256));
   float* partial = reinterpret_cast<float*>(base + image);
+  uint8_t* flags = reinterpret_cast<uint8_t*>(base + image + partial_bytes);
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
   struct { TableDesc td; } host;
@@ -1257,7 +1575,10 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   SC_CUDA_OK(cudaMemcpyAsync(base, &host.td, sizeof(TableDesc), cudaMemcpyHostToDevice, cs));
   SC_CUDA_OK(cudaMemcpyAsync(pool_dev, pool_host, sizeof pool_host, cudaMemcpyHostToDevice, cs));
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(base);
-#define SC_STATIC_CALL(W, K) launch_bwd<W, K>(tabs, 1, chunks, partial, kind, cs)
-  SC_SHAPE_SWITCH(w, k, SC_STATIC_CALL);
+  if (w == 4 && pipe_enabled() && aligned16(activation_grad) && aligned16(pool_host[0]) && aligned16(pool_host[1]) &&
+      aligned16(pool_host[2]))
+    return dispatch_bwd_pipe(tabs, 1, chunks, partial, flags, kind, v.dim, cs);
+#define SC_STATIC_CALL(W, K, G) launch_bwd<W, K, G>(tabs, 1, chunks, partial, flags, kind, cs)
+  SC_SHAPE_SWITCH(w, k, g, SC_STATIC_CALL);
 #undef SC_STATIC_CALL
 }

@@ -121,13 +121,16 @@ def _device_operands(rp, ids, sids, gains):
           _native.as_device(gains, torch.float32, "lhs_gains"))
 
 
-def shape_class(dim: int) -> tuple[int, int]:
-  """(vector width, vectors per lane) the kernels use for a row of `dim` floats."""
+def shape_class(dim: int) -> tuple[int, int, int]:
+  """(vector width, vectors per lane, lanes per row) the kernels use for a row of `dim` floats.
+
+  Tables of one grouped call must agree on it; mirrors pick_group_shape in csrc/sc_lookup.cu.
+  """
   w = 4 if dim % 4 == 0 else 1
-  need = -(-(dim // w) // 32)
-  for k in (1, 2, 4, 8):
-    if need <= k:
-      return w, k
+  vecs = dim // w
+  for limit, k, g in ((4, 1, 4), (8, 1, 8), (16, 2, 8), (32, 4, 8), (64, 4, 16), (128, 4, 32), (256, 8, 32)):
+    if vecs <= limit:
+      return w, k, g
   raise ValueError(f"embedding dimension {dim} is too large")
 
 

@@ -29,7 +29,7 @@ def assert_close(got, want):
 CASES = [c for c in cases.standard_cases() if c.local_device_count == c.global_device_count]
 
 
-def _setup(case, seed=0):
+def _setup(case, seed=0, dim_override=None):
   """Oracle CSR per stack plus random shards / gradients."""
   import torch
 
@@ -43,7 +43,7 @@ def _setup(case, seed=0):
     spec = next(f.table_spec.stacked_table_spec for f in case.feature_specs
                 if f.table_spec.stacked_table_spec.stack_name == name)
     rows = spec.stack_vocab_size // p
-    dim = spec.stack_embedding_dim
+    dim = dim_override or spec.stack_embedding_dim
     bdev = spec.total_sample_count // case.global_device_count
     shards = rng.normal(0, 0.01, size=(p, rows, dim)).astype(np.float32)
     csr = [tuple(out[i][name][d] for i in range(4)) for d in range(case.local_device_count)]
@@ -133,6 +133,43 @@ def test_backward_is_reproducible_and_hot_rows():
   assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
   assert_close(outs[0][0].cpu().numpy(), want[0][0])
   assert_close(outs[0][1].cpu().numpy(), want[1][0])
+
+
+@pytest.mark.parametrize("opt", ["sgd", "adagrad", "adam"])
+@pytest.mark.parametrize("dim", [3, 6, 20, 30, 50, 100, 130, 256, 384, 512, 1024])
+def test_row_length_classes(dim, opt):
+  """Every row-length variant of the kernels (odd dims included) with 0, 1 and 2 slot variables."""
+  import torch
+
+  case = cases.make_case("dims", seed=dim, batch=256, optimizer="adagrad", num_sc_per_device=2, tables=[
+      dict(vocab=700, dim=8, features=[dict(kind="ragged", max_len=12, dist="zipf")])])
+  st = _setup(case, dim_override=dim)["table_0"]
+  shards = st["shards"]
+  kw = _kw(case, st["spec"])
+  want = np.concatenate(lo.forward(st["csr"], shards, num_sc_per_device=2, device_batch_size=st["bdev"]))
+  dev = lambda a: torch.from_numpy(a.reshape(-1, a.shape[-1]).copy()).cuda()
+  got = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
+      *st["flat"], np.int32(1), dev(shards), device_batch_size=st["bdev"], **kw)
+  np.testing.assert_array_equal(got.cpu().numpy(), want)
+  g, touched = lo.table_gradient(st["csr"], st["grads"], shards.shape, num_sc_per_device=2)
+  acc = np.full(shards.shape, 0.1, np.float32)
+  vel = np.full(shards.shape, 1e-4, np.float32)
+  grad = torch.from_numpy(np.concatenate(st["grads"])).cuda()
+  if opt == "sgd":
+    want_all = lo.apply_sgd(shards, g, touched, 0.05)
+    got_all = (sparse_dense_matmul_grad_with_sgd.tpu_sparse_dense_matmul_grad_with_sgd_primitive.bind(
+        *st["flat"], np.int32(1), dev(shards), grad, np.float32(0.05), **kw),)
+  elif opt == "adagrad":
+    want_all = lo.apply_adagrad(shards, acc, g, touched, 0.05)
+    got_all = sparse_dense_matmul_grad_with_adagrad.tpu_sparse_dense_matmul_grad_with_adagrad_primitive.bind(
+        *st["flat"], np.int32(1), dev(shards), dev(acc), grad, np.float32(0.05), **kw)
+  else:
+    hyp = lo.adam_hyperparameters(1e-3, 0.9, 0.999, 1e-8, 2)
+    want_all = lo.apply_adam(shards, acc, vel, g, touched, *hyp)
+    got_all = sparse_dense_matmul_grad_with_adam.tpu_sparse_dense_matmul_grad_with_adam_primitive.bind(
+        *st["flat"], np.int32(1), dev(shards), dev(acc), dev(vel), grad, *hyp, **kw)
+  for a, b in zip(got_all, want_all):
+    assert_close(a.cpu().numpy(), b)
 
 
 def test_rank1_table():
