@@ -244,13 +244,14 @@ int32_t sc_ipc_release(void* peer_pointer);
  * SC_STATIC_SCRATCH_BYTES array built into the library image, so the call performs no
  * cudaMalloc / cudaFree and takes no workspace.  Limits: one shard and one SparseCore per buffer
  * (num_scs == num_sc_per_device == 1) and
- *   512 + ceil(coo_buffer_size / 32) * (8 * dim + 1)  <=  SC_STATIC_SCRATCH_BYTES,
+ *   512 + chunks * (8 * dim + 1) + ceil(chunks / 32) * (4 * dim + 1)  <=  SC_STATIC_SCRATCH_BYTES
+ * with chunks = ceil(coo_buffer_size / 32),
  * e.g. 65536 slots at dim 128; larger inputs are rejected with SC_WORKSPACE_TOO_SMALL.
  * The first call on each device resolves the address of the array (cudaGetSymbolAddress); make
  * that first call before any stream capture begins.  All calls on a device share the one array:
  * the call overwrites every scratch word it later reads, so nothing needs clearing, but two
  * calls that overlap on the GPU (different streams) race and must be serialised by the caller. */
-#define SC_STATIC_SCRATCH_BYTES (2 * 1024 * 1024 + 4096)
+#define SC_STATIC_SCRATCH_BYTES (2 * 1024 * 1024 + 64 * 1024)
 int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const float* activation_grad_device,
                                            float* const* shard_tables_host, float* const* shard_slot0_host,
                                            float* const* shard_slot1_host, const sc_optimizer_t* optimizer,

@@ -116,6 +116,20 @@ __device__ __forceinline__ int find_table(int count, uint32_t x, F base_of) {
   return lo;
 }
 
+// Same result as find_table for an ascending base_of, computed by the whole warp with one load
+// per lane (all 32 lanes must call it).
+template <typename F>
+__device__ __forceinline__ int warp_find_table(int count, uint32_t x, int lane, F base_of) {
+  int t = -1;
+  for (int base = 0; base < count; base += 32) {
+    const int i = base + lane;
+    const uint32_t below = __ballot_sync(0xffffffffu, i < count && base_of(i) <= x);
+    t += __popc(below);
+    if (below != 0xffffffffu) break;
+  }
+  return t;
+}
+
 // Destination shard of slot `local` (relative to its SparseCore slice), or -1 for
 // alignment padding / the unwritten tail.  Shard g owns [round_up(rp[g-1], 8), rp[g]).
 __device__ __forceinline__ int slot_shard(const CsrView& v, int s, int local) {
@@ -570,17 +584,32 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 constexpr int kPipeBlock = 128;
 constexpr int kPipeWarps = kPipeBlock / 32;
 constexpr int kPipeAhead = 2;  // batches in flight while one is consumed
-// Rows copied per batch for K float4 vectors per lane (about 2 KiB), and rows in a warp's ring.
+// Rows copied per batch for K float4 vectors per lane (about 2 KiB).
 __host__ __device__ constexpr int pipe_batch_rows(int K) { return K == 1 ? 4 : K == 2 ? 2 : 1; }
-// While batch b is consumed, batches b + 1 .. b + kPipeAhead are in flight and an entry that
-// ends in batch b may still need up to 1 + NS rows of earlier batches.
-__host__ __device__ constexpr int pipe_ring_rows(int K, int NS) { return (kPipeAhead + 1) * pipe_batch_rows(K) + 1 + NS; }
+// Rows in a warp's ring.  While batch b is consumed, batches b + 1 .. b + kPipeAhead are in
+// flight and the update of batch b may still read the 1 + NS rows before it; rounded up to a
+// power of two so that a row's slot is `row & (R - 1)`.
+__host__ __device__ constexpr int pipe_ring_rows(int K, int NS) {
+  const int need = (kPipeAhead + 1) * pipe_batch_rows(K) + 1 + NS;
+  return need <= 4 ? 4 : need <= 8 ? 8 : 16;
+}
+__host__ __device__ constexpr int pipe_list_rows(int K, int NS) { return 32 * (2 + NS) + pipe_batch_rows(K); }
+// Per-warp shared memory besides the ring: row addresses (8 bytes), descriptors and gains (4 + 4).
+__host__ __device__ constexpr int pipe_list_bytes(int K, int NS) { return pipe_list_rows(K, NS) * 16; }
+
+// What the consumer does with a row of the list.
+constexpr uint32_t kRowGrad = 1;     // a gradient row: acc += gain * row
+constexpr uint32_t kRowZero = 2;     // ... after clearing acc (first entry of a run)
+constexpr uint32_t kRowIgnore = 4;   // ... but the entry has no gradient row: add nothing
+constexpr uint32_t kRowPartial = 8;  // ... and then store acc as the chunk's partial sum
+constexpr uint32_t kRowHead = 16;    // ... in the slot of a run that started in this chunk
+constexpr uint32_t kRowApply = 32;   // the last of the 1 + NS table / slot rows: apply the optimizer
 
 __device__ __forceinline__ float fast_axpy(float a, float g, float x) { return __fmaf_rn(g, x, a); }
 
 // Optimizer step of the pipelined kernel: fused multiply-adds and the hardware reciprocal square
 // root (2 ulp) instead of IEEE sqrt + divide; within 1e-6 relative of apply_opt.
-__device__ __forceinline__ float apply_opt_fast(const OptParams& o, float w, float g, float& s0, float& s1) {
+__device__ __forceinline__ float apply_opt_fast(const OptParams& o, bool clipped, float w, float g, float& s0, float& s1) {
   float nw;
   if (o.kind == 0) {
     nw = __fmaf_rn(-o.h0, g, w);
@@ -592,31 +621,39 @@ __device__ __forceinline__ float apply_opt_fast(const OptParams& o, float w, flo
     s1 = __fmaf_rn(1.0f - o.h2, g * g - s1, s1);
     nw = w - __fdividef(o.h0 * s0, sqrtf(s1) + o.h3);
   }
-  return clip(nw, o.lo, o.hi);
+  return clipped ? clip(nw, o.lo, o.hi) : nw;
+}
+
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
 }
 
 // Same contract as bwd_main_kernel, for rows of `dim` floats with dim % 4 == 0 and 16-byte aligned
 // tables, slot variables and gradients.  A warp owns 32 consecutive entries.  Lane j describes
-// entry j: its gradient row and, when a run that this warp owns entirely ends at j, the table
-// row and the NS slot rows to update.  The addresses of all those rows are laid out, in entry
-// order, in a per-warp list in shared memory.  The warp then streams the list through a ring of
-// row slots with cp.async (16 bytes per lane, nothing held in registers while in flight): B rows
-// per commit group, kPipeAhead groups in flight, and consumes every entry as soon as its last
-// row has landed -- K float4 per lane from shared memory.  The pipeline is therefore as deep for
-// a chunk of 32 single-entry rows as for one long run, and the in-flight bytes per warp do not
-// depend on the optimizer.
+// entry j and appends its rows to a per-warp list in shared memory, in entry order: the
+// gradient row and, when a run that this warp owns entirely ends at j, the table row and the NS
+// slot rows to update -- each with its address, a descriptor (kRow* flags) and the gain.  The
+// warp then streams the list through a ring of R row slots with cp.async (16 bytes per lane,
+// nothing held in registers while in flight): B rows per commit group, kPipeAhead groups in
+// flight, and executes the descriptors of a batch as soon as it has landed -- K float4 per lane
+// from shared memory.  The pipeline is as deep for a chunk of 32 single-entry rows as for one
+// long run, and the bytes in flight per warp do not depend on the optimizer.
 template <int K, int NS>
 __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                              float* __restrict__ partial, uint8_t* __restrict__ chunk_flags,
                                                              int ring_floats) {
   constexpr int B = pipe_batch_rows(K);
   constexpr int R = pipe_ring_rows(K, NS);
-  constexpr int kMaxRows = 32 * (2 + NS);
+  constexpr int kListRows = pipe_list_rows(K, NS);
+  constexpr int kLanesPerRow = 32 / B;        // lanes that copy one row of a batch
+  constexpr int kPieces = K * B;              // 16-byte pieces per lane and row
   extern __shared__ __align__(128) unsigned char pipe_smem[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t gchunk = blockIdx.x * kPipeWarps + wib;
   if (gchunk >= total_chunks) return;
-  const int t = find_table(count, gchunk, [&](int i) { return tabs[i].chunk_base; });
+  const int t = warp_find_table(count, gchunk, lane, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
   const CsrView& v = td.v;
   const int n = entry_count(td);
@@ -628,12 +665,13 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   const RowCtx ctx = make_ctx(td);
   const int dim = ctx.dim;
   const int vec_per_row = dim >> 2;
-  // Shared memory: [rings of all warps | row lists of all warps | gains of all warps].
-  const float* ring = reinterpret_cast<const float*>(pipe_smem) + (size_t)wib * ring_floats;
-  const float** rowlist = reinterpret_cast<const float**>(pipe_smem + (size_t)kPipeWarps * ring_floats * 4) + wib * kMaxRows;
-  float* gains = reinterpret_cast<float*>(pipe_smem + (size_t)kPipeWarps * (ring_floats * 4 + kMaxRows * 8)) + wib * 32;
-  const uint32_t ring_base = smem_addr(ring);
   const uint32_t rowbytes = (uint32_t)dim * 4u;
+  // Shared memory: [rings of all warps | lists of all warps]; a list is addresses, descriptors, gains.
+  const uint32_t ring_base = smem_addr(pipe_smem) + (uint32_t)wib * (uint32_t)ring_floats * 4u;
+  unsigned char* list = pipe_smem + (size_t)kPipeWarps * ring_floats * 4 + (size_t)wib * pipe_list_bytes(K, NS);
+  const float** rowaddr = reinterpret_cast<const float**>(list);
+  uint32_t* rowdesc = reinterpret_cast<uint32_t*>(list + kListRows * 8);
+  float* rowgain = reinterpret_cast<float*>(list + kListRows * 12);
 
   const int e = e0 + lane;
   const uint32_t my_row = entry_row(td, e, n);
@@ -643,6 +681,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   const bool valid = my_row != kNoRow;
   const float* my_src = nullptr;
   float my_gain = 0.f;
+  const float* any_grad = td.grad;  // a readable address for entries without a gradient row
   if (valid) {
     const int q = td.indirect ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
     if (td.pull != nullptr) {
@@ -651,9 +690,10 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
       const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
       const int sid = src.sids[slot];
       my_gain = src.gains[slot];
+      any_grad = src.grad;
       if (sid >= 0 && sid < v.bdev) my_src = src.grad + (int64_t)sid * dim;
     } else {
-      const int s = q / v.coo_per_sc;
+      const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
       const int sid = v.sids[q];
       my_gain = v.gains[q];
       if (sid >= 0 && sid < v.bsc) my_src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
@@ -673,155 +713,234 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   const bool is_end = valid && (lane == 31 || (((starts | ~valids) >> (lane + 1)) & 1u));
   const bool goes_on = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
   const bool w_end = is_end && head_run && !goes_on;                // apply the optimizer here
-  const bool has_src = valid && my_src != nullptr;
-  const uint32_t srcmask = __ballot_sync(0xffffffffu, has_src);
   const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
-  const uint32_t endmask = __ballot_sync(0xffffffffu, is_end);
-  const uint32_t headrunmask = __ballot_sync(0xffffffffu, head_run);
-  const int jmax = 32 - __clz(valids);
   if (lane == 31)
     chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
-  {
-    int o = __popc(srcmask & lt) + (1 + NS) * __popc(wendmask & lt);
-    if (has_src) rowlist[o++] = my_src;
+  const int total = __popc(valids) + (1 + NS) * __popc(wendmask);  // rows to stream
+  if (valid) {
+    int o = __popc(valids & lt) + (1 + NS) * __popc(wendmask & lt);
+    rowaddr[o] = my_src != nullptr ? my_src : any_grad;
+    rowdesc[o] = kRowGrad | (((starts >> lane) & 1u) ? kRowZero : 0u) | (my_src == nullptr ? kRowIgnore : 0u) |
+                 ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u);
+    rowgain[o] = my_gain;
     if (w_end) {
       float *pw, *pa, *pb;
       row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
-      rowlist[o++] = pw;
-      if (NS >= 1) rowlist[o++] = pa;
-      if (NS >= 2) rowlist[o++] = pb;
+      rowaddr[++o] = pw;
+      rowdesc[o] = NS == 0 ? kRowApply : 0u;
+      if (NS >= 1) { rowaddr[++o] = pa; rowdesc[o] = NS == 1 ? kRowApply : 0u; }
+      if (NS >= 2) { rowaddr[++o] = pb; rowdesc[o] = kRowApply; }
     }
-    gains[lane] = my_gain;
   }
-  const int total = __popc(srcmask) + (1 + NS) * __popc(wendmask);  // rows to stream
+  if (lane < B) rowdesc[total + lane] = 0;  // the tail of the last batch does nothing
   __syncwarp();
 
-  // Copies rows [b * B, b * B + B) of the list into their ring slots; always one commit group.
-  auto issue_batch = [&](int b) {
+  // Copies the next B rows of the list into their ring slots, kLanesPerRow lanes per row;
+  // always exactly one commit group.
+  int issue_row = 0;
+  const int my_sub = lane / kLanesPerRow, my_piece = lane % kLanesPerRow;
+  auto issue_batch = [&]() {
+    const int r = issue_row + my_sub;
+    if (r < total) {
+      const char* src = reinterpret_cast<const char*>(rowaddr[r]) + my_piece * 16;
+      const uint32_t dst = ring_base + (uint32_t)(r & (R - 1)) * rowbytes + (uint32_t)my_piece * 16u;
 #pragma unroll
-    for (int i = 0; i < B; ++i) {
-      const int r = b * B + i;
-      if (r < total) {
-        const float* src = rowlist[r];
-        const uint32_t dst = ring_base + (uint32_t)(r % R) * rowbytes;
-#pragma unroll
-        for (int k = 0; k < K; ++k) {
-          const int c = lane + k * 32;
-          if (c < vec_per_row) cp_async16(dst + (uint32_t)c * 16u, src + c * 4);
-        }
-      }
+      for (int k = 0; k < kPieces; ++k)
+        if (my_piece + k * kLanesPerRow < vec_per_row) cp_async16(dst + k * kLanesPerRow * 16, src + k * kLanesPerRow * 16);
     }
+    issue_row += B;
     cp_async_commit();
   };
 
+  const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
   float4 acc[K];
-  // Consumes entry j, whose rows start at list position `off`.
-  auto consume = [&](int j, int off) {
-    const uint32_t bit = 1u << j;
-    if (starts & bit) {
 #pragma unroll
-      for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    if (srcmask & bit) {
-      const float gain = gains[j];
-      const float4* g = reinterpret_cast<const float4*>(ring + (size_t)(off % R) * dim);
+  for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Executes the descriptor of list row r.
+  auto consume_row = [&](int r) {
+    const uint32_t d = rowdesc[r];
+    const uint32_t slot_addr = ring_base + (uint32_t)(r & (R - 1)) * rowbytes + (uint32_t)lane * 16u;
+    if (d & kRowGrad) {
+      if (d & kRowZero) {
 #pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const int c = lane + k * 32;
-        if (c < vec_per_row) {
-          const float4 x = g[c];
-          acc[k].x = fast_axpy(acc[k].x, gain, x.x); acc[k].y = fast_axpy(acc[k].y, gain, x.y);
-          acc[k].z = fast_axpy(acc[k].z, gain, x.z); acc[k].w = fast_axpy(acc[k].w, gain, x.w);
+        for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      if (!(d & kRowIgnore)) {
+        const float gain = rowgain[r];
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          if (lane + k * 32 < vec_per_row) {
+            const float4 x = lds128(slot_addr + k * 512);
+            acc[k].x = fast_axpy(acc[k].x, gain, x.x); acc[k].y = fast_axpy(acc[k].y, gain, x.y);
+            acc[k].z = fast_axpy(acc[k].z, gain, x.z); acc[k].w = fast_axpy(acc[k].w, gain, x.w);
+          }
         }
       }
-      ++off;
-    }
-    if (!(endmask & bit)) return;
-    if (wendmask & bit) {
-      float* pw = const_cast<float*>(rowlist[off]);
-      float* pa = NS >= 1 ? const_cast<float*>(rowlist[off + (NS >= 1 ? 1 : 0)]) : nullptr;
-      float* pb = NS >= 2 ? const_cast<float*>(rowlist[off + (NS >= 2 ? 2 : 0)]) : nullptr;
-      const float4* sw = reinterpret_cast<const float4*>(ring + (size_t)(off % R) * dim);
-      const float4* sa = reinterpret_cast<const float4*>(ring + (size_t)((off + 1) % R) * dim);
-      const float4* sb = reinterpret_cast<const float4*>(ring + (size_t)((off + 2) % R) * dim);
+      if (d & kRowPartial) {
+        float4* dst = reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * dim);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          const int c = lane + k * 32;
+          if (c < vec_per_row) dst[c] = acc[k];
+        }
+      }
+    } else if (d & kRowApply) {
+      // Rows r - NS .. r hold the table row and the slot rows.
+      float* pw = const_cast<float*>(rowaddr[r - NS]);
+      float* pa = NS >= 1 ? const_cast<float*>(rowaddr[r - NS + (NS >= 1 ? 1 : 0)]) : nullptr;
+      float* pb = NS >= 2 ? const_cast<float*>(rowaddr[r]) : nullptr;
+      const uint32_t lane_off = (uint32_t)lane * 16u;
+      const uint32_t aw = ring_base + (uint32_t)((r - NS) & (R - 1)) * rowbytes + lane_off;
+      const uint32_t aa = ring_base + (uint32_t)((r - NS + 1) & (R - 1)) * rowbytes + lane_off;
+      const uint32_t ab = ring_base + (uint32_t)(r & (R - 1)) * rowbytes + lane_off;
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int c = lane + k * 32;
         if (c >= vec_per_row) continue;
-        float4 w = sw[c];
-        float4 x0 = NS >= 1 ? sa[c] : make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 x1 = NS >= 2 ? sb[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 w = lds128(aw + k * 512);
+        float4 x0 = NS >= 1 ? lds128(aa + k * 512) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 x1 = NS >= 2 ? lds128(ab + k * 512) : make_float4(0.f, 0.f, 0.f, 0.f);
         float* wf = reinterpret_cast<float*>(&w);
         float* af = reinterpret_cast<float*>(&x0);
         float* bf = reinterpret_cast<float*>(&x1);
         const float* gf = reinterpret_cast<const float*>(&acc[k]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast(ctx.o, wf[i], gf[i], af[i], bf[i]);
+        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
         reinterpret_cast<float4*>(pw)[c] = w;
         if (NS >= 1) reinterpret_cast<float4*>(pa)[c] = x0;
         if (NS >= 2) reinterpret_cast<float4*>(pb)[c] = x1;
       }
-    } else {
-      float4* dst = reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((headrunmask & bit) ? 1 : 0)) * dim);
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const int c = lane + k * 32;
-        if (c < vec_per_row) dst[c] = acc[k];
-      }
-    }
-  };
-  // Consumes, in order, every entry whose rows lie below list position `landed`.
-  int j = 0;
-  auto consume_upto = [&](int landed) {
-    while (j < jmax) {
-      const uint32_t bit = 1u << j;
-      if (valids & bit) {
-        const uint32_t below = bit - 1u;
-        const int off = __popc(srcmask & below) + (1 + NS) * __popc(wendmask & below);
-        const int cnt = (int)((srcmask >> j) & 1u) + (1 + NS) * (int)((wendmask >> j) & 1u);
-        if (off + cnt > landed) break;
-        consume(j, off);
-      }
-      ++j;
     }
   };
 
   const int batches = (total + B - 1) / B;
 #pragma unroll
-  for (int b = 0; b < kPipeAhead; ++b) issue_batch(b);
+  for (int b = 0; b < kPipeAhead; ++b) issue_batch();
   for (int b = 0; b < batches; ++b) {
-    // The slots that batch b + kPipeAhead overwrites held rows of entries that were consumed in
-    // earlier iterations (see pipe_ring_rows).
-    issue_batch(b + kPipeAhead);
+    // The slots that the next batch overwrites held rows of batch b - 2 or older, which no
+    // descriptor of batch b or later reads (see pipe_ring_rows).
+    issue_batch();
     cp_async_wait<kPipeAhead>();  // this lane's copies of batch b have landed
     __syncwarp();                 // ... and every other lane's
-    consume_upto(min(total, (b + 1) * B));
+#pragma unroll
+    for (int i = 0; i < B; ++i) consume_row(b * B + i);
     __syncwarp();                 // all lanes are done with the slots that the next batch recycles
   }
   cp_async_wait<0>();
-  consume_upto(total);  // entries without rows at the end of the chunk
+}
+
+// Second level of the partial sums, for rows hit by thousands of entries.  Warp per group of 32
+// consecutive chunks: if all of them are flagged kChunkAllContinues (they continue one and the
+// same run), their 32 partial sums are added in chunk order into group_partial[group] and the
+// group is flagged, so that the fix-up of that run reads one row instead of 32.
+template <int W, int K>
+__global__ void __launch_bounds__(kBlock) bwd_group_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
+                                                           const float* __restrict__ partial,
+                                                           const uint8_t* __restrict__ chunk_flags,
+                                                           float* __restrict__ group_partial, uint8_t* __restrict__ group_flags) {
+  using VT = typename Vec<W>::T;
+  const int lane = threadIdx.x & 31;
+  const uint32_t group = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const uint32_t c0 = group * 32u;
+  if (c0 >= total_chunks) return;
+  const uint32_t c = c0 + lane;
+  const bool on = c < total_chunks && (chunk_flags[c] & kChunkAllContinues);
+  const bool all = __ballot_sync(0xffffffffu, on) == 0xffffffffu;
+  if (lane == 0) group_flags[group] = all ? 1 : 0;
+  if (!all) return;
+  const int t = find_table(count, c0, [&](int i) { return tabs[i].chunk_base; });
+  const int dim = tabs[t].v.dim;
+  const int vec_per_row = dim / W;
+  VT acc[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) acc[k] = Vec<W>::zero();
+  constexpr int U = K == 1 ? 16 : K == 2 ? 8 : K == 4 ? 4 : 2;  // partial rows in flight
+  for (int i = 0; i < 32; i += U) {
+    VT p[U][K];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * (c0 + i + u) * dim);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int cc = lane + k * 32;
+        p[u][k] = cc < vec_per_row ? src[cc] : Vec<W>::zero();
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int k = 0; k < K; ++k) Vec<W>::add(acc[k], p[u][k]);
+  }
+  VT* dst = reinterpret_cast<VT*>(group_partial + (int64_t)group * dim);
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const int cc = lane + k * 32;
+    if (cc < vec_per_row) dst[cc] = acc[k];
+  }
 }
 
 // Warp per chunk that is flagged kChunkHeadContinues: adds the partial sums of the run that
-// starts in this chunk and goes on through the following ones, in chunk order, and applies the
-// optimizer once.
+// starts in this chunk and goes on through the following ones -- chunk by chunk up to the next
+// group boundary, then whole flagged groups, then chunk by chunk to the run's end -- and
+// applies the optimizer once.
 template <int W, int K>
-__global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
+__global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                            const float* __restrict__ partial,
-                                                           const uint8_t* __restrict__ chunk_flags) {
+                                                           const uint8_t* __restrict__ chunk_flags,
+                                                           const float* __restrict__ group_partial,
+                                                           const uint8_t* __restrict__ group_flags) {
   using VT = typename Vec<W>::T;
   const int lane = threadIdx.x & 31;
   const uint32_t gchunk = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (gchunk >= total_chunks) return;
   if (!(chunk_flags[gchunk] & kChunkHeadContinues)) return;
-  const int t = find_table(count, gchunk, [&](int i) { return tabs[i].chunk_base; });
+  const int t = warp_find_table(count, gchunk, lane, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
-  const int n = entry_count(td);
-  const int e0 = (int)(gchunk - td.chunk_base) * 32;
-  const uint32_t row = entry_row(td, e0 + 31, n);
-  if (row == kNoRow) return;
+  // The flag says that entry 31 of the chunk exists and holds a valid row.
+  const uint32_t e31 = (gchunk - td.chunk_base) * 32u + 31u;
+  const uint32_t row = td.indirect ? td.rows[td.range[0] + e31] - td.row_base : (uint32_t)td.v.ids[e31];
   const int dim = td.v.dim;
   const int vec_per_row = dim / W;
+  // The run covers chunk gchunk + 1, every following chunk flagged kChunkAllContinues and the
+  // chunk after those (where it ends).  The last chunk of a table never carries a flag.
+  // Segment 1: chunks [s1, s1 + n1), none of them past the next group boundary.
+  const uint32_t s1 = gchunk + 1;
+  const uint32_t boundary = (s1 + 31u) & ~31u;
+  uint32_t n1, ng = 0, s3, n3 = 0;
+  bool ended;
+  {
+    const uint32_t c = s1 + lane;
+    const bool on = c < boundary && c < total_chunks && (chunk_flags[c] & kChunkAllContinues);
+    const uint32_t stop = __ballot_sync(0xffffffffu, !on);  // lanes at or past the boundary stop too
+    const uint32_t first = (uint32_t)__ffs(stop) - 1u;      // stop != 0 unless s1 is aligned and all 32 are on
+    if (stop == 0) { n1 = 32; ended = false; }
+    else if (s1 + first < boundary) { n1 = first + 1; ended = true; }  // the chunk that ends the run is included
+    else { n1 = first; ended = false; }
+  }
+  s3 = s1 + n1;
+  if (!ended) {
+    // Segment 2: whole groups starting at s3 (group aligned).
+    for (;;) {
+      const uint32_t g = s3 / 32u + ng + lane;
+      const bool on = (uint64_t)(g + 1) * 32u <= total_chunks && group_flags[g];
+      const uint32_t stop = __ballot_sync(0xffffffffu, !on);
+      if (stop != 0) { ng += (uint32_t)__ffs(stop) - 1u; break; }
+      ng += 32;
+    }
+    // Segment 3: chunks after the groups, up to and including the one that ends the run.
+    s3 += ng * 32u;
+    const uint32_t c = s3 + lane;
+    const bool on = c < total_chunks && (chunk_flags[c] & kChunkAllContinues);
+    const uint32_t stop = __ballot_sync(0xffffffffu, !on);  // never 0: the next group is not all on
+    n3 = (uint32_t)__ffs(stop);
+  }
+  const float* g0 = group_partial + (int64_t)((s1 + n1) / 32u) * dim;
+  const uint32_t total = n1 + ng + n3;
+  auto row_ptr = [&](uint32_t i) -> const VT* {
+    if (i < n1) return reinterpret_cast<const VT*>(partial + (int64_t)2 * (s1 + i) * dim);
+    if (i < n1 + ng) return reinterpret_cast<const VT*>(g0 + (int64_t)(i - n1) * dim);
+    return reinterpret_cast<const VT*>(partial + (int64_t)2 * (s3 + (i - n1 - ng)) * dim);
+  };
   VT acc[K];
   {
     const VT* src = reinterpret_cast<const VT*>(partial + ((int64_t)2 * gchunk + 1) * dim);
@@ -831,23 +950,13 @@ __global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __re
       acc[k] = c < vec_per_row ? src[c] : Vec<W>::zero();
     }
   }
-  // The run covers chunk gchunk + 1 and every following chunk flagged kChunkAllContinues, plus
-  // the one after those (where it ends).  The last chunk of a table never carries a flag.
-  uint32_t c_end = gchunk + 1;  // last chunk with a partial sum of this run
-  for (;;) {
-    const uint32_t c = c_end + lane;
-    const bool on = c < total_chunks && (chunk_flags[c] & kChunkAllContinues);
-    const uint32_t stop = __ballot_sync(0xffffffffu, !on);
-    if (stop != 0) { c_end += (uint32_t)__ffs(stop) - 1u; break; }
-    c_end += 32;
-  }
-  uint32_t c2 = gchunk + 1;
-  constexpr int U = K == 1 ? 16 : K == 2 ? 8 : K == 4 ? 4 : 2;  // partial rows in flight
-  for (; c2 + U <= c_end + 1; c2 += U) {
+  constexpr int U = K <= 2 ? 4 : 2;  // partial rows in flight
+  uint32_t i = 0;
+  for (; i + U <= total; i += U) {
     VT p[U][K];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * (c2 + u) * dim);
+      const VT* src = row_ptr(i + u);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int c = lane + k * 32;
@@ -859,8 +968,8 @@ __global__ void __launch_bounds__(kBlock) bwd_fixup_kernel(const TableDesc* __re
 #pragma unroll
       for (int k = 0; k < K; ++k) Vec<W>::add(acc[k], p[u][k]);
   }
-  for (; c2 <= c_end; ++c2) {
-    const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * c2 * dim);
+  for (; i < total; ++i) {
+    const VT* src = row_ptr(i);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int c = lane + k * 32;
@@ -1021,48 +1130,61 @@ int launch_fwd(const TableDesc* tabs, int count, uint32_t total_act, const uint3
   return SC_OK;
 }
 
+// Scratch that the update kernel hands to the fix-up kernels.
+struct UpdateScratch {
+  float* partial;        // [2 * chunks][dim]: per chunk, sum of the run continued from before / continuing after
+  uint8_t* flags;        // [chunks] kChunk* flags
+  float* group_partial;  // [ceil(chunks / 32)][dim]
+  uint8_t* group_flags;  // [ceil(chunks / 32)]
+};
+inline size_t update_groups(size_t chunks) { return (chunks + 31) / 32; }
+
 template <int W, int K32>
-int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const float* partial, const uint8_t* flags,
-                 cudaStream_t st) {
+int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
+  const unsigned groups = (unsigned)ceil_div(total_chunks, 32);
+  bwd_group_kernel<W, K32><<<(unsigned)ceil_div(groups, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_chunks, u.partial,
+                                                                                        u.flags, u.group_partial, u.group_flags);
+  SC_LAUNCH_OK("bwd_group_kernel");
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
-  bwd_fixup_kernel<W, K32><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
+  bwd_fixup_kernel<W, K32><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
+                                                     u.group_flags);
   SC_LAUNCH_OK("bwd_fixup_kernel");
   return SC_OK;
 }
 
 template <int K, int NS>
-int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags, int max_dim,
+int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int max_dim,
                    cudaStream_t st) {
   const int ring_floats = pipe_ring_rows(K, NS) * max_dim;
-  const size_t smem = (size_t)kPipeWarps * ((size_t)ring_floats * 4 + 32 * (2 + NS) * 8 + 32 * 4);
+  const size_t smem = (size_t)kPipeWarps * ((size_t)ring_floats * 4 + pipe_list_bytes(K, NS));
   SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   (int)cudaSharedmemCarveoutMaxShared));
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
-  bwd_pipe_kernel<K, NS><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, partial, flags, ring_floats);
+  bwd_pipe_kernel<K, NS><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats);
   SC_LAUNCH_OK("bwd_pipe_kernel");
   return SC_OK;
 }
 
 // Update with the cp.async pipeline kernel; K32 = float4 vectors per lane of a full warp.
 template <int K32>
-int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags, int num_slots,
+int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
                     int max_dim, cudaStream_t st) {
   int rc;
-  if (num_slots == 0) rc = launch_pipe_ns<K32, 0>(tabs, count, total_chunks, partial, flags, max_dim, st);
-  else if (num_slots == 1) rc = launch_pipe_ns<K32, 1>(tabs, count, total_chunks, partial, flags, max_dim, st);
-  else rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, partial, flags, max_dim, st);
+  if (num_slots == 0) rc = launch_pipe_ns<K32, 0>(tabs, count, total_chunks, u, max_dim, st);
+  else if (num_slots == 1) rc = launch_pipe_ns<K32, 1>(tabs, count, total_chunks, u, max_dim, st);
+  else rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, u, max_dim, st);
   if (rc != SC_OK) return rc;
-  return launch_fixup<4, K32>(tabs, count, total_chunks, partial, flags, st);
+  return launch_fixup<4, K32>(tabs, count, total_chunks, u, st);
 }
 
-inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags,
+inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u,
                              int num_slots, int max_dim, cudaStream_t st) {
   const int vecs = (max_dim / 4 + 31) / 32;
-  if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
-  if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
-  if (vecs <= 4) return launch_bwd_pipe<4>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
-  return launch_bwd_pipe<8>(tabs, count, total_chunks, partial, flags, num_slots, max_dim, st);
+  if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, u, num_slots, max_dim, st);
+  if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, u, num_slots, max_dim, st);
+  if (vecs <= 4) return launch_bwd_pipe<4>(tabs, count, total_chunks, u, num_slots, max_dim, st);
+  return launch_bwd_pipe<8>(tabs, count, total_chunks, u, num_slots, max_dim, st);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -1074,16 +1196,16 @@ inline bool pipe_enabled() {
 }
 
 template <int W, int K, int G>
-int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, float* partial, uint8_t* flags, int num_slots,
+int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
                cudaStream_t st) {
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
-  if (num_slots == 0) bwd_main_kernel<W, K, G, 0><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
-  else if (num_slots == 1) bwd_main_kernel<W, K, G, 1><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
-  else bwd_main_kernel<W, K, G, 2><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, partial, flags);
+  if (num_slots == 0) bwd_main_kernel<W, K, G, 0><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags);
+  else if (num_slots == 1) bwd_main_kernel<W, K, G, 1><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags);
+  else bwd_main_kernel<W, K, G, 2><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags);
   SC_LAUNCH_OK("bwd_main_kernel");
   // The fix-up kernel keeps the full warp per row: K32 vectors per lane.
   constexpr int K32 = (K * G + 31) / 32;
-  return launch_fixup<W, K32>(tabs, count, total_chunks, partial, flags, st);
+  return launch_fixup<W, K32>(tabs, count, total_chunks, u, st);
 }
 
 #define SC_SHAPE_SWITCH_W(W, k, g, CALL)             \
@@ -1219,8 +1341,7 @@ struct BwdScratch {
   uint32_t* ranges;
   PullSrc* pull;
   int32_t* pull_begin;
-  float* partial;
-  uint8_t* flags;  // one byte per chunk, written by the update kernel for the fix-up kernel
+  UpdateScratch update;
 };
 
 bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
@@ -1229,8 +1350,10 @@ bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
   s->ranges = ws.take<uint32_t>((size_t)count + 1);
   s->pull = ws.take<PullSrc>((size_t)p.total_sources + 1);
   s->pull_begin = ws.take<int32_t>((size_t)p.total_sources + 1);
-  s->partial = ws.take<float>((size_t)2 * (size_t)p.total_chunks * (size_t)p.max_dim);
-  s->flags = ws.take<uint8_t>((size_t)p.total_chunks + 1);
+  s->update.partial = ws.take<float>((size_t)2 * (size_t)p.total_chunks * (size_t)p.max_dim);
+  s->update.flags = ws.take<uint8_t>((size_t)p.total_chunks + 1);
+  s->update.group_partial = ws.take<float>(update_groups(p.total_chunks) * (size_t)p.max_dim + 1);
+  s->update.group_flags = ws.take<uint8_t>(update_groups(p.total_chunks) + 1);
   return ws.ok();
 }
 
@@ -1396,8 +1519,8 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     SC_LAUNCH_OK("bwd_ranges_kernel");
   }
   const uint32_t total_chunks = (uint32_t)p.total_chunks;
-  if (ring) return dispatch_bwd_pipe(tabs, count, total_chunks, s.partial, s.flags, p.max_slots, p.max_dim, cs);
-#define SC_BWD_CALL(W, K, G) launch_bwd<W, K, G>(tabs, count, total_chunks, s.partial, s.flags, p.max_slots, cs)
+  if (ring) return dispatch_bwd_pipe(tabs, count, total_chunks, s.update, p.max_slots, p.max_dim, cs);
+#define SC_BWD_CALL(W, K, G) launch_bwd<W, K, G>(tabs, count, total_chunks, s.update, p.max_slots, cs)
   SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_BWD_CALL);
 #undef SC_BWD_CALL
 }
@@ -1532,11 +1655,13 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   int w, k, g;
   if (!pick_group_shape(v.dim, &w, &k, &g)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
 
-  // Layout inside the static array: [TableDesc | 3 shard pointers | partial sums | chunk flags].
+  // Layout inside the static array: [TableDesc | 3 shard pointers | partial sums | group sums | chunk flags | group flags].
   const size_t image = align_up(sizeof(TableDesc), 256) + align_up(3 * sizeof(float*), 256);
   const uint32_t chunks = (uint32_t)ceil_div(v.coo, 32);
   const size_t partial_bytes = (size_t)2 * chunks * (size_t)v.dim * sizeof(float);
-  const size_t need = image + partial_bytes + chunks;
+  const size_t groups = update_groups(chunks);
+  const size_t group_bytes = groups * (size_t)v.dim * sizeof(float);
+  const size_t need = image + partial_bytes + group_bytes + chunks + groups;
   if (need > (size_t)SC_STATIC_SCRATCH_BYTES)
     SC_FAIL(SC_WORKSPACE_TOO_SMALL,
             "the allocation-free update needs %zu scratch bytes for coo_buffer_size %d and dim %d but the built-in scratch "
@@ -1554,8 +1679,11 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   }
   char* base = static_cast<char*>(g_static_scratch_ptr[dev]);
   float** pool_dev = reinterpret_cast<float**>(base + align_up(sizeof(TableDesc), 256));
-  float* partial = reinterpret_cast<float*>(base + image);
-  uint8_t* flags = reinterpret_cast<uint8_t*>(base + image + partial_bytes);
+  UpdateScratch u;
+  u.partial = reinterpret_cast<float*>(base + image);
+  u.group_partial = reinterpret_cast<float*>(base + image + partial_bytes);
+  u.flags = reinterpret_cast<uint8_t*>(base + image + partial_bytes + group_bytes);
+  u.group_flags = u.flags + chunks;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
   struct { TableDesc td; } host;
@@ -1577,8 +1705,8 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(base);
   if (w == 4 && pipe_enabled() && aligned16(activation_grad) && aligned16(pool_host[0]) && aligned16(pool_host[1]) &&
       aligned16(pool_host[2]))
-    return dispatch_bwd_pipe(tabs, 1, chunks, partial, flags, kind, v.dim, cs);
-#define SC_STATIC_CALL(W, K, G) launch_bwd<W, K, G>(tabs, 1, chunks, partial, flags, kind, cs)
+    return dispatch_bwd_pipe(tabs, 1, chunks, u, kind, v.dim, cs);
+#define SC_STATIC_CALL(W, K, G) launch_bwd<W, K, G>(tabs, 1, chunks, u, kind, cs)
   SC_SHAPE_SWITCH(w, k, g, SC_STATIC_CALL);
 #undef SC_STATIC_CALL
 }
