@@ -146,31 +146,121 @@ __device__ __forceinline__ int slot_shard(const CsrView& v, int s, int local) {
 
 // ------------------------------------------------------------------------ forward
 
+// The forward plan lists, for every activation row, the slots that feed it, in ascending slot
+// order (the order of the reference's sum).  It is a counting sort by activation row:
+//   1. fwd_count_kernel    key[slot] = activation row, rank[slot] = arrival number in that row
+//   2. exclusive scan      offsets[row] = first list position of the row
+//   3. fwd_place_kernel    list[offsets[key] + rank] = slot
+//   4. fwd_rowsort_kernel  arrival order is arbitrary: put each row's slots in ascending order
+//      (insertion sort by one thread for short rows, fwd_bigrow_kernel for the others)
+// Slots are unique, so the sorted lists do not depend on the arrival order.
+
 // key = global activation row of the slot (total_act for slots that hold no entry).
-__global__ void fwd_keys_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots, uint32_t total_act,
-                                uint32_t* __restrict__ keys) {
+__global__ void fwd_count_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots, uint32_t total_act,
+                                 uint32_t* __restrict__ keys, uint32_t* __restrict__ ranks, uint32_t* __restrict__ counts) {
   const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
   if (gq >= total_slots) return;
   const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
   const CsrView& v = tabs[t].v;
   const int q = (int)(gq - tabs[t].slot_base);
-  const int s = q / v.coo_per_sc, local = q - s * v.coo_per_sc;
+  const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
+  const int local = q - s * v.coo_per_sc;
   uint32_t key = total_act;
   if (slot_shard(v, s, local) >= 0) {
     const int sid = v.sids[q];
     if (sid >= 0 && sid < v.bsc) key = tabs[t].act_base + (uint32_t)(s * v.bsc + sid);
   }
   keys[gq] = key;
+  if (key < total_act) ranks[gq] = atomicAdd(&counts[key], 1u);
 }
 
-// offsets[r] = first sorted position whose key is >= r, for r in [0, total_act].
-__global__ void fwd_offsets_kernel(const uint32_t* __restrict__ sorted_keys, uint32_t n, uint32_t total_act,
-                                   uint32_t* __restrict__ offsets) {
-  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i > n) return;
-  const int64_t cur = i < n ? (int64_t)min(sorted_keys[i], total_act) : (int64_t)total_act;
-  const int64_t prev = i > 0 ? (int64_t)min(sorted_keys[i - 1], total_act) : -1;
-  for (int64_t r = prev + 1; r <= cur; ++r) offsets[r] = i;
+__global__ void fwd_place_kernel(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ ranks,
+                                 const uint32_t* __restrict__ offsets, uint32_t total_slots, uint32_t total_act,
+                                 uint32_t* __restrict__ list) {
+  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= total_slots) return;
+  const uint32_t key = keys[gq];
+  if (key < total_act) list[offsets[key] + ranks[gq]] = gq;
+}
+
+constexpr uint32_t kSerialSortLimit = 64;
+
+// Thread per activation row.  Rows longer than kSerialSortLimit go to big_rows.
+__global__ void fwd_rowsort_kernel(const uint32_t* __restrict__ offsets, uint32_t total_act, uint32_t* __restrict__ list,
+                                   uint32_t* __restrict__ big_rows, uint32_t* __restrict__ big_count) {
+  const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= total_act) return;
+  const uint32_t begin = offsets[r], n = offsets[r + 1] - begin;
+  if (n < 2) return;
+  if (n > kSerialSortLimit) {
+    big_rows[atomicAdd(big_count, 1u)] = r;
+    return;
+  }
+  uint32_t* a = list + begin;
+  for (uint32_t i = 1; i < n; ++i) {  // arrival order is close to slot order: few moves
+    const uint32_t x = a[i];
+    uint32_t j = i;
+    while (j > 0 && a[j - 1] > x) { a[j] = a[j - 1]; --j; }
+    a[j] = x;
+  }
+}
+
+// Warp per long row (grid-stride over big_rows): stable LSD radix sort of the row's slots, 8 bits
+// per pass, between `list` and `scratch`.
+__global__ void __launch_bounds__(kBlock) fwd_bigrow_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ list,
+                                                            uint32_t* __restrict__ scratch, const uint32_t* __restrict__ big_rows,
+                                                            const uint32_t* __restrict__ big_count, int key_bits) {
+  __shared__ uint32_t bins[kWarpsPerBlock][256];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t warps = gridDim.x * kWarpsPerBlock;
+  const uint32_t lt = (1u << lane) - 1u;
+  const uint32_t todo = *big_count;
+  for (uint32_t w = blockIdx.x * kWarpsPerBlock + wib; w < todo; w += warps) {
+    const uint32_t r = big_rows[w];
+    const uint32_t begin = offsets[r], n = offsets[r + 1] - begin;
+    uint32_t* src = list + begin;
+    uint32_t* dst = scratch + begin;
+    for (int shift = 0; shift < key_bits; shift += 8) {
+      for (int i = lane; i < 256; i += 32) bins[wib][i] = 0;
+      __syncwarp();
+      for (uint32_t i = lane; i < n; i += 32) atomicAdd(&bins[wib][(src[i] >> shift) & 255u], 1u);
+      __syncwarp();
+      {  // exclusive scan of the 256 bins: 8 per lane
+        uint32_t local[8], sum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { local[i] = sum; sum += bins[wib][lane * 8 + i]; }
+        uint32_t inc = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const uint32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += o;
+        }
+        const uint32_t base = inc - sum;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) bins[wib][lane * 8 + i] = base + local[i];
+      }
+      __syncwarp();
+      for (uint32_t i0 = 0; i0 < n; i0 += 32) {  // 32 consecutive elements per step keeps the order stable
+        const uint32_t i = i0 + lane;
+        const bool in = i < n;
+        const uint32_t x = in ? src[i] : 0u;
+        const uint32_t d = (x >> shift) & 255u;
+        const uint32_t peers = __match_any_sync(0xffffffffu, in ? d : (0x100u | (uint32_t)lane));
+        const uint32_t pos = in ? bins[wib][d] + __popc(peers & lt) : 0u;
+        __syncwarp();
+        if (in && (peers & lt) == 0) bins[wib][d] += __popc(peers);
+        if (in) dst[pos] = x;
+        __syncwarp();
+      }
+      uint32_t* tmp = src; src = dst; dst = tmp;
+    }
+    if (src != list + begin) {  // odd number of passes: copy back
+      __syncwarp();
+      for (uint32_t i = lane; i < n; i += 32) dst[i] = src[i];
+    }
+    __syncwarp();
+  }
 }
 
 template <int W>
@@ -1258,14 +1348,25 @@ int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
 
 struct FwdScratch {
   char* image;
-  SortBuffers sort;
-  uint32_t* offsets;
+  uint32_t* keys;       // [slots] activation row of every slot
+  uint32_t* ranks;      // [slots] arrival number inside the row
+  uint32_t* list;       // [slots] slots ordered by (activation row, slot)
+  uint32_t* scratch;    // [slots] second buffer of the long-row sort
+  uint32_t* offsets;    // [act + 2] counts, then their exclusive scan; the last word counts the long rows
+  uint32_t* scan_temp;
+  uint32_t* big_rows;   // [slots / kSerialSortLimit + 1]
 };
 
 bool carve_fwd(Workspace& ws, const FwdPlan& p, int count, FwdScratch* s) {
+  const size_t slots = (size_t)p.total_slots, act = (size_t)p.total_act;
   s->image = ws.take<char>(image_bytes(count, p.total_shards));
-  carve_sort(ws, (size_t)p.total_slots, &s->sort);
-  s->offsets = ws.take<uint32_t>((size_t)p.total_act + 1);
+  s->keys = ws.take<uint32_t>(slots);
+  s->ranks = ws.take<uint32_t>(slots);
+  s->list = ws.take<uint32_t>(slots);
+  s->scratch = ws.take<uint32_t>(slots);
+  s->offsets = ws.take<uint32_t>(act + 2);
+  s->scan_temp = ws.take<uint32_t>(scan_temp_elems(act + 1));
+  s->big_rows = ws.take<uint32_t>(slots / kSerialSortLimit + 1);
   return ws.ok();
 }
 
@@ -1403,14 +1504,20 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
   const uint32_t total_slots = (uint32_t)p.total_slots, total_act = (uint32_t)p.total_act;
 
-  fwd_keys_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, cs>>>(tabs, count, total_slots, total_act, s.sort.keys[0]);
-  SC_LAUNCH_OK("fwd_keys_kernel");
-  int res = 0;
-  SC_CUDA_OK(radix_sort_pairs(s.sort, (size_t)total_slots, bit_width_u32(total_act), true, &res, cs));
-  fwd_offsets_kernel<<<(unsigned)ceil_div((int64_t)total_slots + 1, kBlock), kBlock, 0, cs>>>(s.sort.keys[res], total_slots, total_act,
-                                                                                           s.offsets);
-  SC_LAUNCH_OK("fwd_offsets_kernel");
-#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, s.offsets, s.sort.vals[res], cs)
+  uint32_t* big_count = s.offsets + total_act + 1;
+  SC_CUDA_OK(cudaMemsetAsync(s.offsets, 0, ((size_t)total_act + 2) * sizeof(uint32_t), cs));
+  const unsigned slot_blocks = (unsigned)ceil_div(total_slots, kBlock);
+  fwd_count_kernel<<<slot_blocks, kBlock, 0, cs>>>(tabs, count, total_slots, total_act, s.keys, s.ranks, s.offsets);
+  SC_LAUNCH_OK("fwd_count_kernel");
+  SC_CUDA_OK(exclusive_scan<uint32_t>(s.offsets, s.offsets, (size_t)total_act + 1, s.scan_temp, nullptr, cs));
+  fwd_place_kernel<<<slot_blocks, kBlock, 0, cs>>>(s.keys, s.ranks, s.offsets, total_slots, total_act, s.list);
+  SC_LAUNCH_OK("fwd_place_kernel");
+  fwd_rowsort_kernel<<<(unsigned)ceil_div(total_act, kBlock), kBlock, 0, cs>>>(s.offsets, total_act, s.list, s.big_rows, big_count);
+  SC_LAUNCH_OK("fwd_rowsort_kernel");
+  fwd_bigrow_kernel<<<(unsigned)sm_count(), kBlock, 0, cs>>>(s.offsets, s.list, s.scratch, s.big_rows, big_count,
+                                                             bit_width_u32(total_slots));
+  SC_LAUNCH_OK("fwd_bigrow_kernel");
+#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, s.offsets, s.list, cs)
   SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL);
 #undef SC_FWD_CALL
 }

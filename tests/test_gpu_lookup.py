@@ -172,6 +172,22 @@ def test_row_length_classes(dim, opt):
     assert_close(a.cpu().numpy(), b)
 
 
+def test_forward_long_bags():
+  """Samples with hundreds of ids in one table take the long-row path of the forward plan."""
+  import torch
+
+  case = cases.make_case("long", seed=5, batch=64, num_sc_per_device=2, combiner="sum", tables=[
+      dict(vocab=5000, dim=32, features=[dict(kind="ragged", min_len=0, max_len=600)])])
+  st = _setup(case)["table_0"]
+  assert max(len(np.unique(r)) for r in case.features[0]) > 300
+  want = np.concatenate(lo.forward(st["csr"], st["shards"], num_sc_per_device=2, device_batch_size=st["bdev"]))
+  table = torch.from_numpy(st["shards"].reshape(-1, st["shards"].shape[-1])).cuda()
+  for _ in range(2):
+    got = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
+        *st["flat"], np.int32(1), table, device_batch_size=st["bdev"], **_kw(case, st["spec"]))
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
 def test_rank1_table():
   """Tables of rank 1 (dim 1), as in the reference's dim-1 forward test."""
   import torch
