@@ -1,0 +1,158 @@
+"""Generates the committed golden fixtures (run where the reference checkout is mounted).
+
+    python tests/golden/make_fixtures.py [--reference /path/to/jax-tpu-embedding]
+
+1. preprocess_reference.npz - every call that the reference's own unit tests
+   (jax_tpu_embedding/sparsecore/lib/core/tests/pybind_input_preprocessing_test.py) make to the
+   preprocessing binding, recorded while those tests run against the CPU oracle.  A call is kept
+   only if the whole reference test suite passes, i.e. the recorded outputs are the ones the
+   reference's hand-written expectations accept.
+2. lookup_known_answers.npz - the known-answer cases of the reference's primitive tests
+   (lib/core/primitives/tests/sparse_dense_matmul_csr_test.py:30-90,343-404,499-556,
+   sparse_dense_matmul_grad_with_sgd_test.py:100-163, sparse_dense_matmul_grad_with_adagrad_test.py:330-400):
+   inputs restated from those files, expected values computed by the dense formulas the tests
+   state, independently of the oracle's CSR walk.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+for p in (os.path.join(ROOT, "tests"), os.path.join(ROOT, "jax-tpu-embedding_b200"), ROOT, HERE):
+  if p not in sys.path:
+    sys.path.insert(0, p)
+
+import fixture_io as fio  # noqa: E402
+
+
+def record_reference_preprocessing(reference_root):
+  import oracle_backend as ob
+  import reference_harness as rh
+  from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+
+  rh.REFERENCE = reference_root
+  calls = []
+
+  def recording_backend(features, feature_weights, feature_specs, local_device_count, global_device_count, **kw):
+    features, feature_specs = list(features), list(feature_specs)
+    weights = None if feature_weights is None else list(feature_weights)
+    features = [np.array(f, copy=True) if isinstance(f, np.ndarray) and f.dtype != object else
+                np.array([np.array(r) for r in f] + [None], dtype=object)[:-1] for f in features]
+    entry = dict(features=features, weights=weights, specs=fio.specs_to_json(feature_specs),
+                 local_device_count=int(local_device_count), global_device_count=int(global_device_count),
+                 kwargs={k: (int(v) if not isinstance(v, bool) else v) for k, v in kw.items()
+                         if k in ("num_sc_per_device", "sharding_strategy", "has_leading_dimension", "allow_id_dropping")})
+    try:
+      out = ob.oracle_preprocess(features, feature_weights, feature_specs, local_device_count, global_device_count, **kw)
+    except Exception as e:  # pylint: disable=broad-except
+      entry["raises"] = [type(e).__name__, str(e)]
+      calls.append(entry)
+      raise
+    # The caller may reshape or overwrite what it receives: keep private copies.
+    import copy
+    entry["out"] = tuple({k: np.array(v) for k, v in d.items()} for d in out[:4]) + (out[4], copy.deepcopy(out[5]))
+    calls.append(entry)
+    return out
+
+  original = pip.preprocess_sparse_dense_matmul_input
+  try:
+    module = rh.load_pybind_test_module(recording_backend)
+    result = rh.run_cases(module)
+  finally:
+    pip.preprocess_sparse_dense_matmul_input = original
+  problems = result.failures + result.errors
+  if problems or result.testsRun < 30:
+    raise SystemExit(f"reference tests did not pass on the oracle ({result.testsRun} run): {problems[:1]}")
+
+  manifest, arrays = dict(source="pybind_input_preprocessing_test.py", tests_run=result.testsRun, calls=[]), {}
+  for i, c in enumerate(calls):
+    m = dict(specs=c["specs"], local_device_count=c["local_device_count"],
+             global_device_count=c["global_device_count"], kwargs=c["kwargs"], features=[], raises=c.get("raises"))
+    for j, f in enumerate(c["features"]):
+      vals, lens, valency = fio.pack_rows(f)
+      arrays[f"c{i}_f{j}_ids"], arrays[f"c{i}_f{j}_len"] = np.asarray(vals, np.int32), lens
+      has_w = c["weights"] is not None and c["weights"][j] is not None
+      if has_w:
+        arrays[f"c{i}_f{j}_w"] = np.asarray(fio.pack_rows(c["weights"][j])[0], np.float32)
+      m["features"].append(dict(valency=int(valency), weights=bool(has_w)))
+    m["weights_given"] = c["weights"] is not None
+    if "out" in c:
+      rp, ids, sids, gains, _, stats = c["out"]
+      m["stacks"] = sorted(rp)
+      for name in rp:
+        for key, d in (("rp", rp), ("ids", ids), ("sids", sids), ("gains", gains)):
+          arrays[f"c{i}_{name}_{key}"] = np.asarray(d[name])
+        arrays[f"c{i}_{name}_max_ids"] = np.asarray(stats.max_ids_per_partition[name])
+        arrays[f"c{i}_{name}_max_unique"] = np.asarray(stats.max_unique_ids_per_partition[name])
+        arrays[f"c{i}_{name}_required"] = np.asarray(stats.required_buffer_sizes[name])
+        arrays[f"c{i}_{name}_dropped"] = np.asarray(stats.dropped_id_count[name])
+    manifest["calls"].append(m)
+  fio.save(os.path.join(HERE, "preprocess_reference.npz"), manifest, arrays)
+  print(f"preprocess_reference.npz: {len(calls)} calls from {result.testsRun} reference tests")
+
+
+def known_answer_lookup_cases():
+  """Dense restatement of the reference's primitive tests; no CSR involved."""
+  ids16 = np.array([5, 3, 9, 1, 6, 12, 0, 4, 15, 13, 11, 7, 8, 14, 2, 10], np.int32).reshape(16, 1)
+  vocab, dim = 32, 8
+  cases, arrays = [], {}
+
+  def add(name, ids, weights, table, **extra):
+    arrays[f"{name}_ids"], arrays[f"{name}_weights"], arrays[f"{name}_table"] = ids, weights, table
+    for k, v in extra.items():
+      arrays[f"{name}_{k}"] = np.asarray(v)
+    cases.append(dict(name=name, keys=sorted(extra)))
+
+  # Forward: table row i holds the value i, one id per sample -> activation = id.
+  table = np.repeat(np.arange(vocab, dtype=np.float32)[:, None], dim, axis=1)
+  add("forward_single_hot", ids16, np.ones((16, 1), np.float32), table,
+      activations=table[ids16[:, 0]])
+  # Forward, rank-1 table, every sample looks its id up twice -> 2 * (id + 1).
+  ids2 = np.concatenate([np.concatenate([ids16, ids16], axis=1)] * 2, axis=0)
+  table1 = (np.arange(vocab, dtype=np.float32) + 1.0).reshape(vocab, 1)
+  add("forward_dim1_duplicates", ids2, np.ones(ids2.shape, np.float32), table1,
+      activations=(2.0 * table1[ids2[:, 0]]))
+  # SGD: gradient 0.01 everywhere, learning rate 0.01 -> touched rows move by -1e-4, then clip.
+  for tag, lo, hi in (("", None, None), ("_clipped", 2.0, 12.5)):
+    want = table.copy()
+    rows = np.unique(ids16)
+    want[rows] -= np.float32(1e-4)
+    if lo is not None:
+      want[rows] = np.clip(want[rows], lo, hi)
+    add("sgd" + tag, ids16, np.ones((16, 1), np.float32), table, grad=np.full((16, dim), 0.01, np.float32),
+        learning_rate=np.float32(0.01), clip=np.array([np.nan if lo is None else lo, np.nan if hi is None else hi], np.float32),
+        table_out=want)
+  # Adagrad: table row i holds i + 1, accumulator 0.002, learning rate 0.1, gradient 0.012, multi-hot with weights.
+  rng = np.random.default_rng(1234)
+  ids_mh = rng.integers(0, vocab, size=(16, 4)).astype(np.int32)
+  w_mh = rng.choice([0.5, 1.0, 2.0], size=(16, 4)).astype(np.float32)
+  table_p1 = table + 1.0
+  act_grad = np.full((16, dim), 0.012, np.float32)
+  g = np.zeros((vocab, dim), np.float32)
+  for s in range(16):
+    for j in range(4):
+      g[ids_mh[s, j]] += w_mh[s, j] * act_grad[s]
+  acc = np.full((vocab, dim), 0.002, np.float32)
+  touched = np.zeros(vocab, bool)
+  touched[np.unique(ids_mh)] = True
+  acc_new = acc + g * g
+  tab_new = table_p1 - (np.float32(0.1) * g) / np.sqrt(acc_new)
+  add("adagrad_multi_hot", ids_mh, w_mh, table_p1, grad=act_grad, learning_rate=np.float32(0.1), accumulator=acc,
+      clip=np.array([np.nan, np.nan], np.float32),
+      table_out=np.where(touched[:, None], tab_new, table_p1), accumulator_out=np.where(touched[:, None], acc_new, acc))
+  fio.save(os.path.join(HERE, "lookup_known_answers.npz"), dict(cases=cases, vocab=vocab), arrays)
+  print(f"lookup_known_answers.npz: {len(cases)} cases")
+
+
+if __name__ == "__main__":
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--reference", default="/root/reference")
+  args = ap.parse_args()
+  known_answer_lookup_cases()
+  record_reference_preprocessing(args.reference)
