@@ -444,7 +444,7 @@ def main():
   bwd_ms = e0.elapsed_time(e1) / reps
   peak, peak_kind = measured_peak_gbs()
   # DRAM traffic of the backward kernels per launch: ncu measured 1.03 x the algorithmic bytes on a
-  # scaled-down c2 case (profiles/c2_small_bwd_main_fwd_gather_full.md); traffic grows with the same
+  # scaled-down c2 case (profiles/c2_small_bwd_pipe_fwd_gather_full.md); traffic grows with the same
   # quantities as the algorithmic figure, so it is scaled to this launch.
   traffic_ratio = 1.03
   achieved = algo_bytes / (bwd_ms * 1e-3) / 1e9
@@ -522,7 +522,7 @@ def main():
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "lookups_per_s": nnz_in * world / (ms * 1e-3),
-        "roofline": {"bound": "hbm", "kernel": "bwd_main_kernel (+fixup), all tables", "achieved": achieved, "peak": peak,
+        "roofline": {"bound": "hbm", "kernel": "bwd_pipe_kernel + bwd_group_kernel + bwd_fixup_kernel (fused backward, all tables)", "achieved": achieved, "peak": peak,
                      "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
                      "traffic": int(algo_bytes * traffic_ratio) if args.workload == "c2" else None,
                      "algorithmic_bytes": int(algo_bytes), "ms": bwd_ms,
