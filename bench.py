@@ -349,7 +349,8 @@ def main():
     torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     distributed.init()
     config["sharding"] = (f"every stacked table row-sharded mod {world} over {world} GPUs (one process per GPU); forward "
-                          "gathers remote rows over NVLink, backward pulls entries and gradient rows from the peers")
+                          "fetches each distinct remote row once over NVLink; backward reduces per (source, row) first, "
+                          "then the owner of a shard pulls one gradient row per source and row")
 
   # Weak scaling: every GPU brings its own batch of wl['batch'] samples; tables are shared.
   specs = build_specs(wl, global_device_count=world, global_batch=wl["batch"] * world)
@@ -374,17 +375,6 @@ def main():
   stacked = embedding.get_stacked_table_specs(specs)
   gen = torch.Generator(device="cuda").manual_seed(5 + rank)
   grads = [torch.randn((wl["batch"], f.output_shape[-1]), generator=gen, device="cuda") * 1e-2 for f in specs]
-  if world > 1 and len(specs) == len(stacked):
-    # The dense part of a model writes its activation gradients straight into the peer-visible
-    # exchange buffers, which saves the staging copy inside the update.
-    for i, f in enumerate(specs):
-      st = f.table_spec.stacked_table_spec
-      key = f"{st.optimizer.short_name()}-{st.stack_name}"
-      buf = distributed.gradient_buffer(key, pre.lhs_row_pointers[st.stack_name].numel(),
-                                        pre.lhs_embedding_ids[st.stack_name].numel(), wl["batch"], st.stack_embedding_dim)
-      buf.copy_(grads[i])
-      grads[i] = buf
-
   def lookup_update():
     acts = embedding.tpu_sparse_dense_matmul(pre, variables, specs, global_device_count=world, num_sc_per_device=1)
     embedding.tpu_sparse_dense_matmul_grad(grads, pre, variables, specs, global_device_count=world,

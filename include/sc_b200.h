@@ -176,6 +176,11 @@ typedef struct {
   sc_csr_t csr;
   const float* const* shard_tables; /* host array [num_scs] of device pointers */
   float* activations;               /* device, [device_batch_size, dim] */
+  /* One process per GPU with row-sharded tables: the shard this device holds in its own memory
+   * (the other shard pointers are peer mappings).  Rows of the other shards are then fetched once
+   * per distinct row into the workspace and gathered from there, so a row that many samples of
+   * the batch look up crosses NVLink once.  -1: read every shard pointer directly. */
+  int32_t local_shard;
 } sc_fwd_item_t;
 
 /* Buffers of one source device as seen from the owner of a shard (peer-mapped device pointers). */
@@ -211,10 +216,14 @@ typedef struct {
 size_t sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(const sc_fwd_item_t* items, int32_t count);
 int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items, int32_t count, void* workspace_device,
                                            size_t workspace_bytes, sc_stream_t stream);
-/* Pull mode only: copies this device's CSR buffers and activation gradients into its own exchange
- * buffers (sources[shard]) with one kernel launch, skipping buffers that already live there; the
- * workspace of the grouped update is large enough.  Follow with a barrier across the devices,
- * then the grouped update. */
+/* Pull mode only, before the barrier across the devices: publishes what this device holds for every
+ * shard in its own exchange buffers (sources[shard]).  When dim % 4 == 0 the gradient rows of all
+ * entries that hit one (shard, row) are summed here first (in slot order) and the exchange carries
+ * one entry and one reduced gradient row per distinct row: sources[...].activation_grad must then
+ * hold coo_buffer_size rows and must not alias the CSR operands.  Otherwise the CSR buffers and
+ * the activation gradients are copied unchanged (activation_grad of device_batch_size rows).
+ * Follow with a barrier across the devices, then the grouped update. */
+size_t sc_sparse_dense_matmul_grad_stage_workspace_bytes(const sc_grad_item_t* items, int32_t count);
 int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, void* workspace_device,
                                           size_t workspace_bytes, sc_stream_t stream);
 size_t sc_sparse_dense_matmul_grad_grouped_workspace_bytes(const sc_grad_item_t* items, int32_t count);

@@ -42,6 +42,7 @@ namespace {
 constexpr int kBlock = 256;
 constexpr int kWarpsPerBlock = kBlock / 32;
 constexpr uint32_t kNoRow = 0xffffffffu;
+constexpr int kReduceOnly = 3;  // OptParams::kind of the reduce-only mode
 
 struct CsrView {
   const int32_t* row_pointers;
@@ -103,6 +104,17 @@ struct TableDesc {
   int32_t pull_cap;
   int32_t pull_shard;
   int32_t num_sources;
+  int32_t pull_rows;    // rows of a source's gradient buffer (samples, or slots when it holds reduced runs)
+  // Reduce-only mode (opt.kind == kReduceOnly, indirect == 2): the entry list is this device's own
+  // CSR buffer (entry e = slot e, rows[e] = shard * rows_per_shard + id or kNoRow) and the sum of
+  // every run is stored at red[first slot of the run] instead of being applied to a table.
+  float* red;
+  // Forward with remote shards (one process per GPU): rows of every shard but `local_shard` are
+  // first copied, once per run of equal ids, into `remote_rows`; run_ord[global slot] is the row's
+  // index there.  local_shard < 0: every shard pointer is read directly.
+  int32_t local_shard;
+  const uint32_t* run_ord;
+  float* remote_rows;
 };
 
 // Index of the table whose [base, next base) range contains x.
@@ -141,6 +153,20 @@ __device__ __forceinline__ int slot_shard(const CsrView& v, int s, int local) {
     if (rp[mid] > local) hi = mid; else lo = mid + 1;
   }
   const int begin = lo == 0 ? 0 : ((rp[lo - 1] + kAlign - 1) & ~(kAlign - 1));
+  return local >= begin ? lo : -1;
+}
+
+// Like slot_shard, also returning the first slot of the partition.
+__device__ __forceinline__ int slot_shard_begin(const CsrView& v, int s, int local, int* begin_out) {
+  const int32_t* rp = v.row_pointers + s * v.R;
+  if (local >= rp[v.P - 1]) return -1;
+  int lo = 0, hi = v.P - 1;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (rp[mid] > local) hi = mid; else lo = mid + 1;
+  }
+  const int begin = lo == 0 ? 0 : ((rp[lo - 1] + kAlign - 1) & ~(kAlign - 1));
+  *begin_out = begin;
   return local >= begin ? lo : -1;
 }
 
@@ -282,6 +308,111 @@ struct Vec<1> {
   static __device__ __forceinline__ void add(T& a, const T& x) { a += x; }
 };
 
+// flags[slot] = 1 where the slot starts a run of equal ids inside a partition of a REMOTE shard.
+// Entries of a partition are ordered by id, so a run is all lookups of one remote row.
+__global__ void fwd_remote_heads_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+                                        uint32_t* __restrict__ flags) {
+  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= total_slots) return;
+  const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
+  const TableDesc& td = tabs[t];
+  const CsrView& v = td.v;
+  uint32_t head = 0;
+  if (td.local_shard >= 0) {
+    const int q = (int)(gq - td.slot_base);
+    const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
+    const int local = q - s * v.coo_per_sc;
+    int begin;
+    const int g = slot_shard_begin(v, s, local, &begin);
+    if (g >= 0 && g != td.local_shard) head = (local == begin || v.ids[q - 1] != v.ids[q]) ? 1u : 0u;
+  }
+  flags[gq] = head;
+}
+
+// One distinct remote row to fetch.
+struct FetchJob {
+  const float* src;  // row in the (peer-mapped) shard
+  float* dst;        // its place in remote_rows
+  int32_t floats;
+  int32_t pad;
+};
+
+// `before` = exclusive scan of the head flags.  Thread per slot: writes run_ord for every slot of
+// a remote partition and, for run heads, the fetch job of the run's row.
+__global__ void fwd_fetch_plan_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+                                      const uint32_t* __restrict__ before, uint32_t* __restrict__ run_ord,
+                                      FetchJob* __restrict__ jobs) {
+  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= total_slots) return;
+  const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
+  const TableDesc& td = tabs[t];
+  const CsrView& v = td.v;
+  if (td.local_shard < 0) return;
+  const int q = (int)(gq - td.slot_base);
+  const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
+  const int local = q - s * v.coo_per_sc;
+  int begin;
+  const int g = slot_shard_begin(v, s, local, &begin);
+  if (g < 0 || g == td.local_shard) return;
+  const int id = v.ids[q];
+  const bool head = local == begin || v.ids[q - 1] != id;
+  const uint32_t job = before[gq] + (head ? 1u : 0u) - 1u;  // index among all runs of the launch
+  const uint32_t ord = job - before[td.slot_base];           // index among the runs of this table
+  run_ord[gq] = ord;
+  if (head) {
+    FetchJob j;
+    const bool ok = id >= 0 && (int64_t)id < v.rows_per_shard;
+    j.src = ok ? td.table[g] + (int64_t)id * v.dim : nullptr;
+    j.dst = td.remote_rows + (int64_t)ord * v.dim;
+    j.floats = v.dim;
+    j.pad = 0;
+    jobs[job] = j;
+  }
+}
+
+// Copies the rows of the fetch jobs: 8 lanes per row, every lane issues all its loads before its
+// first store, a warp takes 8 consecutive jobs.  total_jobs lives in device memory (the scan's total).
+__global__ void __launch_bounds__(kBlock) fwd_fetch_kernel(const FetchJob* __restrict__ jobs, const uint32_t* __restrict__ total_jobs,
+                                                           uint32_t max_jobs) {
+  const int lane = threadIdx.x & 31, group = lane >> 3, gl = lane & 7;
+  const uint32_t n = min(*total_jobs, max_jobs);
+  const uint32_t warps = gridDim.x * kWarpsPerBlock;
+  for (uint32_t j0 = (blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5)) * 8u; j0 < n; j0 += warps * 8u) {
+    FetchJob job[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint32_t j = j0 + r * 4 + group;
+      job[r].src = nullptr;
+      if (j < n) job[r] = jobs[j];
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (job[r].src == nullptr) continue;
+      const int nf = job[r].floats;
+      if ((nf & 3) == 0 && ((reinterpret_cast<uintptr_t>(job[r].src) | reinterpret_cast<uintptr_t>(job[r].dst)) & 15u) == 0) {
+        const float4* s4 = reinterpret_cast<const float4*>(job[r].src);
+        float4* d4 = reinterpret_cast<float4*>(job[r].dst);
+        const int nv = nf >> 2;
+        for (int c0 = 0; c0 < nv; c0 += 32) {  // 4 vectors per lane in flight
+          float4 x[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int c = c0 + gl + k * 8;
+            if (c < nv) x[k] = s4[c];
+          }
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int c = c0 + gl + k * 8;
+            if (c < nv) d4[c] = x[k];
+          }
+        }
+      } else {
+        for (int c = gl; c < nf; c += 8) job[r].dst[c] = job[r].src[c];
+      }
+    }
+  }
+}
+
 // Resolves the sorted entry `e` of table `td`: byte-free row offset inside its shard (or -1),
 // gain and shard.
 __device__ __forceinline__ void resolve_entry(const TableDesc& td, const uint32_t* __restrict__ slots, uint32_t e,
@@ -294,6 +425,10 @@ __device__ __forceinline__ void resolve_entry(const TableDesc& td, const uint32_
   *gain = v.gains[q];
   *shard = g;
   *off = (g >= 0 && id >= 0 && (int64_t)id < v.rows_per_shard) ? (int64_t)id * v.dim : -1;
+  if (td.local_shard >= 0 && g >= 0 && g != td.local_shard && *off >= 0) {
+    *shard = -1;  // read the staged copy of the remote row
+    *off = (int64_t)td.run_ord[slots[e]] * v.dim;
+  }
 }
 
 // What a forward warp knows about one of its 32 activation rows.
@@ -339,6 +474,7 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
   const int rows_here = (int)min(32u, total_act - r0);
   int cached_t = -1, dim = 0, vec_per_row = 0;
   float* const* table_ptrs = nullptr;
+  const float* remote_rows = nullptr;
   float* act = nullptr;
   uint32_t act_base = 0;
   for (int j = group; j < rows_here; j += NG) {
@@ -348,6 +484,7 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
       dim = td.v.dim;
       vec_per_row = dim / W;
       table_ptrs = td.table;
+      remote_rows = td.remote_rows;
       act = td.act;
       act_base = td.act_base;
       cached_t = m.table;
@@ -356,7 +493,7 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
 #pragma unroll
     for (int k = 0; k < K; ++k) acc[k] = Vec<W>::zero();
     if (m.off >= 0) {
-      const VT* src = reinterpret_cast<const VT*>(table_ptrs[m.shard] + m.off);
+      const VT* src = reinterpret_cast<const VT*>((m.shard < 0 ? remote_rows : table_ptrs[m.shard]) + m.off);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int c = gl + k * G;
@@ -376,7 +513,7 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
         const float gain = __shfl_sync(gmask, e_gain, i, G);
         const int g = __shfl_sync(gmask, e_shard, i, G);
         if (off < 0) continue;
-        const VT* src = reinterpret_cast<const VT*>(table_ptrs[g] + off);
+        const VT* src = reinterpret_cast<const VT*>((g < 0 ? remote_rows : table_ptrs[g]) + off);
 #pragma unroll
         for (int k = 0; k < K; ++k) {
           const int c = gl + k * G;
@@ -418,11 +555,13 @@ __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g,
 }
 
 __device__ __forceinline__ int entry_count(const TableDesc& td) {
+  if (td.indirect == 2) return td.v.coo;
   return td.indirect ? (int)(td.range[1] - td.range[0]) : min(td.v.row_pointers[0], td.v.coo_per_sc);
 }
 
 __device__ __forceinline__ uint32_t entry_row(const TableDesc& td, int e, int n) {
   if (e < 0 || e >= n) return kNoRow;
+  if (td.indirect == 2) return td.rows[e];
   if (td.indirect) return td.rows[td.range[0] + (uint32_t)e] - td.row_base;  // every listed entry is valid
   const int id = td.v.ids[e];
   return (id >= 0 && (int64_t)id < td.v.rows_per_shard) ? (uint32_t)id : kNoRow;
@@ -694,6 +833,7 @@ constexpr uint32_t kRowIgnore = 4;   // ... but the entry has no gradient row: a
 constexpr uint32_t kRowPartial = 8;  // ... and then store acc as the chunk's partial sum
 constexpr uint32_t kRowHead = 16;    // ... in the slot of a run that started in this chunk
 constexpr uint32_t kRowApply = 32;   // the last of the 1 + NS table / slot rows: apply the optimizer
+constexpr uint32_t kRowReduce = 64;  // reduce-only mode: store acc at red[chunk start + bits 8..12]
 
 __device__ __forceinline__ float fast_axpy(float a, float g, float x) { return __fmaf_rn(g, x, a); }
 
@@ -730,7 +870,7 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
 // flight, and executes the descriptors of a batch as soon as it has landed -- K float4 per lane
 // from shared memory.  The pipeline is as deep for a chunk of 32 single-entry rows as for one
 // long run, and the bytes in flight per warp do not depend on the optimizer.
-template <int K, int NS>
+template <int K, int NS, bool REDUCE>
 __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                              float* __restrict__ partial, uint8_t* __restrict__ chunk_flags,
                                                              int ring_floats) {
@@ -773,7 +913,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   float my_gain = 0.f;
   const float* any_grad = td.grad;  // a readable address for entries without a gradient row
   if (valid) {
-    const int q = td.indirect ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
+    const int q = td.indirect == 1 ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
     if (td.pull != nullptr) {
       const int s = q / td.pull_cap;
       const PullSrc& src = td.pull[s];
@@ -781,7 +921,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
       const int sid = src.sids[slot];
       my_gain = src.gains[slot];
       any_grad = src.grad;
-      if (sid >= 0 && sid < v.bdev) my_src = src.grad + (int64_t)sid * dim;
+      if (sid >= 0 && sid < td.pull_rows) my_src = src.grad + (int64_t)sid * dim;
     } else {
       const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
       const int sid = v.sids[q];
@@ -806,14 +946,16 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
   if (lane == 31)
     chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
-  const int total = __popc(valids) + (1 + NS) * __popc(wendmask);  // rows to stream
+  constexpr int kExtra = REDUCE ? 0 : 1 + NS;  // table and slot rows of an entry that applies the optimizer
+  const int total = __popc(valids) + kExtra * __popc(wendmask);  // rows to stream
   if (valid) {
-    int o = __popc(valids & lt) + (1 + NS) * __popc(wendmask & lt);
+    int o = __popc(valids & lt) + kExtra * __popc(wendmask & lt);
     rowaddr[o] = my_src != nullptr ? my_src : any_grad;
     rowdesc[o] = kRowGrad | (((starts >> lane) & 1u) ? kRowZero : 0u) | (my_src == nullptr ? kRowIgnore : 0u) |
-                 ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u);
+                 ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u) |
+                 ((REDUCE && w_end) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u);
     rowgain[o] = my_gain;
-    if (w_end) {
+    if (!REDUCE && w_end) {
       float *pw, *pa, *pb;
       row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
       rowaddr[++o] = pw;
@@ -866,6 +1008,14 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
           }
         }
       }
+      if (REDUCE && (d & kRowReduce)) {
+        float4* dst = reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((d >> 8) & 31u)) * dim);
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          const int c = lane + k * 32;
+          if (c < vec_per_row) dst[c] = acc[k];
+        }
+      }
       if (d & kRowPartial) {
         float4* dst = reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * dim);
 #pragma unroll
@@ -874,7 +1024,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
           if (c < vec_per_row) dst[c] = acc[k];
         }
       }
-    } else if (d & kRowApply) {
+    } else if (!REDUCE && (d & kRowApply)) {
       // Rows r - NS .. r hold the table row and the slot rows.
       float* pw = const_cast<float*>(rowaddr[r - NS]);
       float* pa = NS >= 1 ? const_cast<float*>(rowaddr[r - NS + (NS >= 1 ? 1 : 0)]) : nullptr;
@@ -988,7 +1138,9 @@ __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const
   const TableDesc& td = tabs[t];
   // The flag says that entry 31 of the chunk exists and holds a valid row.
   const uint32_t e31 = (gchunk - td.chunk_base) * 32u + 31u;
-  const uint32_t row = td.indirect ? td.rows[td.range[0] + e31] - td.row_base : (uint32_t)td.v.ids[e31];
+  const uint32_t row = td.indirect == 2 ? td.rows[e31]
+                       : td.indirect  ? td.rows[td.range[0] + e31] - td.row_base
+                                      : (uint32_t)td.v.ids[e31];
   const int dim = td.v.dim;
   const int vec_per_row = dim / W;
   // The run covers chunk gchunk + 1, every following chunk flagged kChunkAllContinues and the
@@ -1066,6 +1218,17 @@ __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const
       if (c < vec_per_row) Vec<W>::add(acc[k], src[c]);
     }
   }
+  if (td.opt.kind == kReduceOnly) {
+    // The run starts at the first entry of this chunk that holds `row` (entries are ordered by row).
+    const uint32_t same = __ballot_sync(0xffffffffu, td.rows[e31 - 31u + (uint32_t)lane] == row);
+    VT* dst = reinterpret_cast<VT*>(td.red + (int64_t)(e31 - 31u + (uint32_t)(__ffs(same) - 1)) * dim);
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = lane + k * 32;
+      if (c < vec_per_row) dst[c] = acc[k];
+    }
+    return;
+  }
   {
     const RowCtx ctx = make_ctx(td);
     VT w[K], x0[K], x1[K];
@@ -1122,6 +1285,43 @@ __global__ void bwd_ranges_kernel(const TableDesc* __restrict__ tabs, int count,
     if (keys[mid] < target) lo = mid + 1; else hi = mid;
   }
   ranges[t] = lo;
+}
+
+// Reduce-only staging, step 1.  keys[slot] = shard * rows_per_shard + id for slots that hold an
+// entry, kNoRow for alignment padding and the unwritten tail.
+__global__ void stage_keys_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+                                  uint32_t* __restrict__ keys) {
+  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= total_slots) return;
+  const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
+  const CsrView& v = tabs[t].v;
+  const int q = (int)(gq - tabs[t].slot_base);
+  const int g = slot_shard(v, 0, q);
+  uint32_t key = kNoRow;
+  if (g >= 0) {
+    const int id = v.ids[q];
+    if (id >= 0 && (int64_t)id < v.rows_per_shard) key = (uint32_t)((int64_t)g * v.rows_per_shard + id);
+  }
+  keys[gq] = key;
+}
+
+// Reduce-only staging, step 2.  Writes the CSR buffers that the owners of the shards will read:
+// one entry per run (at the run's first slot, gain 1, sample id = the slot, i.e. the row of the
+// reduced-gradient buffer), padding everywhere else; row pointers are copied.
+__global__ void stage_meta_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+                                  const uint32_t* __restrict__ keys, const PullSrc* __restrict__ outs) {
+  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= total_slots) return;
+  const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
+  const TableDesc& td = tabs[t];
+  const int q = (int)(gq - td.slot_base);
+  const PullSrc& out = outs[t];
+  const uint32_t key = keys[gq];
+  const bool head = key != kNoRow && (q == 0 || keys[gq - 1] != key);
+  const_cast<int32_t*>(out.ids)[q] = head ? td.v.ids[q] : INT_MAX;
+  const_cast<int32_t*>(out.sids)[q] = head ? q : INT_MAX;
+  const_cast<float*>(out.gains)[q] = head ? 1.0f : nanf("");
+  if (q < td.v.R) const_cast<int32_t*>(out.row_pointers)[q] = td.v.row_pointers[q];
 }
 
 // ------------------------------------------------------------------------ host side
@@ -1242,16 +1442,16 @@ int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const 
   return SC_OK;
 }
 
-template <int K, int NS>
+template <int K, int NS, bool REDUCE = false>
 int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int max_dim,
                    cudaStream_t st) {
   const int ring_floats = pipe_ring_rows(K, NS) * max_dim;
   const size_t smem = (size_t)kPipeWarps * ((size_t)ring_floats * 4 + pipe_list_bytes(K, NS));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   (int)cudaSharedmemCarveoutMaxShared));
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
-  bwd_pipe_kernel<K, NS><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats);
+  bwd_pipe_kernel<K, NS, REDUCE><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats);
   SC_LAUNCH_OK("bwd_pipe_kernel");
   return SC_OK;
 }
@@ -1261,7 +1461,8 @@ template <int K32>
 int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
                     int max_dim, cudaStream_t st) {
   int rc;
-  if (num_slots == 0) rc = launch_pipe_ns<K32, 0>(tabs, count, total_chunks, u, max_dim, st);
+  if (num_slots == kReduceOnly) rc = launch_pipe_ns<K32, 0, true>(tabs, count, total_chunks, u, max_dim, st);
+  else if (num_slots == 0) rc = launch_pipe_ns<K32, 0>(tabs, count, total_chunks, u, max_dim, st);
   else if (num_slots == 1) rc = launch_pipe_ns<K32, 1>(tabs, count, total_chunks, u, max_dim, st);
   else rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, u, max_dim, st);
   if (rc != SC_OK) return rc;
@@ -1278,6 +1479,10 @@ inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_ch
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline bool pipe_enabled();
+// A pull item exchanges reduced runs (one gradient row per distinct table row and source) when its
+// rows can go through the 16-byte asynchronous copies; otherwise the raw entries and gradients.
+inline bool exchanges_reduced_runs(const CsrView& v) { return v.dim % 4 == 0 && pipe_enabled(); }
 
 // The cp.async pipeline is the default; SC_BWD_KERNEL=groups selects the register-only kernel.
 inline bool pipe_enabled() {
@@ -1323,6 +1528,7 @@ int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, const Up
 struct FwdPlan {
   std::vector<CsrView> views;
   uint64_t total_slots = 0, total_act = 0;
+  uint64_t remote_floats = 0;  // staging space for rows of remote shards (tables with local_shard >= 0)
   int total_shards = 0;
   int w = 0, k = 0, g = 0;
 };
@@ -1341,6 +1547,8 @@ int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
     p->total_slots += (uint64_t)p->views[i].coo;
     p->total_act += (uint64_t)p->views[i].bdev;
     p->total_shards += p->views[i].P;
+    if (items[i].local_shard >= p->views[i].P) SC_FAIL(SC_INVALID_ARGUMENT, "local_shard %d out of range", items[i].local_shard);
+    if (items[i].local_shard >= 0 && p->views[i].P > 1) p->remote_floats += (uint64_t)p->views[i].coo * (uint64_t)p->views[i].dim;
   }
   if (p->total_slots >= 0xffffffffull || p->total_act >= 0xffffffffull) SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
   return SC_OK;
@@ -1355,6 +1563,10 @@ struct FwdScratch {
   uint32_t* offsets;    // [act + 2] counts, then their exclusive scan; the last word counts the long rows
   uint32_t* scan_temp;
   uint32_t* big_rows;   // [slots / kSerialSortLimit + 1]
+  uint32_t* run_ord;    // [slots] index of a remote slot's row in remote_rows (remote shards only)
+  uint32_t* heads_temp; // scan scratch of the run heads, then one word: number of runs
+  FetchJob* fetch_jobs; // [slots]
+  float* remote_rows;
 };
 
 bool carve_fwd(Workspace& ws, const FwdPlan& p, int count, FwdScratch* s) {
@@ -1367,6 +1579,10 @@ bool carve_fwd(Workspace& ws, const FwdPlan& p, int count, FwdScratch* s) {
   s->offsets = ws.take<uint32_t>(act + 2);
   s->scan_temp = ws.take<uint32_t>(scan_temp_elems(act + 1));
   s->big_rows = ws.take<uint32_t>(slots / kSerialSortLimit + 1);
+  s->run_ord = ws.take<uint32_t>(p.remote_floats ? slots : 0);
+  s->heads_temp = ws.take<uint32_t>(p.remote_floats ? scan_temp_elems(slots) + 1 : 0);
+  s->fetch_jobs = ws.take<FetchJob>(p.remote_floats ? slots : 0);
+  s->remote_rows = ws.take<float>((size_t)p.remote_floats);
   return ws.ok();
 }
 
@@ -1485,6 +1701,7 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   GroupImage img;
   std::vector<int> pool_index;
   uint32_t slot_base = 0, act_base = 0;
+  size_t remote_base = 0;
   for (int i = 0; i < count; ++i) {
     if (!items[i].shard_tables || !items[i].activations) SC_FAIL(SC_INVALID_ARGUMENT, "null table or activation pointer");
     TableDesc td;
@@ -1492,6 +1709,12 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
     td.v = p.views[i];
     td.act = items[i].activations;
     td.slot_base = slot_base; td.act_base = act_base;
+    td.local_shard = (items[i].local_shard >= 0 && td.v.P > 1) ? items[i].local_shard : -1;
+    if (td.local_shard >= 0) {
+      td.run_ord = s.run_ord;
+      td.remote_rows = s.remote_rows + remote_base;
+      remote_base += (size_t)td.v.coo * (size_t)td.v.dim;
+    }
     slot_base += (uint32_t)td.v.coo; act_base += (uint32_t)td.v.bdev;
     pool_index.push_back((int)img.pool.size()); pool_index.push_back(-1); pool_index.push_back(-1);
     for (int g = 0; g < td.v.P; ++g) {
@@ -1504,6 +1727,19 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
   const uint32_t total_slots = (uint32_t)p.total_slots, total_act = (uint32_t)p.total_act;
 
+  if (p.remote_floats > 0) {
+    // Rows of remote shards: fetch each distinct row once, then gather from the local copies.
+    // s.keys / s.scan_temp are free until the plan below is built (the scan needs no more than slots words).
+    fwd_remote_heads_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, cs>>>(tabs, count, total_slots, s.keys);
+    SC_LAUNCH_OK("fwd_remote_heads_kernel");
+    uint32_t* total_jobs = s.heads_temp + scan_temp_elems((size_t)total_slots);
+    SC_CUDA_OK(exclusive_scan<uint32_t>(s.keys, s.keys, (size_t)total_slots, s.heads_temp, total_jobs, cs));
+    fwd_fetch_plan_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, cs>>>(tabs, count, total_slots, s.keys, s.run_ord,
+                                                                                     s.fetch_jobs);
+    SC_LAUNCH_OK("fwd_fetch_plan_kernel");
+    fwd_fetch_kernel<<<(unsigned)sm_count() * 8, kBlock, 0, cs>>>(s.fetch_jobs, total_jobs, total_slots);
+    SC_LAUNCH_OK("fwd_fetch_kernel");
+  }
   uint32_t* big_count = s.offsets + total_act + 1;
   SC_CUDA_OK(cudaMemsetAsync(s.offsets, 0, ((size_t)total_act + 2) * sizeof(uint32_t), cs));
   const unsigned slot_blocks = (unsigned)ceil_div(total_slots, kBlock);
@@ -1577,6 +1813,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
       td.pull_cap = items[i].partition_capacity;
       td.pull_shard = items[i].shard;
       td.num_sources = items[i].num_sources;
+      td.pull_rows = exchanges_reduced_runs(td.v) ? td.v.coo : td.v.bdev;
       for (int sidx = 0; sidx < items[i].num_sources; ++sidx) {
         const sc_pull_source_t& src = items[i].sources[sidx];
         pull_host.push_back(PullSrc{src.row_pointers, src.embedding_ids, src.sample_ids, src.gains, src.activation_grad});
@@ -1655,42 +1892,151 @@ __global__ void stage_copy_kernel(const CopyJob* __restrict__ jobs) {
   }
 }
 
-// Copies this device's CSR buffers and activation gradients of every pull-mode item into the
-// device's own peer-visible exchange buffers (sources[shard]) with ONE kernel launch; buffers
-// that already live there (same address) are skipped.  `workspace` holds the job list
-// (sc_sparse_dense_matmul_grad_grouped_workspace_bytes covers it).  The caller separates this
-// call from the update with a barrier across the devices.
-extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, void* workspace,
-                                                     size_t workspace_bytes, sc_stream_t stream) {
+struct StagePlan {
+  std::vector<CsrView> views;
+  std::vector<int> reduced;  // per item
+  uint64_t slots = 0, chunks = 0;
+  int reduced_count = 0, max_dim = 0;
+  size_t copy_jobs = 0;
+};
+
+int plan_stage(const sc_grad_item_t* items, int count, StagePlan* p) {
   if (!items || count <= 0) SC_FAIL(SC_INVALID_ARGUMENT, "empty backward group");
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
-  std::vector<CopyJob> jobs;
+  p->views.resize(count);
+  p->reduced.assign(count, 0);
   for (int i = 0; i < count; ++i) {
     const sc_grad_item_t& it = items[i];
     if (!it.sources) continue;
-    CsrView v;
-    int st = make_view(&it.csr, &v);
+    int st = make_view(&it.csr, &p->views[i]);
     if (st != SC_OK) return st;
+    const CsrView& v = p->views[i];
     if (it.shard < 0 || it.shard >= it.num_sources || !it.activation_grad) SC_FAIL(SC_INVALID_ARGUMENT, "bad pull item");
-    const sc_pull_source_t& own = it.sources[it.shard];
-    const void* srcs[5] = {v.row_pointers, v.ids, v.sids, v.gains, it.activation_grad};
-    const void* dsts[5] = {own.row_pointers, own.embedding_ids, own.sample_ids, own.gains, own.activation_grad};
-    const uint64_t words[5] = {(uint64_t)v.R * v.S, (uint64_t)v.coo, (uint64_t)v.coo, (uint64_t)v.coo,
-                               (uint64_t)v.bdev * v.dim};
-    for (int a = 0; a < 5; ++a) {
-      if (srcs[a] == dsts[a] || words[a] == 0) continue;
-      jobs.push_back(CopyJob{static_cast<const uint32_t*>(srcs[a]),
-                             const_cast<uint32_t*>(static_cast<const uint32_t*>(dsts[a])), words[a]});
+    if (v.S != 1) SC_FAIL(SC_UNSUPPORTED, "pull mode needs one SparseCore per device");
+    if (exchanges_reduced_runs(v)) {
+      p->reduced[i] = 1;
+      p->reduced_count += 1;
+      p->slots += (uint64_t)v.coo;
+      p->chunks += (uint64_t)ceil_div(v.coo, 32);
+      p->max_dim = v.dim > p->max_dim ? v.dim : p->max_dim;
+    } else {
+      p->copy_jobs += 5;
     }
   }
-  if (jobs.empty()) return SC_OK;
-  const size_t bytes = jobs.size() * sizeof(CopyJob);
-  if (!workspace || workspace_bytes < bytes) SC_FAIL(SC_WORKSPACE_TOO_SMALL, "staging needs %zu workspace bytes", bytes);
-  SC_CUDA_OK(cudaMemcpyAsync(workspace, jobs.data(), bytes, cudaMemcpyHostToDevice, cs));
-  dim3 grid(32, (unsigned)jobs.size());
-  stage_copy_kernel<<<grid, kBlock, 0, cs>>>(static_cast<const CopyJob*>(workspace));
-  SC_LAUNCH_OK("stage_copy_kernel");
+  if (p->slots >= 0xffffffffull || p->chunks >= 0x7fffffffull) SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
   return SC_OK;
+}
+
+struct StageScratch {
+  CopyJob* jobs;
+  char* image;
+  PullSrc* outs;
+  uint32_t* keys;
+  UpdateScratch update;
+};
+
+bool carve_stage(Workspace& ws, const StagePlan& p, StageScratch* s) {
+  s->jobs = ws.take<CopyJob>(p.copy_jobs + 1);
+  s->image = ws.take<char>(image_bytes(p.reduced_count + 1, p.reduced_count + 1));
+  s->outs = ws.take<PullSrc>((size_t)p.reduced_count + 1);
+  s->keys = ws.take<uint32_t>((size_t)p.slots + 1);
+  s->update.partial = ws.take<float>((size_t)2 * (size_t)p.chunks * (size_t)p.max_dim + 1);
+  s->update.flags = ws.take<uint8_t>((size_t)p.chunks + 1);
+  s->update.group_partial = ws.take<float>(update_groups(p.chunks) * (size_t)p.max_dim + 1);
+  s->update.group_flags = ws.take<uint8_t>(update_groups(p.chunks) + 1);
+  return ws.ok();
+}
+
+extern "C" size_t sc_sparse_dense_matmul_grad_stage_workspace_bytes(const sc_grad_item_t* items, int32_t count) {
+  StagePlan p;
+  if (plan_stage(items, count, &p) != SC_OK) return 0;
+  Workspace ws(nullptr, 0);
+  StageScratch s;
+  carve_stage(ws, p, &s);
+  return ws.used();
+}
+
+// Pull mode, before the barrier: publishes what this device holds for every shard in its own
+// peer-visible exchange buffers (sources[shard]).  Items whose rows allow it publish reduced runs:
+// the gradient rows of all entries of one (shard, row) run are summed here, in slot order, into
+// activation_grad[first slot of the run] of the exchange buffers (which must hold coo_buffer_size
+// rows), and the exchanged CSR lists one entry per run.  A row that many samples of the batch hit
+// then crosses NVLink once per source instead of once per sample.  Other items copy their CSR
+// buffers and activation gradients unchanged.
+extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items, int32_t count, void* workspace,
+                                                     size_t workspace_bytes, sc_stream_t stream) {
+  StagePlan p;
+  int st = plan_stage(items, count, &p);
+  if (st != SC_OK) return st;
+  Workspace ws(workspace, workspace_bytes);
+  StageScratch s;
+  if (!carve_stage(ws, p, &s)) SC_FAIL(SC_WORKSPACE_TOO_SMALL, "staging needs %zu workspace bytes, got %zu", ws.used(), workspace_bytes);
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+
+  std::vector<CopyJob> jobs;
+  GroupImage img;
+  std::vector<int> pool_index;
+  std::vector<PullSrc> outs;
+  uint32_t slot_base = 0, chunk_base = 0;
+  for (int i = 0; i < count; ++i) {
+    const sc_grad_item_t& it = items[i];
+    if (!it.sources) continue;
+    const CsrView& v = p.views[i];
+    const sc_pull_source_t& own = it.sources[it.shard];
+    if (!own.row_pointers || !own.embedding_ids || !own.sample_ids || !own.gains || !own.activation_grad)
+      SC_FAIL(SC_INVALID_ARGUMENT, "this device's exchange buffers are missing");
+    if (!p.reduced[i]) {
+      const void* srcs[5] = {v.row_pointers, v.ids, v.sids, v.gains, it.activation_grad};
+      const void* dsts[5] = {own.row_pointers, own.embedding_ids, own.sample_ids, own.gains, own.activation_grad};
+      const uint64_t words[5] = {(uint64_t)v.R * v.S, (uint64_t)v.coo, (uint64_t)v.coo, (uint64_t)v.coo,
+                                 (uint64_t)v.bdev * v.dim};
+      for (int a = 0; a < 5; ++a) {
+        if (srcs[a] == dsts[a] || words[a] == 0) continue;
+        jobs.push_back(CopyJob{static_cast<const uint32_t*>(srcs[a]),
+                               const_cast<uint32_t*>(static_cast<const uint32_t*>(dsts[a])), words[a]});
+      }
+      continue;
+    }
+    if (!aligned16(it.activation_grad) || !aligned16(own.activation_grad))
+      SC_FAIL(SC_UNSUPPORTED, "activation gradients of a row-sharded table must be 16-byte aligned");
+    if (own.embedding_ids == v.ids || own.sample_ids == v.sids || own.gains == v.gains || own.activation_grad == it.activation_grad)
+      SC_FAIL(SC_INVALID_ARGUMENT, "the exchange buffers must not alias the CSR operands or the activation gradients");
+    TableDesc td;
+    memset(&td, 0, sizeof td);
+    td.v = v;
+    td.grad = it.activation_grad;
+    td.opt.kind = kReduceOnly;
+    td.opt.lo = td.opt.hi = nanf("");
+    td.indirect = 2;
+    td.rows = s.keys + slot_base;
+    td.red = const_cast<float*>(own.activation_grad);
+    td.slot_base = slot_base;
+    td.chunk_base = chunk_base;
+    td.local_shard = -1;
+    slot_base += (uint32_t)v.coo;
+    chunk_base += (uint32_t)ceil_div(v.coo, 32);
+    pool_index.push_back((int)img.pool.size()); pool_index.push_back(-1); pool_index.push_back(-1);
+    img.pool.push_back(td.red);  // make_ctx reads table[0]; never dereferenced in this mode
+    img.tabs.push_back(td);
+    outs.push_back(PullSrc{own.row_pointers, own.embedding_ids, own.sample_ids, own.gains, own.activation_grad});
+  }
+  if (!jobs.empty()) {
+    SC_CUDA_OK(cudaMemcpyAsync(s.jobs, jobs.data(), jobs.size() * sizeof(CopyJob), cudaMemcpyHostToDevice, cs));
+    dim3 grid(32, (unsigned)jobs.size());
+    stage_copy_kernel<<<grid, kBlock, 0, cs>>>(s.jobs);
+    SC_LAUNCH_OK("stage_copy_kernel");
+  }
+  if (img.tabs.empty()) return SC_OK;
+  const int n = (int)img.tabs.size();
+  SC_CUDA_OK(cudaMemcpyAsync(s.outs, outs.data(), outs.size() * sizeof(PullSrc), cudaMemcpyHostToDevice, cs));
+  SC_CUDA_OK(upload(img, s.image, pool_index, cs));
+  const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
+  const uint32_t total_slots = (uint32_t)p.slots;
+  const unsigned slot_blocks = (unsigned)ceil_div(total_slots, kBlock);
+  stage_keys_kernel<<<slot_blocks, kBlock, 0, cs>>>(tabs, n, total_slots, s.keys);
+  SC_LAUNCH_OK("stage_keys_kernel");
+  stage_meta_kernel<<<slot_blocks, kBlock, 0, cs>>>(tabs, n, total_slots, s.keys, s.outs);
+  SC_LAUNCH_OK("stage_meta_kernel");
+  return dispatch_bwd_pipe(tabs, n, (uint32_t)p.chunks, s.update, kReduceOnly, p.max_dim, cs);
 }
 
 // ---- single-table entry points: groups of one ---------------------------------------------
@@ -1699,14 +2045,14 @@ extern "C" size_t sc_sparse_dense_matmul_fwd_workspace_bytes(const sc_csr_t* csr
   if (!csr) return 0;
   float* dummy_ptrs[SC_MAX_SHARDS];
   for (int i = 0; i < SC_MAX_SHARDS; ++i) dummy_ptrs[i] = reinterpret_cast<float*>(256);
-  sc_fwd_item_t item = {*csr, dummy_ptrs, reinterpret_cast<float*>(256)};
+  sc_fwd_item_t item = {*csr, dummy_ptrs, reinterpret_cast<float*>(256), -1};
   return sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(&item, 1);
 }
 
 extern "C" int32_t sc_sparse_dense_matmul_fwd(const sc_csr_t* csr, const float* const* shard_tables, float* activations,
                                               void* workspace, size_t workspace_bytes, sc_stream_t stream) {
   if (!csr) SC_FAIL(SC_INVALID_ARGUMENT, "csr descriptor is null");
-  sc_fwd_item_t item = {*csr, shard_tables, activations};
+  sc_fwd_item_t item = {*csr, shard_tables, activations, -1};
   return sc_sparse_dense_matmul_fwd_grouped(&item, 1, workspace, workspace_bytes, stream);
 }
 

@@ -58,7 +58,7 @@ class Optimizer(ctypes.Structure):
 
 
 class FwdItem(ctypes.Structure):
-  _fields_ = [("csr", Csr), ("shard_tables", ctypes.POINTER(c_vp)), ("activations", c_vp)]
+  _fields_ = [("csr", Csr), ("shard_tables", ctypes.POINTER(c_vp)), ("activations", c_vp), ("local_shard", ctypes.c_int32)]
 
 
 class PullSource(ctypes.Structure):
@@ -134,6 +134,8 @@ def lib() -> ctypes.CDLL:
     l.sc_sparse_dense_matmul_grad_grouped_workspace_bytes.argtypes = [ctypes.POINTER(GradItem), c_i32]
     l.sc_sparse_dense_matmul_grad_grouped.restype = c_i32
     l.sc_sparse_dense_matmul_grad_grouped.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
+    l.sc_sparse_dense_matmul_grad_stage_workspace_bytes.restype = c_sz
+    l.sc_sparse_dense_matmul_grad_stage_workspace_bytes.argtypes = [ctypes.POINTER(GradItem), c_i32]
     l.sc_sparse_dense_matmul_grad_stage.restype = c_i32
     l.sc_sparse_dense_matmul_grad_stage.argtypes = [ctypes.POINTER(GradItem), c_i32, c_vp, c_sz, c_vp]
     l.sc_peer_alloc.restype = c_i32

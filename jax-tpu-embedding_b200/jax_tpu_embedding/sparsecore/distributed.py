@@ -144,13 +144,17 @@ def stream_barrier() -> None:
 
 
 def exchange_buffers(key, rp_size: int, coo: int, batch: int, dim: int):
-  """Peer-visible staging buffers of one stacked table (allocated collectively on first use)."""
+  """Peer-visible staging buffers of one stacked table (allocated collectively on first use).
+
+  `grad` holds max(batch, coo) rows: one reduced gradient row per slot when the sources exchange
+  reduced runs, the plain activation gradients otherwise.
+  """
   torch = _native.torch_mod()
   full_key = (key, rp_size, coo, batch, dim)
   buf = _ctx.exchange.get(full_key)
   if buf is None:
     buf = dict(rp=alloc((rp_size,), torch.int32), ids=alloc((coo,), torch.int32), sids=alloc((coo,), torch.int32),
-               gains=alloc((coo,), torch.float32), grad=alloc((batch, dim), torch.float32))
+               gains=alloc((coo,), torch.float32), grad=alloc((max(batch, coo), dim), torch.float32))
     buf["sources"] = (_native.PullSource * _ctx.world)()
     ptrs = {k: peer_pointers(buf[k]) for k in ("rp", "ids", "sids", "gains", "grad")}
     for r in range(_ctx.world):
@@ -158,14 +162,3 @@ def exchange_buffers(key, rp_size: int, coo: int, batch: int, dim: int):
                                              ptrs["grad"][r])
     _ctx.exchange[full_key] = buf
   return buf
-
-
-def gradient_buffer(exchange_key: str, rp_size: int, coo: int, batch: int, dim: int):
-  """The peer-visible [batch, dim] buffer the backward reads activation gradients from.
-
-  A model that writes its activation gradients of a stacked table directly into this tensor and
-  passes it to `tpu_sparse_dense_matmul_grad(..., perform_stacking=False)` saves the staging copy
-  of the gradients (batch * dim * 8 bytes of HBM traffic per step).  `exchange_key` is
-  "<optimizer short name>-<stack name><label>", the name of the update computation.
-  """
-  return exchange_buffers(exchange_key, rp_size, coo, batch, dim)["grad"]

@@ -148,6 +148,11 @@ class ForwardRequest:
     self.act = torch.empty(out_shape, dtype=torch.float32, device=self.table.device)
     self.csr = self.geo.csr(self.rp, self.ids, self.sids, self.gains, max_ids_per_sample)
     self.ptrs = self.geo.shard_pointers(self.table)
+    self.local_shard = -1
+    if self.geo.l != self.geo.c:  # one process per GPU: the other shards are peer mappings
+      from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
+
+      self.local_shard = distributed.rank() * self.geo.s_eff
 
 
 class ForwardGroupCall:
@@ -171,6 +176,7 @@ class ForwardGroupCall:
         items[j].csr = r.csr
         items[j].shard_tables = r.ptrs
         items[j].activations = r.act.data_ptr()
+        items[j].local_shard = r.local_shard
       nbytes = lib.sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(items, len(idxs))
       if nbytes == 0:
         _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), None, 0, None))
@@ -294,6 +300,11 @@ class GradGroupCall:
       nbytes = lib.sc_sparse_dense_matmul_grad_grouped_workspace_bytes(items, len(idxs))
       if nbytes == 0:
         _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), None, 0, None))
+      if any(requests[i].pull is not None for i in idxs):
+        stage_bytes = lib.sc_sparse_dense_matmul_grad_stage_workspace_bytes(items, len(idxs))
+        if stage_bytes == 0:
+          _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), None, 0, None))
+        nbytes = max(nbytes, stage_bytes)
       self.groups.append((items, idxs, nbytes))
     self.keep = [(r.t_ptrs, r.s_ptrs, r.pull) for r in requests]
     self.sharded = any(r.pull is not None for r in requests)
