@@ -148,7 +148,7 @@ class ClockSampler:
   def start(self):
     try:
       self.proc = subprocess.Popen(
-          ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+          ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
            "-i", str(self.device_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
     except OSError:
       self.proc = None
@@ -192,19 +192,23 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
-def table_stats(pre, specs, name, world=1):
-  """nnz (entries after dedup) and unique rows of one stacked table, from the CSR on device."""
+def table_stats(pre, specs, name, world=1, rank=0):
+  """nnz (entries after dedup), unique rows, and unique rows of the other ranks' shards, of one
+  stacked table, from this rank's CSR on device."""
   import torch
 
   rp = pre.lhs_row_pointers[name].cpu().numpy()
   ids = pre.lhs_embedding_ids[name]
-  n = u = 0
+  n = u = remote = 0
   for g in range(world):
     begin = 0 if g == 0 else (int(rp[g - 1]) + 7) // 8 * 8
     end = int(rp[g])
     n += end - begin
-    u += int(torch.unique_consecutive(ids[begin:end]).numel())
-  return n, u
+    ug = int(torch.unique_consecutive(ids[begin:end]).numel())
+    u += ug
+    if g != rank:
+      remote += ug
+  return n, u, remote
 
 
 # --------------------------------------------------------------------------------- CPU arm
@@ -301,8 +305,8 @@ def cpu_arm(wl, specs, feats, weights, steps=1, warmup=0, threads=None):
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=20)
-  ap.add_argument("--warmup", type=int, default=5)
+  ap.add_argument("--steps", type=int, default=100)
+  ap.add_argument("--warmup", type=int, default=10)
   ap.add_argument("--workload", default="c2")
   ap.add_argument("--scale", type=float, default=1.0, help="scales vocabulary sizes (profiling only)")
   ap.add_argument("--impl", default="b200")
@@ -323,7 +327,7 @@ def main():
       return
     specs = build_specs(wl)
     feats, weights = build_inputs(wl, specs)
-    r = cpu_arm(wl, specs, feats, weights, steps=max(1, min(args.steps, 3)), warmup=min(args.warmup, 1))
+    r = cpu_arm(wl, specs, feats, weights, steps=max(1, args.steps), warmup=max(0, args.warmup))
     line = {"impl": "reference", "metric": "samples/s fwd+Adagrad bwd", "value": r["samples_per_s"], "unit": "samples/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -386,11 +390,26 @@ def main():
       torch.distributed.barrier()
     torch.cuda.synchronize()
 
-  for _ in range(max(args.warmup, 3)):
-    lookup_update()
-  barrier()
+  # The clock sampler runs from the warm-up to the end of the timed region (the GPU is under the same
+  # load throughout); the warm-up lasts at least `--warmup` steps and long enough for several samples.
   sampler = ClockSampler(local_rank)
   sampler.start()
+  warm_steps = max(args.warmup, 3)
+  for _ in range(warm_steps):
+    lookup_update()
+  torch.cuda.synchronize()
+  t_warm = time.time()
+  flag = torch.zeros(1, device="cuda")
+  while True:
+    for _ in range(20):
+      lookup_update()
+    torch.cuda.synchronize()
+    flag.fill_(1.0 if time.time() - t_warm < 0.4 else 0.0)
+    if world > 1:  # all ranks leave the loop together
+      torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MAX)
+    if float(flag.item()) == 0.0:
+      break
+  barrier()
   ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   if args.profile_range:
     torch.cuda.profiler.start()
@@ -413,13 +432,14 @@ def main():
   nnz_in = sum(int(np.prod(f.shape)) if isinstance(f, np.ndarray) else len(f.values) for f in feats)
 
   # ---- roofline of the fused backward (dominant kernel): CUDA events around its launches only.
-  algo_bytes, bwd_ms = 0, 0.0
+  algo_bytes, bwd_ms, remote_row_bytes = 0, 0.0, 0
   per = {}
   for name, spec in stacked.items():
-    n, u = table_stats(pre, specs, name, world)
+    n, u, remote = table_stats(pre, specs, name, world, rank)
     d, bdev = spec.stack_embedding_dim, spec.total_sample_count // world
     slots = spec.optimizer.slot_variables_count()
     per[name] = (n, u)
+    remote_row_bytes += remote * 4 * d
     algo_bytes += bdev * 4 * d + n * 12 + 8 * 4 + u * 4 * d * (1 + slots) * 2
   stacked_grads = embedding.stack_embedding_gradients(grads, specs, 1, world)
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -467,9 +487,18 @@ def main():
     else:
       pinned_w = None
 
+    # Dense id matrices travel as ONE pinned buffer and one copy per step; the features are views of it.
+    dense_all = None
+    if all(isinstance(p, torch.Tensor) for p in pinned) and pinned_w is None:
+      shapes = [tuple(p.shape) for p in pinned]
+      sizes = [p.numel() for p in pinned]
+      dense_all = torch.cat([p.reshape(-1) for p in pinned]).pin_memory()
+
     def e2e_step():
       dev_feats = []
-      for p in pinned:
+      if dense_all is not None:
+        dev_feats = [v.view(shape) for v, shape in zip(dense_all.cuda(non_blocking=True).split(sizes), shapes)]
+      for p in ([] if dense_all is not None else pinned):
         if isinstance(p, torch.Tensor):
           dev_feats.append(p.cuda(non_blocking=True))
         else:
@@ -501,7 +530,7 @@ def main():
 
   cpu = None
   if rank == 0 and world == 1 and not args.no_cpu_baseline:
-    r = cpu_arm(wl, specs, feats, weights, steps=1, warmup=0)
+    r = cpu_arm(wl, specs, feats, weights, steps=3, warmup=1)
     cpu = {"value": r["samples_per_s"], "unit": "samples/s", "cores": r["cores"], "kind": "port",
            "sample": f"1 step of the full batch, tables compacted to touched rows ({r['ms_per_step']:.0f} ms, of which "
                      f"C preprocessing {r['preprocess_ms']:.0f} ms)"}
@@ -520,11 +549,13 @@ def main():
                                  "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9,
                                  "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak}},
         "nvlink": None if world == 1 else {
-            "forward_bytes_per_gpu": int(nnz_in * (world - 1) / world * 4 * wl["tables"][0]["dim"]),
-            "backward_bytes_per_gpu": int(nnz_in * (world - 1) / world * (4 * wl["tables"][0]["dim"] + 12)),
-            "bound_ms": nnz_in * (world - 1) / world * (8 * wl["tables"][0]["dim"] + 12) / 770e9 * 1e3,
-            "note": "remote rows (forward) and remote gradient rows + entries (backward) at the measured 770 GB/s "
-                    "per direction; the step cannot be faster than max(HBM time, this)"},
+            "forward_bytes_per_gpu": int(remote_row_bytes),
+            "backward_bytes_per_gpu": int(remote_row_bytes),
+            "bound_ms": 2 * remote_row_bytes / 770e9 * 1e3,
+            "undeduplicated_bytes_per_gpu": int(nnz_in * (world - 1) / world * 4 * wl["tables"][0]["dim"]),
+            "note": "rank 0: one table row (forward) and one reduced gradient row (backward) per DISTINCT remote row "
+                    "of the batch, at the measured 770 GB/s per direction; the step cannot be faster than "
+                    "max(HBM time, this)"},
         "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
         "gpu_launches": gpu_launches,
         "table_bytes": int(table_bytes),

@@ -370,44 +370,45 @@ __global__ void fwd_fetch_plan_kernel(const TableDesc* __restrict__ tabs, int co
   }
 }
 
-// Copies the rows of the fetch jobs: 8 lanes per row, every lane issues all its loads before its
-// first store, a warp takes 8 consecutive jobs.  total_jobs lives in device memory (the scan's total).
+// Copies the rows of the fetch jobs.  A warp takes 8 consecutive jobs; the whole warp reads one
+// row with 16 bytes per lane (one 512-byte request for a 128-float row) and issues the loads of
+// all 8 rows before its first store.  total_jobs lives in device memory (the scan's total).
 __global__ void __launch_bounds__(kBlock) fwd_fetch_kernel(const FetchJob* __restrict__ jobs, const uint32_t* __restrict__ total_jobs,
                                                            uint32_t max_jobs) {
-  const int lane = threadIdx.x & 31, group = lane >> 3, gl = lane & 7;
+  constexpr int kRows = 8;
+  const int lane = threadIdx.x & 31;
   const uint32_t n = min(*total_jobs, max_jobs);
   const uint32_t warps = gridDim.x * kWarpsPerBlock;
-  for (uint32_t j0 = (blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5)) * 8u; j0 < n; j0 += warps * 8u) {
-    FetchJob job[2];
+  for (uint32_t j0 = (blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5)) * kRows; j0 < n; j0 += warps * kRows) {
+    // Lane r < kRows reads job j0 + r; the fields are then broadcast.
+    FetchJob mine;
+    mine.src = nullptr; mine.dst = nullptr; mine.floats = 0; mine.pad = 0;
+    if (lane < kRows && j0 + lane < n) mine = jobs[j0 + lane];
+    const bool fast = __all_sync(0xffffffffu, mine.src == nullptr ||
+                                                  ((mine.floats & 3) == 0 && mine.floats <= 128 &&
+                                                   ((reinterpret_cast<uintptr_t>(mine.src) | reinterpret_cast<uintptr_t>(mine.dst)) & 15u) == 0));
+    if (fast) {
+      float4 x[kRows];
+      bool on[kRows];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const uint32_t j = j0 + r * 4 + group;
-      job[r].src = nullptr;
-      if (j < n) job[r] = jobs[j];
-    }
+      for (int r = 0; r < kRows; ++r) {
+        const float4* s4 = reinterpret_cast<const float4*>(__shfl_sync(0xffffffffu, (unsigned long long)mine.src, r));
+        const int nv = __shfl_sync(0xffffffffu, mine.floats, r) >> 2;
+        on[r] = s4 != nullptr && lane < nv;
+        if (on[r]) x[r] = s4[lane];
+      }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      if (job[r].src == nullptr) continue;
-      const int nf = job[r].floats;
-      if ((nf & 3) == 0 && ((reinterpret_cast<uintptr_t>(job[r].src) | reinterpret_cast<uintptr_t>(job[r].dst)) & 15u) == 0) {
-        const float4* s4 = reinterpret_cast<const float4*>(job[r].src);
-        float4* d4 = reinterpret_cast<float4*>(job[r].dst);
-        const int nv = nf >> 2;
-        for (int c0 = 0; c0 < nv; c0 += 32) {  // 4 vectors per lane in flight
-          float4 x[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int c = c0 + gl + k * 8;
-            if (c < nv) x[k] = s4[c];
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int c = c0 + gl + k * 8;
-            if (c < nv) d4[c] = x[k];
-          }
-        }
-      } else {
-        for (int c = gl; c < nf; c += 8) job[r].dst[c] = job[r].src[c];
+      for (int r = 0; r < kRows; ++r) {
+        float4* d4 = reinterpret_cast<float4*>(__shfl_sync(0xffffffffu, (unsigned long long)mine.dst, r));
+        if (on[r]) d4[lane] = x[r];
+      }
+    } else {
+      for (int r = 0; r < kRows; ++r) {
+        const float* rs = reinterpret_cast<const float*>(__shfl_sync(0xffffffffu, (unsigned long long)mine.src, r));
+        float* rd = reinterpret_cast<float*>(__shfl_sync(0xffffffffu, (unsigned long long)mine.dst, r));
+        const int nf = __shfl_sync(0xffffffffu, mine.floats, r);
+        if (rs == nullptr) continue;
+        for (int c = lane; c < nf; c += 32) rd[c] = rs[c];
       }
     }
   }

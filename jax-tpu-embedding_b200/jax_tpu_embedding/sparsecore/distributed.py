@@ -41,6 +41,9 @@ class _Context:
     self.allocations: list[_PeerAllocation] = []
     self.exchange: dict = {}
     self.token = None
+    # What the peers may still be doing with this rank's memory since the last barrier.
+    self.peers_may_read_exchange = False  # a pull update was launched: peers read the exchange buffers
+    self.peers_may_write_tables = True    # ... and update the shards that the next lookup reads (or still fill them)
 
 
 _ctx: _Context | None = None
@@ -89,7 +92,11 @@ def alloc(shape, dtype=None):
   dtype = dtype or torch.float32
   lib = _native.lib()
   nbytes = int(np.prod(shape)) * torch.empty(0, dtype=dtype).element_size()
-  nbytes = max((nbytes + 255) // 256 * 256, 256)
+  # Whole 2 MiB pages: a peer mapping of an allocation that is not a multiple of the large page
+  # size falls back to small pages, and random row reads over NVLink then run at a quarter of the
+  # link bandwidth (measured: 160 GB/s against 700 GB/s).
+  page = 2 << 20
+  nbytes = max((nbytes + page - 1) // page * page, page)
   ptr = _native.c_vp()
   _native.check(lib.sc_peer_alloc(nbytes, ctypes.byref(ptr)))
   handle = ctypes.create_string_buffer(64)
@@ -107,6 +114,7 @@ def alloc(shape, dtype=None):
   flat = torch.as_tensor(_RawCudaBuffer(int(ptr.value), nbytes), device="cuda")
   tensor = flat[:int(np.prod(shape)) * torch.empty(0, dtype=dtype).element_size()].view(dtype).view(*shape)
   _ctx.allocations.append(_PeerAllocation(int(ptr.value), nbytes, bases, flat))
+  _ctx.peers_may_write_tables = True  # the owner is about to fill it: the next lookup starts with a barrier
   return tensor
 
 
@@ -141,6 +149,27 @@ def stream_barrier() -> None:
   torch = _native.torch_mod()
   if is_active():
     torch.distributed.all_reduce(_ctx.token, group=_ctx.group)
+    _ctx.peers_may_read_exchange = False
+    _ctx.peers_may_write_tables = False
+
+
+def barrier_before_lookup() -> None:
+  """Remote rows are about to be read: needed only if a peer may still be updating its shard."""
+  if is_active() and _ctx.peers_may_write_tables:
+    stream_barrier()
+
+
+def barrier_before_staging() -> None:
+  """The exchange buffers are about to be overwritten: needed only if a peer may still read them."""
+  if is_active() and _ctx.peers_may_read_exchange:
+    stream_barrier()
+
+
+def note_update_launched() -> None:
+  """Every rank launched its pull update (all ranks run the same call sequence)."""
+  if _ctx is not None:
+    _ctx.peers_may_read_exchange = True
+    _ctx.peers_may_write_tables = True
 
 
 def exchange_buffers(key, rp_size: int, coo: int, batch: int, dim: int):

@@ -182,6 +182,8 @@ class ForwardGroupCall:
         _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), None, 0, None))
       self.groups.append((items, idxs, nbytes))
     self.shapes = [tuple(r.act.shape) for r in requests]
+    self.sizes = [int(np.prod(shape)) for shape in self.shapes]
+    self.total_floats = sum(self.sizes)
     self.first = True
     self.sharded = any(r.geo.l != r.geo.c for r in requests)
     self.keep = [(r.ptrs,) for r in requests]
@@ -195,7 +197,9 @@ class ForwardGroupCall:
       self.first = False
       self.requests = None
     else:
-      outs = [torch.empty(shape, dtype=torch.float32, device="cuda") for shape in self.shapes]
+      # One allocation for all activations of the call.
+      flat = torch.empty(self.total_floats, dtype=torch.float32, device="cuda")
+      outs = [t.view(shape) for t, shape in zip(flat.split(self.sizes), self.shapes)]
       for items, idxs, _ in self.groups:
         for j, i in enumerate(idxs):
           items[j].activations = outs[i].data_ptr()
@@ -204,7 +208,7 @@ class ForwardGroupCall:
       # Every peer must have finished updating its shard before remote rows are read.
       from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
 
-      distributed.stream_barrier()
+      distributed.barrier_before_lookup()
     for items, idxs, nbytes in self.groups:
       ws = _native.workspace(nbytes, "lookup")
       _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
@@ -317,7 +321,7 @@ class GradGroupCall:
     if self.sharded:
       from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
 
-      distributed.stream_barrier()  # peers are done reading the exchange buffers of the previous call
+      distributed.barrier_before_staging()  # peers are done reading the exchange buffers of the previous call
       for items, idxs, nbytes in self.groups:
         ws = _native.workspace(nbytes, "lookup")
         _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
@@ -325,6 +329,8 @@ class GradGroupCall:
     for items, idxs, nbytes in self.groups:
       ws = _native.workspace(nbytes, "lookup")
       _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
+    if self.sharded:
+      distributed.note_update_launched()
     if self.first:
       self.first = False
       self.requests = None

@@ -312,6 +312,225 @@ def _raise_for_status(stats_host: np.ndarray, p: int, s: int, table: str, max_id
       "feature row offsets do not match the batch.")
 
 
+class BufferDict(dict):
+  """dict of output arrays that remembers which device buffers all its values are views of.
+
+  `token` identifies (buffer addresses, layout); callers that cache launch descriptors use it
+  instead of looking at every array.  Any change of the dict drops the token.
+  """
+
+  token = None
+
+  def _changed(self):
+    self.token = None
+
+  def __setitem__(self, k, v):
+    self._changed()
+    super().__setitem__(k, v)
+
+  def __delitem__(self, k):
+    self._changed()
+    super().__delitem__(k)
+
+  def update(self, *a, **k):
+    self._changed()
+    super().update(*a, **k)
+
+  def pop(self, *a):
+    self._changed()
+    return super().pop(*a)
+
+  def clear(self):
+    self._changed()
+    super().clear()
+
+  def setdefault(self, *a):
+    self._changed()
+    return super().setdefault(*a)
+
+  def popitem(self):
+    self._changed()
+    return super().popitem()
+
+
+class _DensePlan:
+  """Everything about a call that depends only on the specs and the input shapes.
+
+  Used when every feature is a dense 2-D int32 CUDA tensor (and every weight a float32 one) and the
+  process handles one device: the launch descriptors, buffer layout and workspace size are built
+  once; a call then only allocates its output buffers and fills in addresses.
+  """
+
+  def __init__(self, feature_specs, shapes, weighted: bool, global_device_count: int, s: int, allow_id_dropping: bool):
+    self.keep = list(feature_specs)
+    self.stacks = list(_group_by_stack(feature_specs).items())
+    self.weighted = weighted
+    p = s * global_device_count
+    self.p, self.s = p, s
+    self.rp_size = max(p, 8) * s
+    self.stats_size = 2 * p + s + 3
+    n = len(self.stacks)
+    self.items = (_native.PreprocessItem * n)()
+    self.descs = []
+    self.members = []
+    self.coos, self.limits, self.names = [], [], []
+    for si, (stack_name, members) in enumerate(self.stacks):
+      stacked = members[0][1].table_spec.stacked_table_spec
+      coo = _coo_buffer_size(stacked.max_ids_per_partition, global_device_count, s,
+                             stacked.suggested_coo_buffer_size_per_device)
+      self.coos.append(coo)
+      self.names.append(stack_name)
+      self.limits.append((stacked.max_ids_per_partition, stacked.max_unique_ids_per_partition))
+      descs, id_base, row_base = [], 0, 0
+      for idx, spec in members:
+        rows, valency = shapes[idx]
+        descs.append(_native.FeatureDesc(row_base, rows, *_transform(spec), valency, id_base))
+        id_base += rows * valency
+        row_base += rows
+      arr = (_native.FeatureDesc * len(descs))(*descs)
+      self.descs.append(arr)
+      self.members.append([idx for idx, _ in members])
+      it = self.items[si]
+      it.row_offsets = None
+      it.weights = None
+      it.nnz, it.total_rows = id_base, row_base
+      it.features = arr
+      it.num_features = len(descs)
+      it.options = _native.PreprocessOptions(
+          int(global_device_count), int(s), _native.COMBINERS.get(stacked.combiner, 0),
+          int(stacked.max_ids_per_partition), int(stacked.max_unique_ids_per_partition),
+          int(bool(allow_id_dropping)), int(coo), int(stacked.stack_vocab_size))
+    # Output layout: one int32 buffer [row pointers | embedding ids | sample ids] per stack, one
+    # float32 buffer of gains; byte offsets of every array.
+    self.int_sizes, self.int_offsets = [], []
+    pos = 0
+    for coo in self.coos:
+      for size in (self.rp_size, coo, coo):
+        self.int_sizes.append(size)
+        self.int_offsets.append(pos * 4)
+        pos += size
+    self.int_total = pos
+    self.float_offsets = [4 * sum(self.coos[:i]) for i in range(n)]
+    self.float_total = sum(self.coos)
+    self.groups = None  # launch groups and workspace sizes, sized on the first run (needs real addresses)
+
+  def _size_groups(self):
+    """Launch groups (bounded by the 32-bit sort key) and their workspace sizes."""
+    lib = _native.lib()
+    n = len(self.stacks)
+    self.groups = []
+    start = 0
+    while start < n:
+      m = n - start
+      while True:
+        sub = ctypes.cast(ctypes.byref(self.items, start * ctypes.sizeof(_native.PreprocessItem)),
+                          ctypes.POINTER(_native.PreprocessItem))
+        nbytes = lib.sc_preprocess_grouped_workspace_bytes(sub, m)
+        if nbytes or m == 1:
+          break
+        m = (m + 1) // 2
+      self.groups.append((sub, m, nbytes))
+      start += m
+
+  def run(self, features, feature_weights, has_leading_dimension: bool, device_output: bool):
+    torch = _native.torch_mod()
+    lib = _native.lib()
+    n = len(self.stacks)
+    ints = torch.empty(self.int_total, dtype=torch.int32, device="cuda")
+    floats = torch.empty(self.float_total, dtype=torch.float32, device="cuda")
+    stats_dev = torch.empty((n, self.stats_size), dtype=torch.int32, device="cuda")
+    ibase, fbase, sbase = ints.data_ptr(), floats.data_ptr(), stats_dev.data_ptr()
+    keep = []
+    for si in range(n):
+      it = self.items[si]
+      idxs = self.members[si]
+      if len(idxs) == 1:
+        it.ids = features[idxs[0]].data_ptr()
+        if self.weighted:
+          it.weights = feature_weights[idxs[0]].data_ptr()
+      else:
+        cat = torch.cat([features[i].reshape(-1) for i in idxs])
+        keep.append(cat)
+        it.ids = cat.data_ptr()
+        if self.weighted:
+          wcat = torch.cat([feature_weights[i].reshape(-1) for i in idxs])
+          keep.append(wcat)
+          it.weights = wcat.data_ptr()
+      it.row_pointers = ibase + self.int_offsets[3 * si]
+      it.embedding_ids = ibase + self.int_offsets[3 * si + 1]
+      it.sample_ids = ibase + self.int_offsets[3 * si + 2]
+      it.gains = fbase + self.float_offsets[si]
+      it.stats = sbase + si * self.stats_size * 4
+    stream = _native.current_stream_ptr()
+    if self.groups is None:
+      self._size_groups()
+    for sub, m, nbytes in self.groups:
+      if nbytes == 0:
+        _native.check(lib.sc_preprocess_grouped(sub, m, None, 0, None))
+      ws = _native.workspace(nbytes, "preprocess")
+      _native.check(lib.sc_preprocess_grouped(sub, m, ws.data_ptr(), ws.numel(), stream))
+    host = stats_dev.cpu().numpy()  # the only synchronisation of the call
+    del keep
+    p, s = self.p, self.s
+    status = host[:, 2 * p + s + 1]
+    if status.any():
+      si = int(np.flatnonzero(status)[0])
+      _raise_for_status(host[si], p, s, self.names[si], *self.limits[si])
+    int_views = ints.split(self.int_sizes)
+    float_views = floats.split(self.coos)
+    out_rp, out_ids, out_sids, out_gains = BufferDict(), BufferDict(), BufferDict(), BufferDict()
+    stats = SparseDenseMatmulInputStats()
+    max_ids, max_unique = host[:, :p].copy(), host[:, p:2 * p].copy()
+    required, dropped = host[:, 2 * p:2 * p + s].copy(), host[:, 2 * p + s]
+    for si, name in enumerate(self.names):
+      arrays = (int_views[3 * si], int_views[3 * si + 1], int_views[3 * si + 2], float_views[si])
+      if has_leading_dimension:
+        arrays = tuple(t.view(1, -1) for t in arrays)
+      if not device_output:
+        arrays = tuple(t.cpu().numpy() for t in arrays)
+      out_rp[name], out_ids[name], out_sids[name], out_gains[name] = arrays
+      stats.max_ids_per_partition[name] = max_ids[si]
+      stats.max_unique_ids_per_partition[name] = max_unique[si]
+      stats.required_buffer_sizes[name] = required[si]
+      stats.dropped_id_count[name] = int(dropped[si])
+    if device_output:
+      # The arrays keep the two buffers alive, so the addresses identify the contents' location.
+      token = (ints.data_ptr(), floats.data_ptr(), id(self), bool(has_leading_dimension))
+      for i, d in enumerate((out_rp, out_ids, out_sids, out_gains)):
+        d.token = token + (i,)
+    return out_rp, out_ids, out_sids, out_gains, 1, stats
+
+
+_DENSE_PLANS: dict = {}
+
+
+def _dense_plan(features, feature_weights, feature_specs, local_device_count, global_device_count, s, allow_id_dropping):
+  """The cached _DensePlan of this call, or None if the inputs do not qualify."""
+  torch = _native.torch_mod()
+  if local_device_count != 1:
+    return None
+  shapes = []
+  for f in features:
+    if not (isinstance(f, torch.Tensor) and f.is_cuda and f.dtype == torch.int32 and f.dim() == 2 and f.shape[1] > 0
+            and f.is_contiguous()):
+      return None
+    shapes.append((int(f.shape[0]), int(f.shape[1])))
+  weighted = feature_weights is not None
+  if weighted:
+    for w, f in zip(feature_weights, features):
+      if not (isinstance(w, torch.Tensor) and w.is_cuda and w.dtype == torch.float32 and w.shape == f.shape
+              and w.is_contiguous()):
+        return None
+  key = (tuple((id(f), id(f.table_spec._stacked_table_spec), id(f._id_transformation)) for f in feature_specs),  # pylint: disable=protected-access
+         tuple(shapes), weighted, global_device_count, s, bool(allow_id_dropping))
+  plan = _DENSE_PLANS.get(key)
+  if plan is None:
+    if len(_DENSE_PLANS) > 16:
+      _DENSE_PLANS.clear()
+    plan = _DENSE_PLANS[key] = _DensePlan(feature_specs, shapes, weighted, global_device_count, s, allow_id_dropping)
+  return plan
+
+
 def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_specs, local_device_count: int,
                                          global_device_count: int, *, num_sc_per_device: int,
                                          sharding_strategy: ShardingStrategy = ShardingStrategy.MOD,
@@ -352,6 +571,9 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
   torch = _native.require_cuda()
   lib = _native.lib()
   l, s = local_device_count, num_sc_per_device
+  plan = _dense_plan(features, feature_weights, feature_specs, l, global_device_count, s, allow_id_dropping)
+  if plan is not None:
+    return plan.run(features, feature_weights, has_leading_dimension, device_output)
   out_rp, out_ids, out_sids, out_gains = {}, {}, {}, {}
   stats = SparseDenseMatmulInputStats()
   stacks = list(_group_by_stack(feature_specs).items())

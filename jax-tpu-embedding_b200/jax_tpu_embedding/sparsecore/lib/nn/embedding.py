@@ -442,6 +442,27 @@ def _is_cuda_tensor(x) -> bool:
 _CALL_CACHE: dict = {}
 
 
+def _csr_key(rps, eids, sids, gains, names):
+  """Identity of the four CSR array dicts for the launch-descriptor cache, or None.
+
+  Dicts that come from this package's preprocessing carry a token naming the device buffers they
+  are views of; otherwise every array is described by (address, shape, dtype).
+  """
+  tokens = tuple(getattr(d, "token", None) for d in (rps, eids, sids, gains))
+  if all(t is not None for t in tokens) and len(rps) == len(names):
+    return tokens
+  arrays = [d[n] for n in names for d in (rps, eids, sids, gains)]
+  if not all(_is_cuda_tensor(x) for x in arrays):
+    return None
+  return tuple((x.data_ptr(), tuple(x.shape), x.dtype) for x in arrays)
+
+
+def _tensor_key(tensors):
+  if not all(_is_cuda_tensor(x) for x in tensors):
+    return None
+  return tuple((x.data_ptr(), tuple(x.shape)) for x in tensors)
+
+
 def _cache_put(key, value):
   if len(_CALL_CACHE) > 32:
     _CALL_CACHE.clear()
@@ -470,10 +491,10 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
   strategy = int(sharding_strategy_to_enum(sharding_strategy))
 
   key = None
-  operands = [(rps[n], eids[n], sids[n], gains[n], embedding_variables[n].table) for n in stacked_table_specs]
-  if all(_is_cuda_tensor(x) for ops in operands for x in ops):
-    key = ("fwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching,
-           tuple((x.data_ptr(), tuple(x.shape), x.dtype) for ops in operands for x in ops))
+  csr_key = _csr_key(rps, eids, sids, gains, stacked_table_specs)
+  table_key = _tensor_key([embedding_variables[n].table for n in stacked_table_specs])
+  if csr_key is not None and table_key is not None:
+    key = ("fwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, csr_key, table_key)
   cached = _CALL_CACHE.get(key) if key is not None else None
   if cached is None:
     requests, local = [], 1
@@ -595,11 +616,12 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
   limits = None if embedding_var_limits is None else tuple(
       tuple(embedding_var_limits[n]) for n in stacked_table_specs)
   key = None
-  operands = [(rps[n], eids[n], sids[n], gains[n], embedding_variables[n].table, *embedding_variables[n].slot,
-               gradients[n]) for n in stacked_table_specs]
-  if all(_is_cuda_tensor(x) for ops in operands for x in ops):
+  csr_key = _csr_key(rps, eids, sids, gains, stacked_table_specs)
+  tensor_key = _tensor_key([x for n in stacked_table_specs
+                            for x in (embedding_variables[n].table, *embedding_variables[n].slot, gradients[n])])
+  if csr_key is not None and tensor_key is not None:
     key = ("bwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, label, limits,
-           tuple(hypers.values()), tuple((x.data_ptr(), tuple(x.shape), x.dtype) for ops in operands for x in ops))
+           tuple(hypers.values()), csr_key, tensor_key)
   call = _CALL_CACHE.get(key) if key is not None else None
   if call is None:
     requests = []
