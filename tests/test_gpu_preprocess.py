@@ -97,3 +97,34 @@ def test_invalid_arguments():
     pip.preprocess_sparse_dense_matmul_input(case.features, None, case.feature_specs, 1, 3, num_sc_per_device=1)
   with pytest.raises(ValueError, match="cannot be empty"):
     pip.preprocess_sparse_dense_matmul_input([], None, [], 1, 1, num_sc_per_device=1)
+
+
+@pytest.mark.parametrize("weighted", [False, True])
+@pytest.mark.parametrize("stack", [False, True])
+def test_dense_device_inputs_take_the_cached_plan(weighted, stack):
+  """Dense int32 CUDA tensors use prebuilt launch descriptors; results equal the general path and the oracle,
+  also when the plan is reused with new data, and the outputs carry a buffer token."""
+  import torch
+
+  def make(seed):
+    return cases.make_case(
+        "dense_plan", seed=seed, batch=256, num_sc_per_device=2, combiner="mean", stack=stack, max_ids=4096,
+        max_unique=4096, weights=True if weighted else None,
+        tables=[dict(vocab=3000, dim=16, features=[dict(kind="dense", valency=3, dist="zipf"), dict(kind="dense", valency=1)]),
+                dict(vocab=500, dim=16, features=[dict(kind="dense", valency=2)])])
+
+  case = make(31)
+  kw = dict(num_sc_per_device=2, has_leading_dimension=False)
+  for seed in (31, 32):  # the second round reuses the plan of the first
+    data = make(seed)
+    feats = [torch.from_numpy(f).cuda() for f in data.features]
+    weights = None if data.weights is None else [torch.from_numpy(w).cuda() for w in data.weights]
+    got = pip.preprocess_sparse_dense_matmul_input(feats, weights, case.feature_specs, 1, 1, device_output=True, **kw)
+    want = ob.oracle_preprocess(data.features, data.weights, case.feature_specs, 1, 1, **kw)
+    assert isinstance(got[0], pip.BufferDict) and got[0].token is not None and got[3].token is not None
+    host = tuple({k: v.cpu().numpy() for k, v in d.items()} for d in got[:4]) + got[4:]
+    _compare(case, host, want)
+    general = pip.preprocess_sparse_dense_matmul_input(data.features, data.weights, case.feature_specs, 1, 1, **kw)
+    _compare(case, general, want)
+  got[0]["extra"] = None
+  assert got[0].token is None
