@@ -156,9 +156,20 @@ int32_t sc_sparse_dense_matmul_fwd(const sc_csr_t* csr, const float* const* shar
  * behind the sgd / adagrad / adam primitives (lib/core/primitives/
  * sparse_dense_matmul_grad_with_sgd.py:98-238, ..._adagrad.py:119-292, ..._adam.py:144-405).
  * clip_min / clip_max clamp the table only (primitives/utils.py:24-59); pass NaN for "no bound". */
+enum {
+  SC_OPT_SGD = 0,              /* hyper {learning_rate}; no slot */
+  SC_OPT_ADAGRAD = 1,          /* hyper {learning_rate}; slot0 accumulator */
+  SC_OPT_ADAM = 2,             /* hyper {alpha_t, beta_1, beta_2, epsilon_hat}; slots momentum, velocity */
+  /* The other fused optimizers of the reference (..._adagrad_momentum.py:262-308, ..._ftrl.py:275-334,
+   * ..._laprop.py:294-335, ..._f2a.py:257-285); flags travel as 0.0 / 1.0. */
+  SC_OPT_ADAGRAD_MOMENTUM = 3, /* hyper {lr, momentum, beta2, epsilon, exponent, use_nesterov}; slots accumulator, momentum */
+  SC_OPT_FTRL = 4,             /* hyper {lr, lr_power, l1, l2, beta, multiply_linear_by_learning_rate}; slots accumulator, linear */
+  SC_OPT_LAPROP = 5,           /* hyper {lr, b1, decay_rate, eps}; slots mu, nu */
+  SC_OPT_F2A = 6               /* hyper {lr, rho, l1, l2, max_lr_multiplier, global_step}; slots accumulator, local_step */
+};
 typedef struct {
-  int32_t optimizer;      /* 0 sgd, 1 adagrad, 2 adam */
-  float hyper[4];         /* sgd/adagrad: {learning_rate}; adam: {alpha_t, beta_1, beta_2, epsilon_hat} */
+  int32_t optimizer;      /* SC_OPT_* */
+  float hyper[8];
   float clip_min, clip_max;
 } sc_optimizer_t;
 

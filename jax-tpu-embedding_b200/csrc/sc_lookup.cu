@@ -42,7 +42,9 @@ namespace {
 constexpr int kBlock = 256;
 constexpr int kWarpsPerBlock = kBlock / 32;
 constexpr uint32_t kNoRow = 0xffffffffu;
-constexpr int kReduceOnly = 3;  // OptParams::kind of the reduce-only mode
+constexpr int kReduceOnly = 100;  // OptParams::kind of the reduce-only mode
+// Slot variables of an optimizer kind.
+inline int optimizer_slots(int kind) { return kind == SC_OPT_SGD ? 0 : kind == SC_OPT_ADAGRAD ? 1 : 2; }
 
 struct CsrView {
   const int32_t* row_pointers;
@@ -58,8 +60,9 @@ struct CsrView {
 };
 
 struct OptParams {
-  int kind;  // 0 sgd, 1 adagrad, 2 adam
-  float h0, h1, h2, h3;
+  int kind;   // SC_OPT_* of sc_b200.h, or kReduceOnly
+  int slots;  // slot variables the update reads and writes: 0, 1 or 2
+  float h0, h1, h2, h3, h4, h5;
   float lo, hi;  // NaN = unbounded
 };
 
@@ -539,18 +542,64 @@ __device__ __forceinline__ float clip(float x, float lo, float hi) {
   return x;
 }
 
+// The two-slot optimizers beyond Adam, one scalar; returns the new (unclipped) weight.
+//  adagrad momentum (sparse_dense_matmul_grad_with_adagrad_momentum.py:262-308 of the reference):
+//    hyper = {lr, momentum, beta2, epsilon, exponent, use_nesterov}; slots (accumulator, momentum)
+//  ftrl (..._ftrl.py:275-334): hyper = {lr, lr_power, l1, l2, beta, multiply_linear_by_lr}; slots (accumulator, linear)
+//  laprop (..._laprop.py:294-335): hyper = {lr, b1, decay_rate, eps}; slots (mu, nu)
+//  f2a (..._f2a.py:257-285): hyper = {lr, rho, l1, l2, max_lr_multiplier, global_step}; slots (accumulator, local_step)
+__device__ __forceinline__ float apply_opt_two_slots(const OptParams& o, float w, float g, float& s0, float& s1) {
+  if (o.kind == SC_OPT_ADAGRAD_MOMENTUM) {
+    const float g2 = g * g;
+    s0 = o.h2 == 1.0f ? s0 + g2 : o.h2 * s0 + (1.0f - o.h2) * g2;
+    const float scaled = powf(s0 + o.h3, -1.0f / o.h4) * g;
+    s1 = o.h1 * s1 + scaled;
+    const float update = o.h5 != 0.0f ? o.h1 * s1 + scaled : s1;
+    return w - o.h0 * update;
+  }
+  if (o.kind == SC_OPT_FTRL) {
+    const float acc_new = s0 + g * g;
+    const float p_new = powf(acc_new, -o.h1);
+    const float delta_p = p_new - powf(s0, -o.h1);
+    const bool by_lr = o.h5 != 0.0f;
+    s0 = acc_new;
+    s1 = by_lr ? (s1 + o.h0 * g) - delta_p * w : (s1 + g) - (delta_p / o.h0) * w;
+    const float l1 = by_lr ? o.h2 * o.h0 : o.h2;
+    const float numer = o.h2 == 0.0f ? -s1 : fminf(fmaxf(s1, -l1), l1) - s1;
+    const float denom = by_lr ? (p_new + 2.0f * (o.h0 * o.h3)) + o.h4 : (p_new + o.h4) / o.h0 + 2.0f * o.h3;
+    return numer / denom;
+  }
+  if (o.kind == SC_OPT_LAPROP) {
+    const float g2 = g * g + o.h3;
+    s1 = s1 * o.h2 + (1.0f - o.h2) * g2;
+    float update = g / sqrtf(s1);
+    update = o.h1 * s0 + sqrtf(1.0f - o.h1 * o.h1) * update;
+    s0 = update;
+    return w - o.h0 * update;
+  }
+  // SC_OPT_F2A
+  s1 = s1 + 1.0f;
+  const float fa = fminf(powf(fmaxf(o.h5, 1.0f) / s1, o.h1), o.h4);
+  s0 = s0 + g * g;
+  const float sign = w > 0.0f ? 1.0f : (w < 0.0f ? -1.0f : 0.0f);
+  const float update = (g * fa) / sqrtf(s0) + (o.h2 * sign + o.h3 * w);
+  return w - o.h0 * update;
+}
+
 // One optimizer step on one scalar; slot values are updated in place.
 __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g, float& s0, float& s1) {
   float nw;
-  if (o.kind == 0) {
+  if (o.kind == SC_OPT_SGD) {
     nw = w - o.h0 * g;
-  } else if (o.kind == 1) {
+  } else if (o.kind == SC_OPT_ADAGRAD) {
     s0 = s0 + g * g;
     nw = w - (o.h0 * g) / sqrtf(s0);
-  } else {
+  } else if (o.kind == SC_OPT_ADAM) {
     s0 = s0 + (1.0f - o.h1) * (g - s0);
     s1 = s1 + (1.0f - o.h2) * (g * g - s1);
     nw = w - (o.h0 * s0) / (sqrtf(s1) + o.h3);
+  } else {
+    nw = apply_opt_two_slots(o, w, g, s0, s1);
   }
   return clip(nw, o.lo, o.hi);
 }
@@ -587,8 +636,8 @@ __device__ __forceinline__ RowCtx make_ctx(const TableDesc& td) {
   c.P = td.v.P;
   c.rows_per_shard = td.v.rows_per_shard;
   c.w0 = td.table[0];
-  c.a0 = c.o.kind >= 1 ? td.slot0[0] : nullptr;
-  c.b0 = c.o.kind >= 2 ? td.slot1[0] : nullptr;
+  c.a0 = c.o.slots >= 1 ? td.slot0[0] : nullptr;
+  c.b0 = c.o.slots >= 2 ? td.slot1[0] : nullptr;
   c.td = &td;
   return c;
 }
@@ -604,8 +653,8 @@ __device__ __forceinline__ void row_pointers_of(const RowCtx& c, int64_t grow, f
   const int g = (int)(grow / c.rows_per_shard);
   const int64_t off = (grow - (int64_t)g * c.rows_per_shard) * c.dim;
   *w = c.td->table[g] + off;
-  *a = c.o.kind >= 1 ? c.td->slot0[g] + off : nullptr;
-  *b = c.o.kind >= 2 ? c.td->slot1[g] + off : nullptr;
+  *a = c.o.slots >= 1 ? c.td->slot0[g] + off : nullptr;
+  *b = c.o.slots >= 2 ? c.td->slot1[g] + off : nullptr;
 }
 
 // Loads the table row (and slot rows) of global row `grow` into registers.
@@ -842,15 +891,17 @@ __device__ __forceinline__ float fast_axpy(float a, float g, float x) { return _
 // root (2 ulp) instead of IEEE sqrt + divide; within 1e-6 relative of apply_opt.
 __device__ __forceinline__ float apply_opt_fast(const OptParams& o, bool clipped, float w, float g, float& s0, float& s1) {
   float nw;
-  if (o.kind == 0) {
+  if (o.kind == SC_OPT_SGD) {
     nw = __fmaf_rn(-o.h0, g, w);
-  } else if (o.kind == 1) {
+  } else if (o.kind == SC_OPT_ADAGRAD) {
     s0 = __fmaf_rn(g, g, s0);
     nw = __fmaf_rn(-(o.h0 * g), rsqrtf(s0), w);
-  } else {
+  } else if (o.kind == SC_OPT_ADAM) {
     s0 = __fmaf_rn(1.0f - o.h1, g - s0, s0);
     s1 = __fmaf_rn(1.0f - o.h2, g * g - s1, s1);
     nw = w - __fdividef(o.h0 * s0, sqrtf(s1) + o.h3);
+  } else {
+    nw = apply_opt_two_slots(o, w, g, s0, s1);
   }
   return clipped ? clip(nw, o.lo, o.hi) : nw;
 }
@@ -1595,7 +1646,7 @@ struct BwdPlan {
   std::vector<uint32_t> n_ent;  // entry index space per table (0 for direct tables)
   uint64_t total_chunks = 0, total_ent = 0, total_rows = 0;
   int total_shards = 0, total_sources = 0;
-  int w = 0, k = 0, g = 0, max_dim = 0, max_slots = 0;
+  int w = 0, k = 0, g = 0, max_dim = 0, kind = 0, max_slots = 0;
 };
 
 int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
@@ -1639,12 +1690,12 @@ int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
     p->total_shards += v.P;
     p->max_dim = v.dim > p->max_dim ? v.dim : p->max_dim;
     const sc_optimizer_t& o = items[i].optimizer;
-    if (o.optimizer < 0 || o.optimizer > 2) SC_FAIL(SC_INVALID_ARGUMENT, "unknown optimizer");
-    if (i == 0) p->max_slots = o.optimizer;
-    if (o.optimizer != p->max_slots) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the optimizer kind");
+    if (o.optimizer < 0 || o.optimizer > SC_OPT_F2A) SC_FAIL(SC_INVALID_ARGUMENT, "unknown optimizer");
+    if (i == 0) { p->kind = o.optimizer; p->max_slots = optimizer_slots(o.optimizer); }
+    if (o.optimizer != p->kind) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the optimizer kind");
     if ((!pull && !items[i].activation_grad) || !items[i].shard_tables) SC_FAIL(SC_INVALID_ARGUMENT, "null gradient or table pointer");
-    if (o.optimizer >= 1 && !items[i].shard_slot0) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 0");
-    if (o.optimizer >= 2 && !items[i].shard_slot1) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
+    if (p->max_slots >= 1 && !items[i].shard_slot0) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 0");
+    if (p->max_slots >= 2 && !items[i].shard_slot1) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
     if (!isnan(o.clip_min) && !isnan(o.clip_max) && o.clip_min > o.clip_max)
       SC_FAIL(SC_INVALID_ARGUMENT, "min_value must be less than or equal to max_value");
   }
@@ -1793,7 +1844,9 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     td.v = p.views[i];
     td.grad = items[i].activation_grad;
     td.opt.kind = o.optimizer;
+    td.opt.slots = p.max_slots;
     td.opt.h0 = o.hyper[0]; td.opt.h1 = o.hyper[1]; td.opt.h2 = o.hyper[2]; td.opt.h3 = o.hyper[3];
+    td.opt.h4 = o.hyper[4]; td.opt.h5 = o.hyper[5];
     td.opt.lo = o.clip_min; td.opt.hi = o.clip_max;
     td.chunk_base = chunk_base;
     td.indirect = p.indirect[i];
@@ -1823,8 +1876,8 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
       source_base += items[i].num_sources;
       td.v.P = 1;  // row -> pointer arithmetic of the update sees the owned shard only
     }
-    float* const* srcs[3] = {items[i].shard_tables, o.optimizer >= 1 ? items[i].shard_slot0 : nullptr,
-                             o.optimizer >= 2 ? items[i].shard_slot1 : nullptr};
+    float* const* srcs[3] = {items[i].shard_tables, p.max_slots >= 1 ? items[i].shard_slot0 : nullptr,
+                             p.max_slots >= 2 ? items[i].shard_slot1 : nullptr};
     for (int a = 0; a < 3; ++a) {
       if (!srcs[a]) { pool_index.push_back(-1); continue; }
       pool_index.push_back((int)img.pool.size());
@@ -2100,10 +2153,11 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   if (v.S != 1 || v.P != 1)
     SC_FAIL(SC_UNSUPPORTED, "the allocation-free update handles one shard and one SparseCore per buffer (got %d, %d)", v.P, v.S);
   const int kind = optimizer->optimizer;
-  if (kind < 0 || kind > 2) SC_FAIL(SC_INVALID_ARGUMENT, "unknown optimizer");
+  if (kind < 0 || kind > SC_OPT_F2A) SC_FAIL(SC_INVALID_ARGUMENT, "unknown optimizer");
   if (!activation_grad || !shard_tables || !shard_tables[0]) SC_FAIL(SC_INVALID_ARGUMENT, "null gradient or table pointer");
-  if (kind >= 1 && (!shard_slot0 || !shard_slot0[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 0");
-  if (kind >= 2 && (!shard_slot1 || !shard_slot1[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
+  const int nslots = optimizer_slots(kind);
+  if (nslots >= 1 && (!shard_slot0 || !shard_slot0[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 0");
+  if (nslots >= 2 && (!shard_slot1 || !shard_slot1[0])) SC_FAIL(SC_INVALID_ARGUMENT, "optimizer needs slot variable 1");
   if (!isnan(optimizer->clip_min) && !isnan(optimizer->clip_max) && optimizer->clip_min > optimizer->clip_max)
     SC_FAIL(SC_INVALID_ARGUMENT, "min_value must be less than or equal to max_value");
   int w, k, g;
@@ -2145,22 +2199,24 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   host.td.v = v;
   host.td.grad = activation_grad;
   host.td.opt.kind = kind;
+  host.td.opt.slots = nslots;
   host.td.opt.h0 = optimizer->hyper[0]; host.td.opt.h1 = optimizer->hyper[1];
   host.td.opt.h2 = optimizer->hyper[2]; host.td.opt.h3 = optimizer->hyper[3];
+  host.td.opt.h4 = optimizer->hyper[4]; host.td.opt.h5 = optimizer->hyper[5];
   host.td.opt.lo = optimizer->clip_min; host.td.opt.hi = optimizer->clip_max;
   host.td.table = pool_dev;
-  host.td.slot0 = kind >= 1 ? pool_dev + 1 : nullptr;
-  host.td.slot1 = kind >= 2 ? pool_dev + 2 : nullptr;
+  host.td.slot0 = nslots >= 1 ? pool_dev + 1 : nullptr;
+  host.td.slot1 = nslots >= 2 ? pool_dev + 2 : nullptr;
   host.td.total_rows = (uint32_t)v.rows_per_shard;
-  float* pool_host[3] = {shard_tables[0], kind >= 1 ? shard_slot0[0] : nullptr, kind >= 2 ? shard_slot1[0] : nullptr};
+  float* pool_host[3] = {shard_tables[0], nslots >= 1 ? shard_slot0[0] : nullptr, nslots >= 2 ? shard_slot1[0] : nullptr};
   // Both sources are pageable stack memory: the copies are staged before the calls return.
   SC_CUDA_OK(cudaMemcpyAsync(base, &host.td, sizeof(TableDesc), cudaMemcpyHostToDevice, cs));
   SC_CUDA_OK(cudaMemcpyAsync(pool_dev, pool_host, sizeof pool_host, cudaMemcpyHostToDevice, cs));
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(base);
   if (w == 4 && pipe_enabled() && aligned16(activation_grad) && aligned16(pool_host[0]) && aligned16(pool_host[1]) &&
       aligned16(pool_host[2]))
-    return dispatch_bwd_pipe(tabs, 1, chunks, u, kind, v.dim, cs);
-#define SC_STATIC_CALL(W, K, G) launch_bwd<W, K, G>(tabs, 1, chunks, u, kind, cs)
+    return dispatch_bwd_pipe(tabs, 1, chunks, u, nslots, v.dim, cs);
+#define SC_STATIC_CALL(W, K, G) launch_bwd<W, K, G>(tabs, 1, chunks, u, nslots, cs)
   SC_SHAPE_SWITCH(w, k, g, SC_STATIC_CALL);
 #undef SC_STATIC_CALL
 }

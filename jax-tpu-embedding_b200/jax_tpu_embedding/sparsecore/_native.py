@@ -54,7 +54,7 @@ class Csr(ctypes.Structure):
 
 
 class Optimizer(ctypes.Structure):
-  _fields_ = [("optimizer", c_i32), ("hyper", c_f32 * 4), ("clip_min", c_f32), ("clip_max", c_f32)]
+  _fields_ = [("optimizer", c_i32), ("hyper", c_f32 * 8), ("clip_min", c_f32), ("clip_max", c_f32)]
 
 
 class FwdItem(ctypes.Structure):

@@ -224,7 +224,7 @@ def run_forward(rp, ids, sids, gains, table, **kw):
   return run_forward_group([ForwardRequest(rp, ids, sids, gains, table, **kw)])[0]
 
 
-_OPT_KIND = {"sgd": 0, "adagrad": 1, "adam": 2}
+_OPT_KIND = {"sgd": 0, "adagrad": 1, "adam": 2, "adagrad_momentum": 3, "ftrl": 4, "laprop": 5, "f2a": 6}
 
 
 class GradRequest:
@@ -246,7 +246,7 @@ class GradRequest:
     self.csr = self.geo.csr(self.rp, self.ids, self.sids, self.gains)
     opt = _native.Optimizer()
     opt.optimizer = _OPT_KIND[kind]
-    for i in range(4):
+    for i in range(8):
       opt.hyper[i] = float(hyper[i]) if i < len(hyper) else 0.0
     opt.clip_min = float("nan") if min_value is None else float(min_value)
     opt.clip_max = float("nan") if max_value is None else float(max_value)

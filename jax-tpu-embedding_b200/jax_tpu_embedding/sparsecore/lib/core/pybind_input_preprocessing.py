@@ -653,3 +653,45 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
       arrays = tuple(t.cpu().numpy() for t in arrays)
     out_rp[stack_name], out_ids[stack_name], out_sids[stack_name], out_gains[stack_name] = arrays
   return out_rp, out_ids, out_sids, out_gains, 1, stats
+
+
+def preprocess_sparse_dense_matmul_sparse_coo_input(indices, values, dense_shapes, feature_specs, local_device_count: int,
+                                                    global_device_count: int, *, num_sc_per_device: int,
+                                                    sharding_strategy: ShardingStrategy = ShardingStrategy.MOD,
+                                                    has_leading_dimension: bool = False,
+                                                    allow_id_dropping: bool = False, batch_number: int = 0,
+                                                    enable_minibatching: bool = False, all_reduce_interface=None,
+                                                    device_output: bool = False):
+  """Same as preprocess_sparse_dense_matmul_input for features given as sparse COO tensors.
+
+  Per feature: `indices` int [N, 2] of (sample, position) in row-major order, `values` int32 [N]
+  of embedding ids, `dense_shape` (batch, max positions).  Every id has weight 1.  Mirrors
+  `preprocess_sparse_dense_matmul_sparse_coo_input` of the reference's pybind module
+  (jax_tpu_embedding/sparsecore/lib/core/pybind_input_preprocessing.cc:301-310; the row pointers
+  of sparse_coo_input_batch.cc:35-79 are the row splits built here).
+  """
+  indices, values, dense_shapes = list(indices), list(values), list(dense_shapes)
+  if not (len(indices) == len(values) == len(dense_shapes) == len(list(feature_specs))):
+    raise ValueError("indices, values, dense_shapes and feature_specs must have the same length")
+  features = []
+  for idx, val, shape in zip(indices, values, dense_shapes):
+    idx = np.asarray(idx.cpu() if _is_torch(idx) else idx)
+    val_host = np.asarray(val.cpu() if _is_torch(val) else val)
+    shape = np.asarray(shape).reshape(-1)
+    if idx.ndim != 2 or idx.shape[1] != 2:
+      raise ValueError(f"indices must have shape [N, 2], got {idx.shape}")
+    if val_host.ndim != 1 or len(val_host) != len(idx):
+      raise ValueError("values must be 1-D with one id per index")
+    if len(shape) != 2:
+      raise ValueError("dense_shape must have two elements")
+    batch = int(shape[0])
+    rows = idx[:, 0]
+    if len(rows) and (np.any(np.diff(rows) < 0) or rows[0] < 0 or rows[-1] >= batch):
+      raise ValueError("indices must be in row-major order with row ids inside the dense shape")
+    splits = np.searchsorted(rows, np.arange(batch + 1), side="left").astype(np.int64)
+    features.append(RaggedInput(np.ascontiguousarray(val_host, dtype=np.int32), splits, None))
+  return preprocess_sparse_dense_matmul_input(
+      features, None, feature_specs, local_device_count, global_device_count, num_sc_per_device=num_sc_per_device,
+      sharding_strategy=sharding_strategy, has_leading_dimension=has_leading_dimension,
+      allow_id_dropping=allow_id_dropping, batch_number=batch_number, enable_minibatching=enable_minibatching,
+      all_reduce_interface=all_reduce_interface, device_output=device_output)

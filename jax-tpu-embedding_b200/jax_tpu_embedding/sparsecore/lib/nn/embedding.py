@@ -308,6 +308,39 @@ def preprocess_sparse_dense_matmul_input(features, features_weights, feature_spe
   return (PreprocessedInput(SparseDenseMatmulInput(*csr), minibatches), SparseDenseMatmulInputStats.from_cc(stats))
 
 
+def preprocess_sparse_dense_matmul_input_from_sparse_tensor(indices, values, dense_shapes, feature_specs,
+                                                            local_device_count: int, global_device_count: int, *,
+                                                            num_sc_per_device: int | None = None,
+                                                            sharding_strategy: str = "MOD",
+                                                            has_leading_dimension: bool = False,
+                                                            allow_id_dropping: bool = False, batch_number: int = 0,
+                                                            enable_minibatching: bool = False,
+                                                            all_reduce_interface=None, device_output: bool = True
+                                                            ) -> tuple[PreprocessedInput, SparseDenseMatmulInputStats]:
+  """preprocess_sparse_dense_matmul_input for features given as sparse tensors (unit weights).
+
+  `indices`: per feature an int [N, 2] array of (sample, position), row-major; `values`: int32 [N]
+  embedding ids; `dense_shapes`: (batch, max positions).  All three have the structure of
+  `feature_specs` (reference: lib/nn/embedding.py:708-819).
+  """
+  num_sc_per_device = _get_num_sc_per_device(num_sc_per_device)
+  _assert_same_structure(indices, feature_specs, "indices", "feature_specs")
+  _assert_same_structure(values, feature_specs, "values", "feature_specs")
+  _assert_same_structure(dense_shapes, feature_specs, "dense_shapes", "feature_specs")
+  if enable_minibatching and all_reduce_interface is None and local_device_count < global_device_count:
+    raise ValueError("all_reduce_interface must be provided when minibatching is enabled for multi-host.")
+  *csr, num_minibatches, stats = pybind_input_preprocessing.preprocess_sparse_dense_matmul_sparse_coo_input(
+      _leaves(indices), _leaves(values), _leaves(dense_shapes), _leaves(feature_specs), local_device_count,
+      global_device_count, num_sc_per_device=num_sc_per_device,
+      sharding_strategy=sharding_strategy_to_enum(sharding_strategy), has_leading_dimension=has_leading_dimension,
+      allow_id_dropping=allow_id_dropping, batch_number=batch_number, enable_minibatching=enable_minibatching,
+      all_reduce_interface=all_reduce_interface, device_output=device_output)
+  minibatches = np.full(local_device_count, num_minibatches, dtype=np.int32)
+  if has_leading_dimension:
+    minibatches = minibatches.reshape(local_device_count, 1)
+  return (PreprocessedInput(SparseDenseMatmulInput(*csr), minibatches), SparseDenseMatmulInputStats.from_cc(stats))
+
+
 @dataclasses.dataclass(frozen=True)
 class ShapeDtype:
   shape: tuple[int, ...]
@@ -632,6 +665,8 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
       extra = {}
       if embedding_var_limits is not None:
         extra["min_value"], extra["max_value"] = embedding_var_limits[name]
+      if isinstance(stacked.optimizer, embedding_spec.FTRLOptimizerSpec):
+        extra["multiply_linear_by_learning_rate"] = stacked.optimizer.multiply_linear_by_learning_rate
       requests.append(stacked.optimizer.get_optimizer_primitive().prepare(
           _flat(rps[name]), _flat(eids[name]), _flat(sids[name]), _flat(gains[name]), np.int32(1), variables.table,
           *variables.slot, gradients[name], *hyper,

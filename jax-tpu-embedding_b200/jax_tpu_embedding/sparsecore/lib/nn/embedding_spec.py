@@ -39,6 +39,26 @@ class AdamSlotVariables(NamedTuple):
   velocity: Any
 
 
+class AdagradMomentumSlotVariables(NamedTuple):
+  accumulator: Any
+  momentum: Any
+
+
+class FTRLSlotVariables(NamedTuple):
+  accumulator: Any
+  linear: Any
+
+
+class LaPropSlotVariables(NamedTuple):
+  mu: Any
+  nu: Any
+
+
+class F2ASlotVariables(NamedTuple):
+  accumulator: Any
+  local_step: Any
+
+
 def _f32(x) -> np.ndarray:
   return np.asarray(x, dtype=np.float32)
 
@@ -174,6 +194,170 @@ class AdamOptimizerSpec(OptimizerSpec):
     from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_grad_with_adam as m  # pylint: disable=g-import-not-at-top
 
     return m.tpu_sparse_dense_matmul_grad_with_adam_primitive
+
+
+def _primitive(module_name: str):
+  import importlib  # pylint: disable=g-import-not-at-top
+
+  mod = importlib.import_module(f"jax_tpu_embedding.sparsecore.lib.core.primitives.{module_name}")
+  return getattr(mod, f"tpu_{module_name}_primitive")
+
+
+class AdagradMomentumOptimizerSpec(OptimizerSpec):
+  """Adagrad-scaled gradient fed through (optionally Nesterov) momentum.
+
+  a <- a + g^2 (beta2 == 1) or beta2 a + (1 - beta2) g^2; s = (a + epsilon)^(-1/exponent) g;
+  m <- momentum m + s; theta <- theta - lr (momentum m + s if use_nesterov else m).
+  Mirrors the reference's AdagradMomentumOptimizerSpec (lib/nn/embedding_spec.py:560-650).
+  """
+
+  def __init__(self, learning_rate=0.001, momentum: float = 0.9, beta2: float = 1.0, epsilon: float = 1e-10,
+               exponent: float = 2.0, use_nesterov: bool = False, initial_accumulator_value: float = 0.1,
+               initial_momentum_value: float = 0.0):
+    super().__init__(learning_rate)
+    self.momentum = momentum
+    self.beta2 = beta2
+    self.epsilon = epsilon
+    self.exponent = exponent
+    self.use_nesterov = use_nesterov
+    self.initial_accumulator_value = initial_accumulator_value
+    self.initial_momentum_value = initial_momentum_value
+
+  def slot_variables_initializers(self):
+    return AdagradMomentumSlotVariables(accumulator=initializers.constant(float(self.initial_accumulator_value)),
+                                        momentum=initializers.constant(float(self.initial_momentum_value)))
+
+  def get_hyperparameters(self, step=None):
+    return (self.get_learning_rate(step), _f32(self.momentum), _f32(self.beta2), _f32(self.epsilon),
+            _f32(self.exponent), np.asarray(bool(self.use_nesterov)))
+
+  def __hash__(self) -> int:
+    return hash((self.learning_rate, self.momentum, self.beta2, self.epsilon, self.exponent, self.use_nesterov,
+                 self.initial_accumulator_value, self.initial_momentum_value))
+
+  def short_name(self) -> str:
+    return "adagrad_momentum"
+
+  def get_optimizer_primitive(self):
+    return _primitive("sparse_dense_matmul_grad_with_adagrad_momentum")
+
+
+class FTRLOptimizerSpec(OptimizerSpec):
+  """Follow-the-regularized-leader with per-coordinate learning rates.
+
+  Mirrors the reference's FTRLOptimizerSpec (lib/nn/embedding_spec.py:652-742); the update is in
+  lib/core/primitives/sparse_dense_matmul_grad_with_ftrl.py:275-334.
+  """
+
+  def __init__(self, learning_rate=0.01, learning_rate_power: float = -0.5, l1_regularization_strength: float = 0.0,
+               l2_regularization_strength: float = 0.0, beta: float = 0.0, initial_accumulator_value: float = 0.1,
+               initial_linear_value: float = 0.0, multiply_linear_by_learning_rate: bool = False):
+    super().__init__(learning_rate)
+    self.learning_rate_power = learning_rate_power
+    self.l1_regularization_strength = l1_regularization_strength
+    self.l2_regularization_strength = l2_regularization_strength
+    self.beta = beta
+    self.initial_accumulator_value = initial_accumulator_value
+    self.initial_linear_value = initial_linear_value
+    self.multiply_linear_by_learning_rate = multiply_linear_by_learning_rate
+
+  def slot_variables_initializers(self):
+    return FTRLSlotVariables(accumulator=initializers.constant(float(self.initial_accumulator_value)),
+                             linear=initializers.constant(float(self.initial_linear_value)))
+
+  def get_hyperparameters(self, step=None):
+    return (self.get_learning_rate(step), _f32(self.learning_rate_power), _f32(self.l1_regularization_strength),
+            _f32(self.l2_regularization_strength), _f32(self.beta))
+
+  def __hash__(self) -> int:
+    return hash((self.learning_rate, self.learning_rate_power, self.l1_regularization_strength,
+                 self.l2_regularization_strength, self.beta, self.initial_accumulator_value,
+                 self.initial_linear_value, self.multiply_linear_by_learning_rate))
+
+  def short_name(self) -> str:
+    return "ftrl"
+
+  def get_optimizer_primitive(self):
+    return _primitive("sparse_dense_matmul_grad_with_ftrl")
+
+
+class LaPropOptimizerSpec(OptimizerSpec):
+  """LaProp: RMS-normalised gradient, then momentum (https://arxiv.org/abs/2002.04839).
+
+  Mirrors the reference's LaPropOptimizerSpec (lib/nn/embedding_spec.py:744-831): the decay rate of
+  the second moment carries the bias correction, b2 (1 - b2^step) / (1 - b2^(step + 1)).
+  """
+
+  def __init__(self, learning_rate=0.001, b1: float = 0.9, b2: float = 0.95, eps: float = 1e-30,
+               rms_clip_threshold: float | None = None, initial_slot_value: float = 0.0):
+    super().__init__(learning_rate)
+    self.b1 = b1
+    self.b2 = b2
+    self.eps = eps
+    if rms_clip_threshold is not None:
+      raise ValueError("rms_clip_threshold is not yet supported in LaProp optimizer.")
+    self.initial_slot_value = initial_slot_value
+
+  def slot_variables_initializers(self):
+    return LaPropSlotVariables(mu=initializers.constant(float(self.initial_slot_value)),
+                               nu=initializers.constant(float(self.initial_slot_value)))
+
+  def get_decay_rate(self, step=None) -> np.ndarray:
+    if step is None:
+      return _f32(self.b2)
+    step = np.asarray(step, dtype=np.float64)
+    return _f32(self.b2 * (1.0 - np.power(self.b2, step)) / (1.0 - np.power(self.b2, step + 1.0)))
+
+  def get_hyperparameters(self, step=None):
+    return (self.get_learning_rate(step), _f32(self.b1), self.get_decay_rate(step), _f32(self.eps))
+
+  def __hash__(self) -> int:
+    return hash((self.learning_rate, self.b1, self.b2, self.eps, self.initial_slot_value))
+
+  def short_name(self) -> str:
+    return "laprop"
+
+  def get_optimizer_primitive(self):
+    return _primitive("sparse_dense_matmul_grad_with_laprop")
+
+
+class F2AOptimizerSpec(OptimizerSpec):
+  """Frequency-aware Adagrad: rows that are updated rarely get a larger step.
+
+  multiplier = min((max(global_step, 1) / (local_step + 1))^rho, max_lr_multiplier).  Mirrors the
+  reference's F2AOptimizerSpec (lib/nn/embedding_spec.py:833-917).
+  """
+
+  def __init__(self, learning_rate=0.01, rho: float = 0.5, initial_accumulator_value: float = 0.1,
+               initial_local_step_value: float = 0.0, l1_regularization_strength: float = 0.0,
+               l2_regularization_strength: float = 0.0, max_lr_multiplier: float = 1e6):
+    super().__init__(learning_rate)
+    self.rho = rho
+    self.initial_accumulator_value = initial_accumulator_value
+    self.initial_local_step_value = initial_local_step_value
+    self.l1_regularization_strength = l1_regularization_strength
+    self.l2_regularization_strength = l2_regularization_strength
+    self.max_lr_multiplier = max_lr_multiplier
+
+  def slot_variables_initializers(self):
+    return F2ASlotVariables(accumulator=initializers.constant(float(self.initial_accumulator_value)),
+                            local_step=initializers.constant(float(self.initial_local_step_value)))
+
+  def get_hyperparameters(self, step=None):
+    if step is None:
+      step = 0
+    return (self.get_learning_rate(step), _f32(self.rho), _f32(self.l1_regularization_strength),
+            _f32(self.l2_regularization_strength), _f32(self.max_lr_multiplier), _f32(step))
+
+  def __hash__(self) -> int:
+    return hash((self.learning_rate, self.rho, self.initial_accumulator_value, self.initial_local_step_value,
+                 self.l1_regularization_strength, self.l2_regularization_strength, self.max_lr_multiplier))
+
+  def short_name(self) -> str:
+    return "f2a"
+
+  def get_optimizer_primitive(self):
+    return _primitive("sparse_dense_matmul_grad_with_f2a")
 
 
 @dataclasses.dataclass(eq=True, frozen=True)

@@ -14,6 +14,11 @@ CPU expected-value code of the reference's own tests, which this file restates:
              update body of sparse_dense_matmul_grad_with_adagrad.py:206-226
 * Adam     - .../sparse_dense_matmul_grad_with_adam_test.py:403-437 and
              sparse_dense_matmul_grad_with_adam.py:296-341
+* AdagradMomentum / FTRL / LaProp / F2A - the per-row update bodies of
+             sparse_dense_matmul_grad_with_{adagrad_momentum,ftrl,laprop,f2a}.py (lines cited at
+             each function), which are also the formulas of their tests' CPU expectations
+             (tests/sparse_dense_matmul_grad_with_ftrl_test.py:235-320,
+             ..._laprop_test.py:483-515, tolerance atol=1e-5 there)
 * clipping - primitives/utils.py:24-59 (table only)
 
 Everything is float32; sums run in buffer order (device, SparseCore, partition,
@@ -124,6 +129,71 @@ def apply_adam(table, mom, vel, g, touched, alpha_t, beta_1, beta_2, eps_hat, lo
   return (np.where(m, new, table).astype(np.float32),
           np.where(m, m_new, mom).astype(np.float32),
           np.where(m, v_new, vel).astype(np.float32))
+
+
+def _lazy(touched, new, old):
+  return np.where(touched[..., None], new, old).astype(np.float32)
+
+
+def apply_adagrad_momentum(table, acc, mom, g, touched, lr, momentum, beta2, eps, exponent, use_nesterov,
+                           lo=None, hi=None):
+  """sparse_dense_matmul_grad_with_adagrad_momentum.py:262-308 of the reference, on touched rows."""
+  f = np.float32
+  g2 = g * g
+  acc_new = acc + g2 if f(beta2) == f(1.0) else f(beta2) * acc + (f(1.0) - f(beta2)) * g2
+  scaled = np.power(acc_new + f(eps), f(-1.0) / f(exponent), dtype=np.float32) * g
+  mom_new = f(momentum) * mom + scaled
+  update = f(momentum) * mom_new + scaled if use_nesterov else mom_new
+  new = _clip(table - f(lr) * update, lo, hi)
+  return _lazy(touched, new, table), _lazy(touched, acc_new, acc), _lazy(touched, mom_new, mom)
+
+
+def apply_ftrl(table, acc, linear, g, touched, lr, lr_power, l1, l2, beta, multiply_linear_by_learning_rate=False,
+               lo=None, hi=None):
+  """sparse_dense_matmul_grad_with_ftrl.py:275-334 of the reference, on touched rows."""
+  f = np.float32
+  lr, l1, l2, beta = f(lr), f(l1), f(l2), f(beta)
+  with np.errstate(divide="ignore", invalid="ignore"):
+    acc_new = acc + g * g
+    p_old = np.power(acc, -f(lr_power), dtype=np.float32)
+    p_new = np.power(acc_new, -f(lr_power), dtype=np.float32)
+    delta_p = p_new - p_old
+    if multiply_linear_by_learning_rate:
+      linear_new = (linear + lr * g) - delta_p * table
+      scale = lr
+      denom = (p_new + f(2.0) * (lr * l2)) + beta
+    else:
+      linear_new = (linear + g) - (delta_p / lr) * table
+      scale = f(1.0)
+      denom = (p_new + beta) / lr + f(2.0) * l2
+    l1s = l1 * scale
+    numer = -linear_new if l1 == 0 else np.clip(linear_new, -l1s, l1s) - linear_new
+    new = _clip((numer / denom).astype(np.float32), lo, hi)
+  return _lazy(touched, new, table), _lazy(touched, acc_new, acc), _lazy(touched, linear_new, linear)
+
+
+def apply_laprop(table, mu, nu, g, touched, lr, b1, decay_rate, eps, lo=None, hi=None):
+  """sparse_dense_matmul_grad_with_laprop.py:294-335 of the reference, on touched rows."""
+  f = np.float32
+  with np.errstate(divide="ignore", invalid="ignore"):
+    g2 = g * g + f(eps)
+    nu_new = nu * f(decay_rate) + (f(1.0) - f(decay_rate)) * g2
+    update = g / np.sqrt(nu_new)
+    update = f(b1) * mu + np.sqrt(f(1.0) - f(b1) * f(b1), dtype=np.float32) * update
+    new = _clip(table - f(lr) * update, lo, hi)
+  return _lazy(touched, new, table), _lazy(touched, update, mu), _lazy(touched, nu_new, nu)
+
+
+def apply_f2a(table, acc, local_step, g, touched, lr, rho, l1, l2, max_lr_multiplier, global_step, lo=None, hi=None):
+  """sparse_dense_matmul_grad_with_f2a.py:257-285 of the reference, on touched rows."""
+  f = np.float32
+  step_new = local_step + f(1.0)
+  ratio = np.maximum(f(global_step), f(1.0)) / step_new
+  fa = np.minimum(np.power(ratio, f(rho), dtype=np.float32), f(max_lr_multiplier))
+  acc_new = acc + g * g
+  update = (g * fa) / np.sqrt(acc_new) + (f(l1) * np.sign(table) + f(l2) * table)
+  new = _clip(table - f(lr) * update, lo, hi)
+  return _lazy(touched, new, table), _lazy(touched, acc_new, acc), _lazy(touched, step_new, local_step)
 
 
 def adam_hyperparameters(lr, beta_1, beta_2, eps, step):

@@ -11,6 +11,7 @@ import cases
 from oracle import lookup_oracle as lo
 from jax_tpu_embedding.sparsecore.lib.nn import embedding
 from jax_tpu_embedding.sparsecore.lib.nn import embedding_spec
+from jax_tpu_embedding.sparsecore.lib.nn import initializers
 from jax_tpu_embedding.sparsecore.lib.nn import table_stacking
 
 pytestmark = pytest.mark.gpu
@@ -117,3 +118,57 @@ def test_update_preprocessing_parameters_roundtrip():
                                                                num_sc_per_device=2)
   assert stats2.id_drop_counters["table_0"] == 0
   assert pre.lhs_embedding_ids["table_0"].shape[0] == spec.suggested_coo_buffer_size_per_device
+
+
+@pytest.mark.parametrize("kind", ["adagrad_momentum", "ftrl", "laprop", "f2a"])
+def test_two_slot_optimizers_through_the_api(kind):
+  """Variables created by init_embedding_variables, one update through the public API, checked
+  against the float64 definition of each optimizer (fresh slots: accumulator 0.1 or 0, others 0)."""
+  import torch
+
+  opt = {"adagrad_momentum": embedding_spec.AdagradMomentumOptimizerSpec(learning_rate=0.05, momentum=0.9, use_nesterov=True),
+         "ftrl": embedding_spec.FTRLOptimizerSpec(learning_rate=0.05, l1_regularization_strength=0.001,
+                                                  l2_regularization_strength=0.01, beta=0.1,
+                                                  multiply_linear_by_learning_rate=True),
+         "laprop": embedding_spec.LaPropOptimizerSpec(learning_rate=0.01, b1=0.9, b2=0.95, eps=1e-12),
+         "f2a": embedding_spec.F2AOptimizerSpec(learning_rate=0.05, rho=0.5, l2_regularization_strength=0.01)}[kind]
+  table = embedding_spec.TableSpec(name="t", vocabulary_size=500, embedding_dim=16,
+                                   initializer=initializers.normal(0.05), optimizer=opt, combiner="sum",
+                                   max_ids_per_partition=4096, max_unique_ids_per_partition=4096)
+  feature = embedding_spec.FeatureSpec(name="f", table_spec=table, input_shape=[128, 3], output_shape=[128, 16])
+  embedding.prepare_feature_specs_for_training([feature], 1, 2)
+  variables = embedding.init_embedding_variables(7, [table], 1, num_sparsecore_per_device=2)
+  name = table.stacked_table_spec.stack_name
+  assert type(variables[name].slot)._fields == type(opt.slot_variables_initializers())._fields
+  rng = np.random.default_rng(3)
+  ids = rng.integers(0, 500, size=(128, 3)).astype(np.int32)
+  grad = (rng.normal(size=(128, 16)) * 1e-2).astype(np.float32)
+  before = table_stacking.unshard_and_unstack_tables({"t": table}, {name: variables[name].table.cpu().numpy()}, 2)["t"]
+  pre, _ = embedding.preprocess_sparse_dense_matmul_input([ids], None, [feature], 1, 1, num_sc_per_device=2)
+  updated = embedding.tpu_sparse_dense_matmul_grad([torch.from_numpy(grad).cuda()], pre, variables, [feature],
+                                                   global_device_count=1, num_sc_per_device=2, step=4)
+  after = table_stacking.unshard_and_unstack_tables({"t": table}, {name: updated[name].table.cpu().numpy()}, 2)["t"]
+  g = np.zeros((500, 16))
+  for s in range(128):
+    for j in range(3):
+      g[ids[s, j]] += grad[s]
+  touched = np.zeros(500, bool)
+  touched[ids.reshape(-1)] = True
+  w = before.astype(np.float64)
+  if kind == "adagrad_momentum":
+    s = g / np.sqrt(0.1 + g * g + 1e-10)
+    want = w - 0.05 * (0.9 * s + s)
+  elif kind == "ftrl":
+    a1 = 0.1 + g * g
+    dp = np.sqrt(a1) - np.sqrt(0.1)
+    lin = 0.05 * g - dp * w
+    want = (np.clip(lin, -0.001 * 0.05, 0.001 * 0.05) - lin) / (np.sqrt(a1) + 2 * 0.05 * 0.01 + 0.1)
+  elif kind == "laprop":
+    decay = float(opt.get_decay_rate(4))
+    nu = (1 - decay) * (g * g + 1e-12)
+    want = w - 0.01 * np.sqrt(1 - 0.81) * g / np.sqrt(nu)
+  else:
+    fa = min((4.0 / 1.0) ** 0.5, 1e6)
+    want = w - 0.05 * (g * fa / np.sqrt(0.1 + g * g) + 0.01 * w)
+  want = np.where(touched[:, None], want, w)
+  np.testing.assert_allclose(after, want, rtol=3e-5, atol=1e-7)

@@ -113,6 +113,53 @@ def test_backward_matches_oracle(case, opt, clip):
     np.testing.assert_array_equal(got[0].cpu().numpy().reshape(shards.shape)[untouched], shards[untouched])
 
 
+_TWO_SLOT = [
+    ("adagrad_momentum", (0.05, 0.9, 1.0, 1e-10, 2.0, False), {}),
+    ("adagrad_momentum", (0.05, 0.8, 0.95, 1e-6, 3.0, True), {}),
+    ("ftrl", (0.05, -0.5, 0.0, 0.0, 0.0), {"multiply_linear_by_learning_rate": False}),
+    ("ftrl", (0.05, -0.5, 0.001, 0.01, 0.1), {"multiply_linear_by_learning_rate": True}),
+    ("ftrl", (0.05, -0.4, 0.002, 0.0, 0.0), {"multiply_linear_by_learning_rate": False}),
+    ("laprop", (0.01, 0.9, 0.73, 1e-30), {}),
+    ("f2a", (0.05, 0.5, 0.001, 0.002, 1e6, 40.0), {}),
+]
+
+
+@pytest.mark.parametrize("clip", [None, (-0.012, 0.011)])
+@pytest.mark.parametrize("which", range(len(_TWO_SLOT)))
+@pytest.mark.parametrize("case", [c for c in CASES if c.name in ("dense_single_hot_zipf", "mean_unity_dups", "sqrtn_unity")],
+                         ids=lambda c: c.name)
+def test_two_slot_optimizers_match_oracle(case, which, clip):
+  """AdagradMomentum, FTRL, LaProp and F2A epilogues of the fused update."""
+  import importlib
+  import torch
+
+  name, hyper, flags = _TWO_SLOT[which]
+  prim = getattr(importlib.import_module(
+      f"jax_tpu_embedding.sparsecore.lib.core.primitives.sparse_dense_matmul_grad_with_{name}"),
+      f"tpu_sparse_dense_matmul_grad_with_{name}_primitive")
+  apply = getattr(lo, f"apply_{name}")
+  rng = np.random.default_rng(17)
+  for st in _setup(case).values():
+    shards = st["shards"]
+    g, touched = lo.table_gradient(st["csr"], st["grads"], shards.shape, num_sc_per_device=case.num_sc_per_device)
+    lo_, hi_ = clip if clip else (None, None)
+    slot0 = rng.uniform(0.05, 0.2, size=shards.shape).astype(np.float32)
+    slot1 = rng.uniform(0.0, 3.0 if name == "f2a" else 1e-2, size=shards.shape).astype(np.float32)
+    if name == "f2a":
+      slot1 = np.floor(slot1)
+    dev = lambda a: torch.from_numpy(a.reshape(-1, a.shape[-1]).copy()).cuda()
+    grad = torch.from_numpy(np.concatenate(st["grads"])).cuda()
+    want = apply(shards, slot0, slot1, g, touched, *hyper, *flags.values(), lo_, hi_)
+    operands = [np.float32(h) if not isinstance(h, bool) else np.bool_(h) for h in hyper]
+    got = prim.bind(*st["flat"], np.int32(1), dev(shards), dev(slot0), dev(slot1), grad, *operands,
+                    **dict(_kw(case, st["spec"]), min_value=lo_, max_value=hi_, **flags))
+    for a, b in zip(got, want):
+      assert_close(a.cpu().numpy(), b)
+    untouched = ~touched
+    for a, b in zip(got, (shards, slot0, slot1)):
+      np.testing.assert_array_equal(a.cpu().numpy().reshape(shards.shape)[untouched], b[untouched])
+
+
 def test_backward_is_reproducible_and_hot_rows():
   """One row hit by thousands of entries: chunked partial sums stay deterministic and accurate."""
   import torch

@@ -128,3 +128,29 @@ def test_dense_device_inputs_take_the_cached_plan(weighted, stack):
     _compare(case, general, want)
   got[0]["extra"] = None
   assert got[0].token is None
+
+
+def test_sparse_coo_input_equals_ragged_input():
+  """The same bags as sparse tensors (indices, values, dense shape) give the same buffers as ragged rows."""
+  case = cases.make_case("coo", seed=77, batch=64, num_sc_per_device=2, combiner="mean", stack=True, max_ids=2048,
+                         max_unique=2048,
+                         tables=[dict(vocab=900, dim=16, features=[dict(kind="ragged", min_len=0, max_len=7)]),
+                                 dict(vocab=300, dim=16, features=[dict(kind="ragged", max_len=4, dist="zipf")])])
+  indices, values, shapes = [], [], []
+  for feat in case.features:
+    idx = [(r, j) for r, row in enumerate(feat) for j in range(len(row))]
+    indices.append(np.asarray(idx, dtype=np.int64).reshape(-1, 2))
+    values.append(np.concatenate([np.asarray(row, np.int32) for row in feat]))
+    shapes.append(np.asarray([len(feat), max(len(row) for row in feat)], dtype=np.int64))
+  kw = dict(num_sc_per_device=2)
+  got = pip.preprocess_sparse_dense_matmul_sparse_coo_input(indices, values, shapes, case.feature_specs, 1, 1, **kw)
+  want = ob.oracle_preprocess(case.features, None, case.feature_specs, 1, 1, **kw)
+  _compare(case, got, want)
+  pre, stats = embedding.preprocess_sparse_dense_matmul_input_from_sparse_tensor(
+      indices, values, shapes, case.feature_specs, 1, 1, num_sc_per_device=2)
+  for name in want[0]:
+    np.testing.assert_array_equal(pre.lhs_row_pointers[name].cpu().numpy(), want[0][name])
+  assert pre.num_minibatches.dtype == np.int32
+  with pytest.raises(ValueError, match="row-major"):
+    pip.preprocess_sparse_dense_matmul_sparse_coo_input([indices[0][::-1]], [values[0]], [shapes[0]],
+                                                        case.feature_specs[:1], 1, 1, **kw)

@@ -134,6 +134,52 @@ def test_optimizer_hyperparameters():
   assert adam.short_name() == "adam" and es.AdagradOptimizerSpec().short_name() == "adagrad"
 
 
+def test_two_slot_optimizer_specs():
+  """AdagradMomentum, FTRL, LaProp, F2A: hyper-parameter order, slot names, operators, and the oracle's formulas
+  on scalars worked out by hand."""
+  from oracle import lookup_oracle as lo
+
+  am = es.AdagradMomentumOptimizerSpec(learning_rate=0.1, momentum=0.5, use_nesterov=True)
+  hp = am.get_hyperparameters()
+  assert [float(h) for h in hp[:5]] == [np.float32(0.1), 0.5, 1.0, np.float32(1e-10), 2.0] and hp[5].dtype == np.bool_
+  assert am.slot_variables_initializers()._fields == ("accumulator", "momentum") and am.short_name() == "adagrad_momentum"
+  ftrl = es.FTRLOptimizerSpec(learning_rate=0.5, l1_regularization_strength=0.25, beta=1.0)
+  assert [float(h) for h in ftrl.get_hyperparameters()] == [0.5, -0.5, 0.25, 0.0, 1.0]
+  assert ftrl.slot_variables_initializers()._fields == ("accumulator", "linear")
+  lap = es.LaPropOptimizerSpec(b2=0.5)
+  np.testing.assert_allclose(lap.get_hyperparameters(2)[2], 0.5 * (1 - 0.25) / (1 - 0.125), rtol=1e-6)
+  assert float(lap.get_hyperparameters()[2]) == 0.5 and lap.slot_variables_initializers()._fields == ("mu", "nu")
+  with pytest.raises(ValueError, match="rms_clip_threshold"):
+    es.LaPropOptimizerSpec(rms_clip_threshold=1.0)
+  f2a = es.F2AOptimizerSpec()
+  assert float(f2a.get_hyperparameters(7)[5]) == 7.0 and f2a.slot_variables_initializers()._fields == ("accumulator", "local_step")
+  for spec in (am, ftrl, lap, f2a):
+    assert spec.slot_variables_count() == 2
+    assert spec.get_optimizer_primitive().name == f"sparse_dense_matmul_grad_with_{spec.short_name()}_primitive"
+    assert spec == type(spec)(**{k: v for k, v in vars(spec).items()})
+
+  one = lambda v: np.full((1, 1, 1), v, np.float32)
+  hit = np.ones((1, 1), bool)
+  # FTRL, lr 0.5, power -0.5, no regularisation: a' = 1 + 9 = 10... use a = 0, g = 2 -> a' = 4, sqrt = 2,
+  # linear' = 0 + 2 - (2 - 0) / 0.5 * w = 2 - 4 w, w' = -linear' / (2 / 0.5) with w = 1 -> linear' = -2, w' = 0.5.
+  w, a, l = lo.apply_ftrl(one(1.0), one(0.0), one(0.0), one(2.0), hit, 0.5, -0.5, 0.0, 0.0, 0.0)
+  assert (w.item(), a.item(), l.item()) == (0.5, 4.0, -2.0)
+  # LaProp, b1 0, decay 0, eps 0: nu' = g^2, update = g / |g| = 1 -> w' = w - lr.
+  w, mu, nu = lo.apply_laprop(one(1.0), one(5.0), one(7.0), one(-3.0), hit, 0.25, 0.0, 0.0, 0.0)
+  assert (w.item(), mu.item(), nu.item()) == (1.25, -1.0, 9.0)
+  # Adagrad momentum, beta2 1, exponent 2, eps 0, a = 3, g = 1 -> a' = 4, s = 0.5; m' = 0.5 * 2 + 0.5 = 1.5;
+  # nesterov: 0.5 * 1.5 + 0.5 = 1.25 -> w' = 1 - 0.1 * 1.25.
+  w, a, m = lo.apply_adagrad_momentum(one(1.0), one(3.0), one(2.0), one(1.0), hit, 0.1, 0.5, 1.0, 0.0, 2.0, True)
+  np.testing.assert_allclose([w.item(), a.item(), m.item()], [0.875, 4.0, 1.5], rtol=1e-6)
+  # F2A, rho 1, global step 8, local step 3 -> multiplier 8 / 4 = 2; a = 0, g = 3 -> g f / sqrt(a') = 2;
+  # l1 0.5 sign(w) + l2 0.25 w with w = 2 -> 1.0; w' = 2 - 0.1 * 3.
+  w, a, s = lo.apply_f2a(one(2.0), one(0.0), one(3.0), one(3.0), hit, 0.1, 1.0, 0.5, 0.25, 1e6, 8.0)
+  np.testing.assert_allclose([w.item(), a.item(), s.item()], [1.7, 9.0, 4.0], rtol=1e-6)
+  # Untouched rows keep everything.
+  w, a, s = lo.apply_f2a(one(2.0), one(0.0), one(3.0), one(3.0), ~hit, 0.1, 1.0, 0.5, 0.25, 1e6, 8.0)
+  assert (w.item(), a.item(), s.item()) == (2.0, 0.0, 3.0)
+
+
 def test_quantization_config_validation():
   with pytest.raises(ValueError):
     es.QuantizationConfig(min_value=0.0, max_value=1.0, num_buckets=1)
