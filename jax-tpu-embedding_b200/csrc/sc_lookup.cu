@@ -548,14 +548,15 @@ __device__ __forceinline__ float clip(float x, float lo, float hi) {
 //  ftrl (..._ftrl.py:275-334): hyper = {lr, lr_power, l1, l2, beta, multiply_linear_by_lr}; slots (accumulator, linear)
 //  laprop (..._laprop.py:294-335): hyper = {lr, b1, decay_rate, eps}; slots (mu, nu)
 //  f2a (..._f2a.py:257-285): hyper = {lr, rho, l1, l2, max_lr_multiplier, global_step}; slots (accumulator, local_step)
-__device__ __forceinline__ float apply_opt_two_slots(const OptParams& o, float w, float g, float& s0, float& s1) {
+// Not inlined: the common optimizers must not pay for its registers.
+__device__ __noinline__ float3 apply_opt_two_slots(const OptParams& o, float w, float g, float s0, float s1) {
   if (o.kind == SC_OPT_ADAGRAD_MOMENTUM) {
     const float g2 = g * g;
     s0 = o.h2 == 1.0f ? s0 + g2 : o.h2 * s0 + (1.0f - o.h2) * g2;
     const float scaled = powf(s0 + o.h3, -1.0f / o.h4) * g;
     s1 = o.h1 * s1 + scaled;
     const float update = o.h5 != 0.0f ? o.h1 * s1 + scaled : s1;
-    return w - o.h0 * update;
+    return make_float3(w - o.h0 * update, s0, s1);
   }
   if (o.kind == SC_OPT_FTRL) {
     const float acc_new = s0 + g * g;
@@ -567,7 +568,7 @@ __device__ __forceinline__ float apply_opt_two_slots(const OptParams& o, float w
     const float l1 = by_lr ? o.h2 * o.h0 : o.h2;
     const float numer = o.h2 == 0.0f ? -s1 : fminf(fmaxf(s1, -l1), l1) - s1;
     const float denom = by_lr ? (p_new + 2.0f * (o.h0 * o.h3)) + o.h4 : (p_new + o.h4) / o.h0 + 2.0f * o.h3;
-    return numer / denom;
+    return make_float3(numer / denom, s0, s1);
   }
   if (o.kind == SC_OPT_LAPROP) {
     const float g2 = g * g + o.h3;
@@ -575,7 +576,7 @@ __device__ __forceinline__ float apply_opt_two_slots(const OptParams& o, float w
     float update = g / sqrtf(s1);
     update = o.h1 * s0 + sqrtf(1.0f - o.h1 * o.h1) * update;
     s0 = update;
-    return w - o.h0 * update;
+    return make_float3(w - o.h0 * update, s0, s1);
   }
   // SC_OPT_F2A
   s1 = s1 + 1.0f;
@@ -583,15 +584,17 @@ __device__ __forceinline__ float apply_opt_two_slots(const OptParams& o, float w
   s0 = s0 + g * g;
   const float sign = w > 0.0f ? 1.0f : (w < 0.0f ? -1.0f : 0.0f);
   const float update = (g * fa) / sqrtf(s0) + (o.h2 * sign + o.h3 * w);
-  return w - o.h0 * update;
+  return make_float3(w - o.h0 * update, s0, s1);
 }
 
-// One optimizer step on one scalar; slot values are updated in place.
+// One optimizer step on one scalar; slot values are updated in place.  NS < 0: any optimizer;
+// otherwise only the optimizers with NS slot variables can occur.
+template <int NS = -1>
 __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g, float& s0, float& s1) {
   float nw;
-  if (o.kind == SC_OPT_SGD) {
+  if (NS == 0 || (NS < 0 && o.kind == SC_OPT_SGD)) {
     nw = w - o.h0 * g;
-  } else if (o.kind == SC_OPT_ADAGRAD) {
+  } else if (NS == 1 || (NS < 0 && o.kind == SC_OPT_ADAGRAD)) {
     s0 = s0 + g * g;
     nw = w - (o.h0 * g) / sqrtf(s0);
   } else if (o.kind == SC_OPT_ADAM) {
@@ -599,7 +602,8 @@ __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g,
     s1 = s1 + (1.0f - o.h2) * (g * g - s1);
     nw = w - (o.h0 * s0) / (sqrtf(s1) + o.h3);
   } else {
-    nw = apply_opt_two_slots(o, w, g, s0, s1);
+    const float3 r = apply_opt_two_slots(o, w, g, s0, s1);
+    nw = r.x; s0 = r.y; s1 = r.z;
   }
   return clip(nw, o.lo, o.hi);
 }
@@ -834,7 +838,7 @@ __global__ void __launch_bounds__(kBlock) bwd_main_kernel(const TableDesc* __res
         const float* gf = reinterpret_cast<const float*>(&acc[k]);
         float dead0 = 0.f, dead1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < W; ++i) wf[i] = apply_opt(ctx.o, wf[i], gf[i], NS >= 1 ? af[i] : dead0, NS >= 2 ? bf[i] : dead1);
+        for (int i = 0; i < W; ++i) wf[i] = apply_opt<NS>(ctx.o, wf[i], gf[i], NS >= 1 ? af[i] : dead0, NS >= 2 ? bf[i] : dead1);
         reinterpret_cast<VT*>(pw)[c] = w[k];
         if (NS >= 1) reinterpret_cast<VT*>(pa)[c] = x0[NS >= 1 ? k : 0];
         if (NS >= 2) reinterpret_cast<VT*>(pb)[c] = x1[NS >= 2 ? k : 0];
@@ -889,19 +893,22 @@ __device__ __forceinline__ float fast_axpy(float a, float g, float x) { return _
 
 // Optimizer step of the pipelined kernel: fused multiply-adds and the hardware reciprocal square
 // root (2 ulp) instead of IEEE sqrt + divide; within 1e-6 relative of apply_opt.
+// EXTRA: the optimizer is one of the two-slot ones beyond Adam (only with NS == 2).
+template <int NS, bool EXTRA>
 __device__ __forceinline__ float apply_opt_fast(const OptParams& o, bool clipped, float w, float g, float& s0, float& s1) {
   float nw;
-  if (o.kind == SC_OPT_SGD) {
+  if (NS == 0) {
     nw = __fmaf_rn(-o.h0, g, w);
-  } else if (o.kind == SC_OPT_ADAGRAD) {
+  } else if (NS == 1) {
     s0 = __fmaf_rn(g, g, s0);
     nw = __fmaf_rn(-(o.h0 * g), rsqrtf(s0), w);
-  } else if (o.kind == SC_OPT_ADAM) {
+  } else if (!EXTRA) {
     s0 = __fmaf_rn(1.0f - o.h1, g - s0, s0);
     s1 = __fmaf_rn(1.0f - o.h2, g * g - s1, s1);
     nw = w - __fdividef(o.h0 * s0, sqrtf(s1) + o.h3);
   } else {
-    nw = apply_opt_two_slots(o, w, g, s0, s1);
+    const float3 r = apply_opt_two_slots(o, w, g, s0, s1);
+    nw = r.x; s0 = r.y; s1 = r.z;
   }
   return clipped ? clip(nw, o.lo, o.hi) : nw;
 }
@@ -922,7 +929,7 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
 // flight, and executes the descriptors of a batch as soon as it has landed -- K float4 per lane
 // from shared memory.  The pipeline is as deep for a chunk of 32 single-entry rows as for one
 // long run, and the bytes in flight per warp do not depend on the optimizer.
-template <int K, int NS, bool REDUCE>
+template <int K, int NS, bool REDUCE, bool EXTRA>
 __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                              float* __restrict__ partial, uint8_t* __restrict__ chunk_flags,
                                                              int ring_floats) {
@@ -1097,7 +1104,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
         float* bf = reinterpret_cast<float*>(&x1);
         const float* gf = reinterpret_cast<const float*>(&acc[k]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
+        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast<NS, EXTRA>(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
         reinterpret_cast<float4*>(pw)[c] = w;
         if (NS >= 1) reinterpret_cast<float4*>(pa)[c] = x0;
         if (NS >= 2) reinterpret_cast<float4*>(pb)[c] = x1;
@@ -1523,16 +1530,16 @@ int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const 
   return SC_OK;
 }
 
-template <int K, int NS, bool REDUCE = false>
+template <int K, int NS, bool REDUCE = false, bool EXTRA = false>
 int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int max_dim,
                    cudaStream_t st) {
   const int ring_floats = pipe_ring_rows(K, NS) * max_dim;
   const size_t smem = (size_t)kPipeWarps * ((size_t)ring_floats * 4 + pipe_list_bytes(K, NS));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE, EXTRA>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   (int)cudaSharedmemCarveoutMaxShared));
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
-  bwd_pipe_kernel<K, NS, REDUCE><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats);
+  bwd_pipe_kernel<K, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats);
   SC_LAUNCH_OK("bwd_pipe_kernel");
   return SC_OK;
 }
@@ -1540,23 +1547,24 @@ int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, cons
 // Update with the cp.async pipeline kernel; K32 = float4 vectors per lane of a full warp.
 template <int K32>
 int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
-                    int max_dim, cudaStream_t st) {
+                    bool extra, int max_dim, cudaStream_t st) {
   int rc;
   if (num_slots == kReduceOnly) rc = launch_pipe_ns<K32, 0, true>(tabs, count, total_chunks, u, max_dim, st);
   else if (num_slots == 0) rc = launch_pipe_ns<K32, 0>(tabs, count, total_chunks, u, max_dim, st);
   else if (num_slots == 1) rc = launch_pipe_ns<K32, 1>(tabs, count, total_chunks, u, max_dim, st);
-  else rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, u, max_dim, st);
+  else if (!extra) rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, u, max_dim, st);
+  else rc = launch_pipe_ns<K32, 2, false, true>(tabs, count, total_chunks, u, max_dim, st);
   if (rc != SC_OK) return rc;
   return launch_fixup<4, K32>(tabs, count, total_chunks, u, st);
 }
 
 inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u,
-                             int num_slots, int max_dim, cudaStream_t st) {
+                             int num_slots, bool extra, int max_dim, cudaStream_t st) {
   const int vecs = (max_dim / 4 + 31) / 32;
-  if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, u, num_slots, max_dim, st);
-  if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, u, num_slots, max_dim, st);
-  if (vecs <= 4) return launch_bwd_pipe<4>(tabs, count, total_chunks, u, num_slots, max_dim, st);
-  return launch_bwd_pipe<8>(tabs, count, total_chunks, u, num_slots, max_dim, st);
+  if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
+  if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
+  if (vecs <= 4) return launch_bwd_pipe<4>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
+  return launch_bwd_pipe<8>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
 }
 
 // SC_BWD_SORT=radix forces the radix sort of the indirect entry list.
@@ -2020,7 +2028,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     SC_LAUNCH_OK("bwd_ranges_kernel");
   }
   const uint32_t total_chunks = (uint32_t)p.total_chunks;
-  if (ring) return dispatch_bwd_pipe(tabs, count, total_chunks, s.update, p.max_slots, p.max_dim, cs);
+  if (ring) return dispatch_bwd_pipe(tabs, count, total_chunks, s.update, p.max_slots, p.kind >= SC_OPT_ADAGRAD_MOMENTUM, p.max_dim, cs);
 #define SC_BWD_CALL(W, K, G) launch_bwd<W, K, G>(tabs, count, total_chunks, s.update, p.max_slots, cs)
   SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_BWD_CALL);
 #undef SC_BWD_CALL
@@ -2193,7 +2201,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items
   SC_LAUNCH_OK("stage_keys_kernel");
   stage_meta_kernel<<<slot_blocks, kBlock, 0, cs>>>(tabs, n, total_slots, s.keys, s.outs);
   SC_LAUNCH_OK("stage_meta_kernel");
-  return dispatch_bwd_pipe(tabs, n, (uint32_t)p.chunks, s.update, kReduceOnly, p.max_dim, cs);
+  return dispatch_bwd_pipe(tabs, n, (uint32_t)p.chunks, s.update, kReduceOnly, false, p.max_dim, cs);
 }
 
 // ---- single-table entry points: groups of one ---------------------------------------------
@@ -2318,7 +2326,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(base);
   if (w == 4 && pipe_enabled() && aligned16(activation_grad) && aligned16(pool_host[0]) && aligned16(pool_host[1]) &&
       aligned16(pool_host[2]))
-    return dispatch_bwd_pipe(tabs, 1, chunks, u, nslots, v.dim, cs);
+    return dispatch_bwd_pipe(tabs, 1, chunks, u, nslots, kind >= SC_OPT_ADAGRAD_MOMENTUM, v.dim, cs);
 #define SC_STATIC_CALL(W, K, G) launch_bwd<W, K, G>(tabs, 1, chunks, u, nslots, cs)
   SC_SHAPE_SWITCH(w, k, g, SC_STATIC_CALL);
 #undef SC_STATIC_CALL

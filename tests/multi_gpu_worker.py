@@ -32,12 +32,14 @@ def main():
   distributed.init()
   c = world
 
-  for optimizer, combiner, weights in (("adagrad", "mean", None), ("sgd", "sum", True), ("adam", "sqrtn", None)):
+  # Row lengths 128, 64 and 32 floats: one, two and four rows per warp instruction in the update kernels.
+  for optimizer, combiner, weights, dim in (("adagrad", "mean", None, 128), ("sgd", "sum", True, 64),
+                                            ("adam", "sqrtn", None, 32)):
     case = cases.make_case(
         "dist", seed=4040 + c, global_device_count=c, local_device_count=c, batch=256 * c, combiner=combiner,
         optimizer=optimizer, weights=weights, stack=True, max_ids=4096, max_unique=4096, dup_prob=0.1,
-        tables=[dict(vocab=3000, dim=128, features=[dict(kind="ragged", max_len=12, dist="zipf", a=1.05)]),
-                dict(vocab=500, dim=128, features=[dict(kind="dense", valency=3)])])
+        tables=[dict(vocab=3000, dim=dim, features=[dict(kind="ragged", max_len=12, dist="zipf", a=1.05)]),
+                dict(vocab=500, dim=dim, features=[dict(kind="dense", valency=3)])])
     specs = case.feature_specs
     want = ob.oracle_preprocess(case.features, case.weights, specs, c, c, num_sc_per_device=1, has_leading_dimension=True)
     name = next(iter(want[0]))

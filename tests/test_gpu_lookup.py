@@ -183,7 +183,7 @@ def test_backward_is_reproducible_and_hot_rows():
 
 
 @pytest.mark.parametrize("opt", ["sgd", "adagrad", "adam"])
-@pytest.mark.parametrize("dim", [3, 6, 20, 30, 50, 100, 130, 256, 384, 512, 1024])
+@pytest.mark.parametrize("dim", [3, 6, 20, 30, 32, 48, 50, 64, 100, 130, 256, 384, 512, 1024])
 def test_row_length_classes(dim, opt):
   """Every row-length variant of the kernels (odd dims included) with 0, 1 and 2 slot variables."""
   import torch
@@ -233,6 +233,47 @@ def test_forward_long_bags():
     got = sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.bind(
         *st["flat"], np.int32(1), table, device_batch_size=st["bdev"], **_kw(case, st["spec"]))
     np.testing.assert_array_equal(got.cpu().numpy(), want)
+
+
+def test_hot_rows_over_several_sparsecores():
+  """Rows hit by thousands of entries spread over four SparseCore slices: the entry list is ordered by the
+  counting sort (long-row path included) and must equal the radix-sorted order bit for bit."""
+  import os
+  import subprocess
+  import sys
+  import torch
+
+  case = cases.make_case("hot4", seed=12, num_sc_per_device=4, optimizer="adagrad", batch=8192, tables=[
+      dict(vocab=64, dim=128, features=[dict(kind="dense", valency=1, dist="zipf", a=2.0)])])
+  st = _setup(case)["table_0"]
+  shards = st["shards"]
+  g, touched = lo.table_gradient(st["csr"], st["grads"], shards.shape, num_sc_per_device=4)
+  acc = np.full(shards.shape, 0.1, np.float32)
+  want = lo.apply_adagrad(shards, acc, g, touched, 0.01)
+  dev = lambda a: torch.from_numpy(a.reshape(-1, a.shape[-1]).copy()).cuda()
+  outs = []
+  for _ in range(2):
+    outs.append(sparse_dense_matmul_grad_with_adagrad.tpu_sparse_dense_matmul_grad_with_adagrad_primitive.bind(
+        *st["flat"], np.int32(1), dev(shards), dev(acc), torch.from_numpy(np.concatenate(st["grads"])).cuda(),
+        np.float32(0.01), **_kw(case, st["spec"])))
+  assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+  assert_close(outs[0][0].cpu().numpy(), want[0])
+  assert_close(outs[0][1].cpu().numpy(), want[1])
+  np.save("/tmp/sc_hot4_table.npy", outs[0][0].cpu().numpy())
+  # The same update with the radix sort (chosen per process) in a child process.
+  code = (
+      "import sys, numpy as np, torch; sys.path[:0] = %r\n"
+      "import cases, test_gpu_lookup as t\n"
+      "from jax_tpu_embedding.sparsecore.lib.core.primitives import sparse_dense_matmul_grad_with_adagrad as m\n"
+      "case = cases.make_case('hot4', seed=12, num_sc_per_device=4, optimizer='adagrad', batch=8192, tables=["
+      "dict(vocab=64, dim=128, features=[dict(kind='dense', valency=1, dist='zipf', a=2.0)])])\n"
+      "st = t._setup(case)['table_0']; sh = st['shards']; acc = np.full(sh.shape, 0.1, np.float32)\n"
+      "dev = lambda a: torch.from_numpy(a.reshape(-1, a.shape[-1]).copy()).cuda()\n"
+      "out = m.tpu_sparse_dense_matmul_grad_with_adagrad_primitive.bind(*st['flat'], np.int32(1), dev(sh), dev(acc), "
+      "torch.from_numpy(np.concatenate(st['grads'])).cuda(), np.float32(0.01), **t._kw(case, st['spec']))\n"
+      "assert np.array_equal(out[0].cpu().numpy(), np.load('/tmp/sc_hot4_table.npy'))\n" % (sys.path,))
+  run = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, SC_BWD_SORT="radix"), capture_output=True, text=True)
+  assert run.returncode == 0, run.stderr[-2000:]
 
 
 def test_rank1_table():
