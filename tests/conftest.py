@@ -11,7 +11,8 @@ for p in (ROOT, PKG, os.path.dirname(os.path.abspath(__file__))):
   if p not in sys.path:
     sys.path.insert(0, p)
 
-REFERENCE = "/root/reference"
+# Checkout of the reference project: $SC_REFERENCE_ROOT, else a "reference" directory beside this repository.
+REFERENCE = os.environ.get("SC_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
 
 
 def pytest_configure(config):

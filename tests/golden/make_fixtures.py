@@ -36,7 +36,7 @@ def record_reference_preprocessing(reference_root):
   import reference_harness as rh
   from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
 
-  rh.REFERENCE = reference_root
+  rh.set_reference_root(reference_root)
   calls = []
 
   def recording_backend(features, feature_weights, feature_specs, local_device_count, global_device_count, **kw):
@@ -152,7 +152,7 @@ def known_answer_lookup_cases():
 
 if __name__ == "__main__":
   ap = argparse.ArgumentParser()
-  ap.add_argument("--reference", default="/root/reference")
+  ap.add_argument("--reference", default=os.environ.get("SC_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference")))
   args = ap.parse_args()
   known_answer_lookup_cases()
   record_reference_preprocessing(args.reference)

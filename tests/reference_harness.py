@@ -15,7 +15,8 @@ import sys
 import types
 import unittest
 
-REFERENCE = "/root/reference"
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE = os.environ.get("SC_REFERENCE_ROOT", os.path.join(os.path.dirname(_REPO), "reference"))
 _CORE_TESTS = os.path.join(REFERENCE, "jax_tpu_embedding/sparsecore/lib/core/tests")
 
 
@@ -64,6 +65,12 @@ def load_pybind_test_module(backend):
   sys.modules["jax_tpu_embedding.sparsecore.lib.core.tests"].test_utils = tu
   return _load("reference_pybind_input_preprocessing_test",
                os.path.join(_CORE_TESTS, "pybind_input_preprocessing_test.py"))
+
+
+def set_reference_root(root: str) -> None:
+  global REFERENCE, _CORE_TESTS
+  REFERENCE = root
+  _CORE_TESTS = os.path.join(root, "jax_tpu_embedding/sparsecore/lib/core/tests")
 
 
 def run_cases(module, skip_classes=("MinibatchingNodeTest",)):
