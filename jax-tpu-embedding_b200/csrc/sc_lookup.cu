@@ -589,7 +589,7 @@ __device__ __noinline__ float3 apply_opt_two_slots(const OptParams& o, float w, 
 
 // One optimizer step on one scalar; slot values are updated in place.  NS < 0: any optimizer;
 // otherwise only the optimizers with NS slot variables can occur.
-template <int NS = -1>
+template <int NS = -1, bool EXTRA = true>
 __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g, float& s0, float& s1) {
   float nw;
   if (NS == 0 || (NS < 0 && o.kind == SC_OPT_SGD)) {
@@ -597,7 +597,7 @@ __device__ __forceinline__ float apply_opt(const OptParams& o, float w, float g,
   } else if (NS == 1 || (NS < 0 && o.kind == SC_OPT_ADAGRAD)) {
     s0 = s0 + g * g;
     nw = w - (o.h0 * g) / sqrtf(s0);
-  } else if (o.kind == SC_OPT_ADAM) {
+  } else if (!EXTRA || o.kind == SC_OPT_ADAM) {
     s0 = s0 + (1.0f - o.h1) * (g - s0);
     s1 = s1 + (1.0f - o.h2) * (g * g - s1);
     nw = w - (o.h0 * s0) / (sqrtf(s1) + o.h3);
@@ -683,7 +683,8 @@ __device__ __forceinline__ void load_row(const RowCtx& ctx, int64_t grow, int la
 }
 
 // Applies the optimizer to a row held in registers and stores it (single write per array).
-template <int W, int K>
+// EXTRA = false: the optimizer is known to be sgd, adagrad or adam.
+template <int W, int K, bool EXTRA>
 __device__ __forceinline__ void store_row(const RowCtx& ctx, int64_t grow, int lane, const typename Vec<W>::T (&gsum)[K],
                                           typename Vec<W>::T (&w)[K], typename Vec<W>::T (&x0)[K],
                                           typename Vec<W>::T (&x1)[K]) {
@@ -703,7 +704,7 @@ __device__ __forceinline__ void store_row(const RowCtx& ctx, int64_t grow, int l
     float* bf = reinterpret_cast<float*>(&x1[k]);
     const float* gf = reinterpret_cast<const float*>(&gsum[k]);
 #pragma unroll
-    for (int i = 0; i < W; ++i) wf[i] = apply_opt(ctx.o, wf[i], gf[i], af[i], bf[i]);
+    for (int i = 0; i < W; ++i) wf[i] = apply_opt<-1, EXTRA>(ctx.o, wf[i], gf[i], af[i], bf[i]);
     tw[c] = w[k];
     if (t0) t0[c] = x0[k];
     if (t1) t1[c] = x1[k];
@@ -1182,7 +1183,7 @@ __global__ void __launch_bounds__(kBlock) bwd_group_kernel(const TableDesc* __re
 // starts in this chunk and goes on through the following ones -- chunk by chunk up to the next
 // group boundary, then whole flagged groups, then chunk by chunk to the run's end -- and
 // applies the optimizer once.
-template <int W, int K>
+template <int W, int K, bool EXTRA>
 __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                            const float* __restrict__ partial,
                                                            const uint8_t* __restrict__ chunk_flags,
@@ -1292,7 +1293,7 @@ __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const
     const RowCtx ctx = make_ctx(td);
     VT w[K], x0[K], x1[K];
     load_row<W, K>(ctx, (int64_t)row, lane, w, x0, x1);
-    store_row<W, K>(ctx, (int64_t)row, lane, acc, w, x0, x1);
+    store_row<W, K, EXTRA>(ctx, (int64_t)row, lane, acc, w, x0, x1);
   }
 }
 
@@ -1518,14 +1519,18 @@ struct UpdateScratch {
 inline size_t update_groups(size_t chunks) { return (chunks + 31) / 32; }
 
 template <int W, int K32>
-int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
+int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, bool extra, cudaStream_t st) {
   const unsigned groups = (unsigned)ceil_div(total_chunks, 32);
   bwd_group_kernel<W, K32><<<(unsigned)ceil_div(groups, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_chunks, u.partial,
                                                                                         u.flags, u.group_partial, u.group_flags);
   SC_LAUNCH_OK("bwd_group_kernel");
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
-  bwd_fixup_kernel<W, K32><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
-                                                     u.group_flags);
+  if (extra)
+    bwd_fixup_kernel<W, K32, true><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
+                                                             u.group_flags);
+  else
+    bwd_fixup_kernel<W, K32, false><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
+                                                              u.group_flags);
   SC_LAUNCH_OK("bwd_fixup_kernel");
   return SC_OK;
 }
@@ -1555,7 +1560,7 @@ int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, con
   else if (!extra) rc = launch_pipe_ns<K32, 2>(tabs, count, total_chunks, u, max_dim, st);
   else rc = launch_pipe_ns<K32, 2, false, true>(tabs, count, total_chunks, u, max_dim, st);
   if (rc != SC_OK) return rc;
-  return launch_fixup<4, K32>(tabs, count, total_chunks, u, st);
+  return launch_fixup<4, K32>(tabs, count, total_chunks, u, extra, st);
 }
 
 inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u,
@@ -1595,7 +1600,7 @@ int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, const Up
   SC_LAUNCH_OK("bwd_main_kernel");
   // The fix-up kernel keeps the full warp per row: K32 vectors per lane.
   constexpr int K32 = (K * G + 31) / 32;
-  return launch_fixup<W, K32>(tabs, count, total_chunks, u, st);
+  return launch_fixup<W, K32>(tabs, count, total_chunks, u, true, st);
 }
 
 #define SC_SHAPE_SWITCH_W(W, k, g, CALL)             \
