@@ -722,7 +722,8 @@ struct EntMeta {
   float gain;
 };
 
-// Warp per 32 consecutive entries of one table.  partial[(2 * global_chunk + k) * dim ...]:
+// Warp per 32 consecutive entries of one table.  partial[(2 * global_chunk + k) * pstride ...]
+// (pstride = longest row of the group, so tables of different dims never share a scratch row):
 // k = 0 holds the sum of a run that started in an earlier chunk, k = 1 of a run that continues
 // into the next chunk.  After the lane-parallel metadata phase the warp splits into 32 / G groups
 // of G lanes; each group owns every (32 / G)-th run of the chunk, issues the loads of the run's
@@ -730,7 +731,8 @@ struct EntMeta {
 // single store per array.  NS is the number of slot variables (0 sgd, 1 adagrad, 2 adam).
 template <int W, int K, int G, int NS>
 __global__ void __launch_bounds__(kBlock) bwd_main_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
-                                                          float* __restrict__ partial, uint8_t* __restrict__ chunk_flags) {
+                                                          float* __restrict__ partial, uint8_t* __restrict__ chunk_flags,
+                                                          int pstride) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
   __shared__ EntMeta s_ent[kWarpsPerBlock][32];
@@ -845,7 +847,7 @@ __global__ void __launch_bounds__(kBlock) bwd_main_kernel(const TableDesc* __res
         if (NS >= 2) reinterpret_cast<VT*>(pb)[c] = x1[NS >= 2 ? k : 0];
       }
     } else {
-      VT* dst = reinterpret_cast<VT*>(partial + ((int64_t)2 * gchunk + (is_head ? 1 : 0)) * dim);
+      VT* dst = reinterpret_cast<VT*>(partial + ((int64_t)2 * gchunk + (is_head ? 1 : 0)) * pstride);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int c = gl + k * G;
@@ -933,7 +935,7 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
 template <int K, int NS, bool REDUCE, bool EXTRA>
 __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                              float* __restrict__ partial, uint8_t* __restrict__ chunk_flags,
-                                                             int ring_floats) {
+                                                             int ring_floats, int pstride) {
   constexpr int B = pipe_batch_rows(K);
   constexpr int R = pipe_ring_rows(K, NS);
   constexpr int kListRows = pipe_list_rows(K, NS);
@@ -1077,7 +1079,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
         }
       }
       if (d & kRowPartial) {
-        float4* dst = reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * dim);
+        float4* dst = reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * pstride);
 #pragma unroll
         for (int k = 0; k < K; ++k) {
           const int c = lane + k * 32;
@@ -1137,7 +1139,8 @@ template <int W, int K>
 __global__ void __launch_bounds__(kBlock) bwd_group_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
                                                            const float* __restrict__ partial,
                                                            const uint8_t* __restrict__ chunk_flags,
-                                                           float* __restrict__ group_partial, uint8_t* __restrict__ group_flags) {
+                                                           float* __restrict__ group_partial, uint8_t* __restrict__ group_flags,
+                                                           int pstride) {
   using VT = typename Vec<W>::T;
   const int lane = threadIdx.x & 31;
   const uint32_t group = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -1159,7 +1162,7 @@ __global__ void __launch_bounds__(kBlock) bwd_group_kernel(const TableDesc* __re
     VT p[U][K];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * (c0 + i + u) * dim);
+      const VT* src = reinterpret_cast<const VT*>(partial + (int64_t)2 * (c0 + i + u) * pstride);
 #pragma unroll
       for (int k = 0; k < K; ++k) {
         const int cc = lane + k * 32;
@@ -1171,7 +1174,7 @@ __global__ void __launch_bounds__(kBlock) bwd_group_kernel(const TableDesc* __re
 #pragma unroll
       for (int k = 0; k < K; ++k) Vec<W>::add(acc[k], p[u][k]);
   }
-  VT* dst = reinterpret_cast<VT*>(group_partial + (int64_t)group * dim);
+  VT* dst = reinterpret_cast<VT*>(group_partial + (int64_t)group * pstride);
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const int cc = lane + k * 32;
@@ -1188,7 +1191,7 @@ __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const
                                                            const float* __restrict__ partial,
                                                            const uint8_t* __restrict__ chunk_flags,
                                                            const float* __restrict__ group_partial,
-                                                           const uint8_t* __restrict__ group_flags) {
+                                                           const uint8_t* __restrict__ group_flags, int pstride) {
   using VT = typename Vec<W>::T;
   const int lane = threadIdx.x & 31;
   const uint32_t gchunk = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
@@ -1236,16 +1239,16 @@ __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const
     const uint32_t stop = __ballot_sync(0xffffffffu, !on);  // never 0: the next group is not all on
     n3 = (uint32_t)__ffs(stop);
   }
-  const float* g0 = group_partial + (int64_t)((s1 + n1) / 32u) * dim;
+  const float* g0 = group_partial + (int64_t)((s1 + n1) / 32u) * pstride;
   const uint32_t total = n1 + ng + n3;
   auto row_ptr = [&](uint32_t i) -> const VT* {
-    if (i < n1) return reinterpret_cast<const VT*>(partial + (int64_t)2 * (s1 + i) * dim);
-    if (i < n1 + ng) return reinterpret_cast<const VT*>(g0 + (int64_t)(i - n1) * dim);
-    return reinterpret_cast<const VT*>(partial + (int64_t)2 * (s3 + (i - n1 - ng)) * dim);
+    if (i < n1) return reinterpret_cast<const VT*>(partial + (int64_t)2 * (s1 + i) * pstride);
+    if (i < n1 + ng) return reinterpret_cast<const VT*>(g0 + (int64_t)(i - n1) * pstride);
+    return reinterpret_cast<const VT*>(partial + (int64_t)2 * (s3 + (i - n1 - ng)) * pstride);
   };
   VT acc[K];
   {
-    const VT* src = reinterpret_cast<const VT*>(partial + ((int64_t)2 * gchunk + 1) * dim);
+    const VT* src = reinterpret_cast<const VT*>(partial + ((int64_t)2 * gchunk + 1) * pstride);
 #pragma unroll
     for (int k = 0; k < K; ++k) {
       const int c = lane + k * 32;
@@ -1515,6 +1518,7 @@ struct UpdateScratch {
   uint8_t* flags;        // [chunks] kChunk* flags
   float* group_partial;  // [ceil(chunks / 32)][dim]
   uint8_t* group_flags;  // [ceil(chunks / 32)]
+  int pstride;           // floats between consecutive rows of partial / group_partial: the group's longest row
 };
 inline size_t update_groups(size_t chunks) { return (chunks + 31) / 32; }
 
@@ -1522,15 +1526,15 @@ template <int W, int K32>
 int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, bool extra, cudaStream_t st) {
   const unsigned groups = (unsigned)ceil_div(total_chunks, 32);
   bwd_group_kernel<W, K32><<<(unsigned)ceil_div(groups, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_chunks, u.partial,
-                                                                                        u.flags, u.group_partial, u.group_flags);
+                                                                                        u.flags, u.group_partial, u.group_flags, u.pstride);
   SC_LAUNCH_OK("bwd_group_kernel");
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
   if (extra)
     bwd_fixup_kernel<W, K32, true><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
-                                                             u.group_flags);
+                                                             u.group_flags, u.pstride);
   else
     bwd_fixup_kernel<W, K32, false><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
-                                                              u.group_flags);
+                                                              u.group_flags, u.pstride);
   SC_LAUNCH_OK("bwd_fixup_kernel");
   return SC_OK;
 }
@@ -1544,7 +1548,8 @@ int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, cons
   SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE, EXTRA>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   (int)cudaSharedmemCarveoutMaxShared));
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
-  bwd_pipe_kernel<K, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats);
+  bwd_pipe_kernel<K, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats,
+                                                                          u.pstride);
   SC_LAUNCH_OK("bwd_pipe_kernel");
   return SC_OK;
 }
@@ -1594,9 +1599,9 @@ template <int W, int K, int G>
 int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
                cudaStream_t st) {
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
-  if (num_slots == 0) bwd_main_kernel<W, K, G, 0><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags);
-  else if (num_slots == 1) bwd_main_kernel<W, K, G, 1><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags);
-  else bwd_main_kernel<W, K, G, 2><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags);
+  if (num_slots == 0) bwd_main_kernel<W, K, G, 0><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
+  else if (num_slots == 1) bwd_main_kernel<W, K, G, 1><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
+  else bwd_main_kernel<W, K, G, 2><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
   SC_LAUNCH_OK("bwd_main_kernel");
   // The fix-up kernel keeps the full warp per row: K32 vectors per lane.
   constexpr int K32 = (K * G + 31) / 32;
@@ -1809,6 +1814,7 @@ bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
   s->update.flags = ws.take<uint8_t>((size_t)p.total_chunks + 1);
   s->update.group_partial = ws.take<float>(update_groups(p.total_chunks) * (size_t)p.max_dim + 1);
   s->update.group_flags = ws.take<uint8_t>(update_groups(p.total_chunks) + 1);
+  s->update.pstride = p.max_dim;
   return ws.ok();
 }
 
@@ -2113,6 +2119,7 @@ bool carve_stage(Workspace& ws, const StagePlan& p, StageScratch* s) {
   s->update.flags = ws.take<uint8_t>((size_t)p.chunks + 1);
   s->update.group_partial = ws.take<float>(update_groups(p.chunks) * (size_t)p.max_dim + 1);
   s->update.group_flags = ws.take<uint8_t>(update_groups(p.chunks) + 1);
+  s->update.pstride = p.max_dim;
   return ws.ok();
 }
 
@@ -2308,6 +2315,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   u.group_partial = reinterpret_cast<float*>(base + image + partial_bytes);
   u.flags = reinterpret_cast<uint8_t*>(base + image + partial_bytes + group_bytes);
   u.group_flags = u.flags + chunks;
+  u.pstride = v.dim;
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
   struct { TableDesc td; } host;

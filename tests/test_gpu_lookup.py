@@ -306,3 +306,49 @@ def test_operand_validation():
     bind(*st["flat"], np.int32(1), table, **dict(kw, max_ids_per_partition=0))
   with pytest.raises(ValueError, match="equal rank 1 shapes"):
     bind(st["flat"][0], st["flat"][1][:-8], st["flat"][2], st["flat"][3], np.int32(1), table, **kw)
+
+
+@pytest.mark.parametrize("dims", [(128, 96), (16, 8), (96, 128), (64, 40)])
+@pytest.mark.parametrize("opt", ["sgd", "adagrad", "adam"])
+def test_mixed_dims_in_one_group(dims, opt):
+  """Two tables of different dims in the same row-length class share ONE grouped launch; hot rows of
+  both span several 32-entry chunks, so both use the partial-sum scratch at the same time."""
+  import torch
+  from jax_tpu_embedding.sparsecore.lib.core.primitives import _ops
+
+  prim = {"sgd": sparse_dense_matmul_grad_with_sgd.tpu_sparse_dense_matmul_grad_with_sgd_primitive,
+          "adagrad": sparse_dense_matmul_grad_with_adagrad.tpu_sparse_dense_matmul_grad_with_adagrad_primitive,
+          "adam": sparse_dense_matmul_grad_with_adam.tpu_sparse_dense_matmul_grad_with_adam_primitive}[opt]
+  assert _ops.shape_class(dims[0]) == _ops.shape_class(dims[1])
+  requests, wants, fwd_requests, fwd_wants = [], [], [], []
+  for ti, dim in enumerate(dims):
+    case = cases.make_case(f"mixed{ti}", seed=31 + ti, batch=4096, optimizer="adagrad", tables=[
+        dict(vocab=40, dim=8, features=[dict(kind="dense", valency=1, dist="zipf", a=1.3)])], max_ids=4096, max_unique=4096)
+    st = _setup(case, seed=ti, dim_override=dim)["table_0"]
+    shards = st["shards"]
+    g, touched = lo.table_gradient(st["csr"], st["grads"], shards.shape, num_sc_per_device=1)
+    acc = np.full(shards.shape, 0.1, np.float32)
+    vel = np.full(shards.shape, 1e-4, np.float32)
+    dev = lambda a: torch.from_numpy(a.reshape(-1, a.shape[-1]).copy()).cuda()
+    grad = torch.from_numpy(np.concatenate(st["grads"])).cuda()
+    kw = _kw(case, st["spec"])
+    fwd_requests.append(sparse_dense_matmul_csr.tpu_sparse_dense_matmul_csr_primitive.prepare(
+        *st["flat"], np.int32(1), dev(shards), device_batch_size=st["bdev"], **kw))
+    fwd_wants.append(np.concatenate(lo.forward(st["csr"], shards, num_sc_per_device=1, device_batch_size=st["bdev"])))
+    if opt == "sgd":
+      wants.append(lo.apply_sgd(shards, g, touched, 0.05))
+      requests.append(prim.prepare(*st["flat"], np.int32(1), dev(shards), grad, np.float32(0.05), **kw))
+    elif opt == "adagrad":
+      wants.append(lo.apply_adagrad(shards, acc, g, touched, 0.05))
+      requests.append(prim.prepare(*st["flat"], np.int32(1), dev(shards), dev(acc), grad, np.float32(0.05), **kw))
+    else:
+      hyp = lo.adam_hyperparameters(1e-3, 0.9, 0.999, 1e-8, 2)
+      wants.append(lo.apply_adam(shards, acc, vel, g, touched, *hyp))
+      requests.append(prim.prepare(*st["flat"], np.int32(1), dev(shards), dev(acc), dev(vel), grad, *hyp, **kw))
+  call = _ops.GradGroupCall(requests)
+  assert len(call.groups) == 1, "both tables must travel in one grouped launch"
+  for got_all, want_all in zip(call.run(), wants):
+    for a, b in zip(got_all, want_all):
+      assert_close(a.cpu().numpy(), b)
+  for got, want in zip(_ops.run_forward_group(fwd_requests), fwd_wants):
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
