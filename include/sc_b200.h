@@ -120,6 +120,11 @@ typedef struct {
   int32_t* sample_ids;
   float* gains;
   int32_t* stats;
+  /* Optional (both or neither, device): the forward plan of the emitted buffers, for
+   * sc_fwd_item_t.plan_slots / plan_bags.  plan_slots[nnz] and plan_bags[2 * total_rows]; bag r covers
+   * the activation row `SparseCore * (total_rows / num_sc_per_device) + sample`. */
+  uint32_t* plan_slots;
+  uint32_t* plan_bags;
 } sc_preprocess_item_t;
 
 size_t sc_preprocess_grouped_workspace_bytes(const sc_preprocess_item_t* items, int32_t count);
@@ -192,6 +197,13 @@ typedef struct {
    * per distinct row into the workspace and gathered from there, so a row that many samples of
    * the batch look up crosses NVLink once.  -1: read every shard pointer directly. */
   int32_t local_shard;
+  /* Optional forward plan emitted by sc_preprocess_grouped for the same buffers (both or neither;
+   * device pointers): plan_bags[2 * r], plan_bags[2 * r + 1] delimit, inside plan_slots, the slots of
+   * activation row r in ascending order.  The reference's operator signature carries only the id-major
+   * arrays, so without a plan the sample-major view is rebuilt on every call (one scatter when
+   * csr.max_ids_per_sample == 1, a counting sort otherwise). */
+  const uint32_t* plan_slots;
+  const uint32_t* plan_bags;
 } sc_fwd_item_t;
 
 /* Buffers of one source device as seen from the owner of a shard (peer-mapped device pointers). */

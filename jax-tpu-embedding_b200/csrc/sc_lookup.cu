@@ -118,6 +118,12 @@ struct TableDesc {
   int32_t local_shard;
   const uint32_t* run_ord;
   float* remote_rows;
+  // Forward plan: bags[2 * r] .. bags[2 * r + 1] delimit the entries of local activation row r inside
+  // `plan`, whose values minus plan_bias are slots of this table's buffer in ascending order
+  // (plan == nullptr: the position itself is the value).
+  const uint32_t* plan;
+  const uint32_t* bags;
+  uint32_t plan_bias;
 };
 
 // Index of the table whose [base, next base) range contains x.
@@ -214,12 +220,15 @@ __global__ void fwd_place_kernel(const uint32_t* __restrict__ keys, const uint32
 
 constexpr uint32_t kSerialSortLimit = 64;
 
-// Thread per activation row.  Rows longer than kSerialSortLimit go to big_rows.
+// Thread per activation row.  Rows longer than kSerialSortLimit go to big_rows.  With `bags` the
+// row's (begin, end) pair is stored there as well.
 __global__ void fwd_rowsort_kernel(const uint32_t* __restrict__ offsets, uint32_t total_act, uint32_t* __restrict__ list,
-                                   uint32_t* __restrict__ big_rows, uint32_t* __restrict__ big_count) {
+                                   uint32_t* __restrict__ big_rows, uint32_t* __restrict__ big_count,
+                                   uint32_t* __restrict__ bags) {
   const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= total_act) return;
   const uint32_t begin = offsets[r], n = offsets[r + 1] - begin;
+  if (bags != nullptr) { bags[2 * r] = begin; bags[2 * r + 1] = begin + n; }
   if (n < 2) return;
   if (n > kSerialSortLimit) {
     big_rows[atomicAdd(big_count, 1u)] = r;
@@ -235,10 +244,11 @@ __global__ void fwd_rowsort_kernel(const uint32_t* __restrict__ offsets, uint32_
 }
 
 // Warp per long row (grid-stride over big_rows): stable LSD radix sort of the row's slots, 8 bits
-// per pass, between `list` and `scratch`.
+// per pass, between `list` and `scratch`.  Row r spans [offsets[r * stride], offsets[r * stride + 1]):
+// stride 1 for an offsets array, 2 for (begin, end) pairs.
 __global__ void __launch_bounds__(kBlock) fwd_bigrow_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ list,
                                                             uint32_t* __restrict__ scratch, const uint32_t* __restrict__ big_rows,
-                                                            const uint32_t* __restrict__ big_count, int key_bits) {
+                                                            const uint32_t* __restrict__ big_count, int key_bits, int stride) {
   __shared__ uint32_t bins[kWarpsPerBlock][256];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t warps = gridDim.x * kWarpsPerBlock;
@@ -246,7 +256,7 @@ __global__ void __launch_bounds__(kBlock) fwd_bigrow_kernel(const uint32_t* __re
   const uint32_t todo = *big_count;
   for (uint32_t w = blockIdx.x * kWarpsPerBlock + wib; w < todo; w += warps) {
     const uint32_t r = big_rows[w];
-    const uint32_t begin = offsets[r], n = offsets[r + 1] - begin;
+    const uint32_t begin = offsets[(size_t)r * stride], n = offsets[(size_t)r * stride + 1] - begin;
     uint32_t* src = list + begin;
     uint32_t* dst = scratch + begin;
     for (int shift = 0; shift < key_bits; shift += 8) {
@@ -417,58 +427,73 @@ __global__ void __launch_bounds__(kBlock) fwd_fetch_kernel(const FetchJob* __res
   }
 }
 
-// Resolves the sorted entry `e` of table `td`: byte-free row offset inside its shard (or -1),
-// gain and shard.
-__device__ __forceinline__ void resolve_entry(const TableDesc& td, const uint32_t* __restrict__ slots, uint32_t e,
-                                              int64_t* off, float* gain, int* shard) {
+// Resolves position `pos` of table `td`'s forward plan: the table row to read (in its shard, or
+// its staged copy when the shard is remote; nullptr when the entry contributes nothing) and the gain.
+__device__ __forceinline__ const float* resolve_entry(const TableDesc& td, uint32_t pos, float* gain) {
   const CsrView& v = td.v;
-  const int q = (int)(slots[e] - td.slot_base);
-  const int s = q / v.coo_per_sc;
-  const int g = v.P == 1 ? 0 : slot_shard(v, s, q - s * v.coo_per_sc);
+  const int q = (int)((td.plan != nullptr ? td.plan[pos] : pos) - td.plan_bias);
+  int g = 0;
+  if (v.P > 1) {
+    const int s = q / v.coo_per_sc;
+    g = slot_shard(v, s, q - s * v.coo_per_sc);
+  }
   const int id = v.ids[q];
   *gain = v.gains[q];
-  *shard = g;
-  *off = (g >= 0 && id >= 0 && (int64_t)id < v.rows_per_shard) ? (int64_t)id * v.dim : -1;
-  if (td.local_shard >= 0 && g >= 0 && g != td.local_shard && *off >= 0) {
-    *shard = -1;  // read the staged copy of the remote row
-    *off = (int64_t)td.run_ord[slots[e]] * v.dim;
-  }
+  if (g < 0 || id < 0 || (int64_t)id >= v.rows_per_shard) return nullptr;
+  if (td.local_shard >= 0 && g != td.local_shard) return td.remote_rows + (int64_t)td.run_ord[td.slot_base + (uint32_t)q] * v.dim;
+  return td.table[g] + (int64_t)id * v.dim;
+}
+
+// Single-valent inputs (at most one entry per activation row): the plan is the identity and a bag
+// is (slot, slot + 1), stored with one 8-byte write.  `bags` must be zero beforehand.
+__global__ void fwd_single_bags_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+                                       uint2* __restrict__ bags) {
+  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= total_slots) return;
+  const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
+  const CsrView& v = tabs[t].v;
+  const int q = (int)(gq - tabs[t].slot_base);
+  const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
+  if (slot_shard(v, s, q - s * v.coo_per_sc) < 0) return;
+  const int sid = v.sids[q];
+  if (sid >= 0 && sid < v.bsc) bags[tabs[t].act_base + (uint32_t)(s * v.bsc + sid)] = make_uint2(gq, gq + 1u);
 }
 
 // What a forward warp knows about one of its 32 activation rows.
 struct RowMeta {
-  int64_t off;       // first entry: float offset of the table row inside its shard, -1 if none
+  const float* src;  // table row of the first entry, nullptr if it contributes nothing
   uint32_t begin, end;
   int32_t table;
-  int32_t shard;
   float gain;
-  int32_t pad;
 };
 
-// One warp per 32 consecutive global activation rows.  Lane l first resolves the range and the
-// first entry of row r0 + l, so the dependent index loads of 32 rows overlap.  The warp is then
-// split into 32 / G groups of G lanes; each group owns every (32 / G)-th row and covers one table
-// row with K vectors of width W per lane, so 32 / G table rows (K loads per lane each) are in
-// flight per warp.  Every activation row is written exactly once.
+// One warp per 32 consecutive global activation rows.  Lane l first reads the bag of row r0 + l and
+// resolves its first entry, so the dependent index loads of 32 rows overlap.  The warp is then
+// split into 32 / G groups of G lanes; a group owns every (32 / G)-th row and covers one table row
+// with K vectors of width W per lane.  The lanes of a group resolve G entries of the bag at a
+// time (and the next G while these are summed); the table rows of up to U entries are loaded before
+// the first of them is added, in bag order, so 32 / G * U rows are in flight per warp.  Every
+// activation row is written exactly once; the sum runs in ascending slot order.
 template <int W, int K, int G>
-__global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act,
-                                                            const uint32_t* __restrict__ offsets,
-                                                            const uint32_t* __restrict__ slots) {
+__global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
+  constexpr int U = K >= 4 ? 4 : 8;
   __shared__ RowMeta s_meta[kWarpsPerBlock][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + wib) * 32u;
   if (r0 >= total_act) return;
   {
     RowMeta m;
-    m.off = -1; m.begin = m.end = 0; m.table = 0; m.shard = 0; m.gain = 0.f; m.pad = 0;
+    m.src = nullptr; m.begin = m.end = 0; m.table = 0; m.gain = 0.f;
     const uint32_t my_r = r0 + lane;
     if (my_r < total_act) {
-      m.begin = offsets[my_r];
-      m.end = offsets[my_r + 1];
       m.table = find_table(count, my_r, [&](int i) { return tabs[i].act_base; });
-      if (m.end > m.begin) resolve_entry(tabs[m.table], slots, m.begin, &m.off, &m.gain, &m.shard);
+      const TableDesc& td = tabs[m.table];
+      const uint2 bag = reinterpret_cast<const uint2*>(td.bags)[my_r - td.act_base];
+      m.begin = bag.x;
+      m.end = bag.y;
+      if (m.end > m.begin) m.src = resolve_entry(td, m.begin, &m.gain);
     }
     s_meta[wib][lane] = m;
   }
@@ -477,8 +502,6 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
   const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (group * G));
   const int rows_here = (int)min(32u, total_act - r0);
   int cached_t = -1, dim = 0, vec_per_row = 0;
-  float* const* table_ptrs = nullptr;
-  const float* remote_rows = nullptr;
   float* act = nullptr;
   uint32_t act_base = 0;
   for (int j = group; j < rows_here; j += NG) {
@@ -487,8 +510,6 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
       const TableDesc& td = tabs[m.table];
       dim = td.v.dim;
       vec_per_row = dim / W;
-      table_ptrs = td.table;
-      remote_rows = td.remote_rows;
       act = td.act;
       act_base = td.act_base;
       cached_t = m.table;
@@ -496,33 +517,58 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
     VT acc[K];
 #pragma unroll
     for (int k = 0; k < K; ++k) acc[k] = Vec<W>::zero();
-    if (m.off >= 0) {
-      const VT* src = reinterpret_cast<const VT*>((m.shard < 0 ? remote_rows : table_ptrs[m.shard]) + m.off);
-#pragma unroll
-      for (int k = 0; k < K; ++k) {
-        const int c = gl + k * G;
-        if (c < vec_per_row) Vec<W>::axpy(acc[k], m.gain, __ldg(src + c));
-      }
-    }
-    for (uint32_t base = m.begin + 1; base < m.end; base += G) {
-      // Each lane of the group resolves one entry; the group then walks them in order.
-      const uint32_t e = base + gl;
-      int64_t e_off = -1;
-      float e_gain = 0.f;
-      int e_shard = 0;
-      if (e < m.end) resolve_entry(tabs[m.table], slots, e, &e_off, &e_gain, &e_shard);
-      const int cnt = (int)min((uint32_t)G, m.end - base);
-      for (int i = 0; i < cnt; ++i) {
-        const int64_t off = __shfl_sync(gmask, e_off, i, G);
-        const float gain = __shfl_sync(gmask, e_gain, i, G);
-        const int g = __shfl_sync(gmask, e_shard, i, G);
-        if (off < 0) continue;
-        const VT* src = reinterpret_cast<const VT*>((g < 0 ? remote_rows : table_ptrs[g]) + off);
+    if (m.end - m.begin == 1u) {
+      if (m.src != nullptr) {
+        const VT* src = reinterpret_cast<const VT*>(m.src);
 #pragma unroll
         for (int k = 0; k < K; ++k) {
           const int c = gl + k * G;
-          if (c < vec_per_row) Vec<W>::axpy(acc[k], gain, __ldg(src + c));
+          if (c < vec_per_row) Vec<W>::axpy(acc[k], m.gain, __ldg(src + c));
         }
+      }
+    } else if (m.end > m.begin) {
+      const TableDesc& td = tabs[m.table];
+      uint32_t base = m.begin;
+      const float* c_ptr = nullptr;
+      float c_gain = 0.f;
+      if (gl == 0) { c_ptr = m.src; c_gain = m.gain; }
+      else if (base + gl < m.end) c_ptr = resolve_entry(td, base + gl, &c_gain);
+      for (;;) {
+        const uint32_t nbase = base + G;
+        const float* n_ptr = nullptr;
+        float n_gain = 0.f;
+        if (nbase + gl < m.end) n_ptr = resolve_entry(td, nbase + gl, &n_gain);
+        const int cnt = (int)min((uint32_t)G, m.end - base);
+        for (int i0 = 0; i0 < cnt; i0 += U) {
+          VT x[U][K];
+          float gn[U];
+          bool on[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int idx = i0 + u;
+            const VT* src = reinterpret_cast<const VT*>(__shfl_sync(gmask, (unsigned long long)c_ptr, idx, G));
+            gn[u] = __shfl_sync(gmask, c_gain, idx, G);
+            on[u] = idx < cnt && src != nullptr;
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+              const int c = gl + k * G;
+              if (on[u] && c < vec_per_row) x[u][k] = __ldg(src + c);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (!on[u]) continue;
+#pragma unroll
+            for (int k = 0; k < K; ++k) {
+              const int c = gl + k * G;
+              if (c < vec_per_row) Vec<W>::axpy(acc[k], gn[u], x[u][k]);
+            }
+          }
+        }
+        if (nbase >= m.end) break;
+        base = nbase;
+        c_ptr = n_ptr;
+        c_gain = n_gain;
       }
     }
     VT* dst = reinterpret_cast<VT*>(act + (int64_t)(r0 + j - act_base) * dim);
@@ -532,6 +578,210 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
       if (c < vec_per_row) dst[c] = acc[k];
     }
   }
+}
+
+// ---- cp.async pipeline variant of the gather
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(__cvta_generic_to_global(src)) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+constexpr int kFwdBlock = 128;
+constexpr int kFwdWarps = kFwdBlock / 32;
+constexpr int kFwdTile = 32;  // steps whose entries are resolved at a time
+// Steps held in a warp's ring for K 16-byte vectors per lane (8 KiB, 16 KiB for the longest rows).
+__host__ __device__ constexpr int fwd_ring_steps(int K) { return K <= 1 ? 16 : K == 2 ? 8 : 4; }
+__host__ __device__ constexpr size_t fwd_ring_warp_bytes(int K, int NG) {
+  return (size_t)fwd_ring_steps(K) * K * 512 + (size_t)2 * NG * kFwdTile * 16 + 32 * 24;
+}
+
+// One resolved entry of a consumer group's list.
+struct FwdEntry {
+  const float* src;  // table row (or its staged copy)
+  float gain;
+  uint32_t meta;     // bits 0..4: row of the warp that the entry belongs to; kEnt* flags
+};
+constexpr uint32_t kEntEnds = 0x80000000u;  // last entry of its activation row: store the sum
+constexpr uint32_t kEntSkip = 0x40000000u;  // contributes nothing
+
+// Forward for rows of `dim` floats with dim % 4 == 0 and 16-byte aligned tables and activations.
+// A warp owns 32 consecutive global activation rows.  It is split into NG consumer groups of
+// 32 / NG lanes (NG = 4, 2, 1 for rows of up to 32, 64, more floats); group g owns rows g, g + NG,
+// ... and sums their entries one after the other, in bag order, so every group walks ONE list of
+// entries (the concatenation of its rows' bags) and all groups advance in lockstep: in step t every
+// group handles the t-th entry of its list.  The lists are resolved lane-parallel, kFwdTile steps
+// at a time (plan -> slot -> id, gain -> address; the next tile while this one streams), and the
+// table rows stream through a ring of R step slots in shared memory with cp.async (16 bytes per
+// lane and vector, nothing held in registers while in flight, R / 2 steps in flight): bytes in
+// flight do not depend on the bag lengths, and a step costs the same few instructions whether it
+// moves one 512-byte row or four 128-byte rows.  Every activation row is written exactly once
+// (rows without entries are zeroed by the warp); sums run in ascending slot order with separately
+// rounded multiply and add, so the result equals a sequential float32 loop bit for bit.
+template <int K, int NG>
+__global__ void __launch_bounds__(kFwdBlock) fwd_ring_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
+  constexpr int Gc = 32 / NG;           // lanes of a consumer group
+  constexpr int RPG = 32 / NG;          // rows of a consumer group
+  constexpr int R = fwd_ring_steps(K);
+  constexpr int A = R / 2;              // steps in flight while one is consumed
+  constexpr int T = kFwdTile;
+  constexpr uint32_t kStepBytes = (uint32_t)K * 512u;
+  extern __shared__ __align__(128) unsigned char fwd_smem[];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t r0 = (blockIdx.x * kFwdWarps + wib) * 32u;
+  if (r0 >= total_act) return;
+  unsigned char* mine = fwd_smem + (size_t)wib * fwd_ring_warp_bytes(K, NG);
+  const uint32_t ring_base = smem_addr(mine);
+  FwdEntry* list = reinterpret_cast<FwdEntry*>(mine + (size_t)R * kStepBytes);
+  float** s_act = reinterpret_cast<float**>(mine + (size_t)R * kStepBytes + (size_t)2 * NG * T * 16);
+  uint32_t* s_begin = reinterpret_cast<uint32_t*>(s_act + 32);
+  uint32_t* s_pref = s_begin + 32;
+  uint32_t* s_len = s_pref + 32;
+  uint32_t* s_tv = s_len + 32;  // table index | vectors per row << 16
+
+  // Lane l describes row r0 + l.
+  uint32_t begin = 0, len = 0, tv = 0;
+  float* actp = nullptr;
+  const bool valid = r0 + lane < total_act;
+  if (valid) {
+    const uint32_t my_r = r0 + lane;
+    const int t = find_table(count, my_r, [&](int i) { return tabs[i].act_base; });
+    const TableDesc& td = tabs[t];
+    const uint32_t lr = my_r - td.act_base;
+    const uint2 bag = reinterpret_cast<const uint2*>(td.bags)[lr];
+    begin = bag.x;
+    len = bag.y > bag.x ? bag.y - bag.x : 0u;
+    tv = (uint32_t)t | ((uint32_t)(td.v.dim >> 2) << 16);
+    actp = td.act + (int64_t)lr * td.v.dim;
+  }
+  // Position of every row inside its group's list: inclusive scan over the lanes of equal l % NG.
+  uint32_t inc = len;
+#pragma unroll
+  for (int d = NG; d < 32; d <<= 1) {
+    const uint32_t o = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += o;
+  }
+  s_begin[lane] = begin; s_pref[lane] = inc - len; s_len[lane] = len; s_tv[lane] = tv; s_act[lane] = actp;
+  uint32_t glen[NG];
+  uint32_t max_len = 0;
+#pragma unroll
+  for (int g = 0; g < NG; ++g) {
+    glen[g] = __shfl_sync(0xffffffffu, inc, 32 - NG + g);
+    max_len = max(max_len, glen[g]);
+  }
+  const int my_group = lane / Gc, gl = lane % Gc;
+  uint32_t my_len = glen[0];
+#pragma unroll
+  for (int g = 1; g < NG; ++g)
+    if (my_group == g) my_len = glen[g];
+  uint32_t zero_rows = __ballot_sync(0xffffffffu, valid && len == 0);
+  __syncwarp();
+  while (zero_rows) {  // rows without entries: the warp writes the zeros
+    const int i = __ffs(zero_rows) - 1;
+    zero_rows &= zero_rows - 1;
+    float4* dst = reinterpret_cast<float4*>(s_act[i]);
+    const int v = (int)(s_tv[i] >> 16);
+    for (int c = lane; c < v; c += 32) dst[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (max_len == 0) return;
+
+  // Resolves the entries of steps [n * T, n * T + T) of every group; lane l takes step n * T + l.
+  auto build_list = [&](uint32_t n) {
+    FwdEntry* L = list + (size_t)(n & 1u) * NG * T;
+    const uint32_t p = n * T + (uint32_t)lane;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      FwdEntry e;
+      e.src = nullptr; e.gain = 0.f; e.meta = kEntSkip;
+      if (p < glen[g]) {
+        int lo = 0, hi = RPG - 1;  // last row of the group whose list position is <= p
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (s_pref[mid * NG + g] <= p) lo = mid; else hi = mid - 1;
+        }
+        const int row = lo * NG + g;
+        const uint32_t off = p - s_pref[row];
+        e.src = resolve_entry(tabs[s_tv[row] & 0xffffu], s_begin[row] + off, &e.gain);
+        e.meta = (uint32_t)row | (off + 1u == s_len[row] ? kEntEnds : 0u) | (e.src == nullptr ? kEntSkip : 0u);
+      }
+      L[g * T + lane] = e;
+    }
+  };
+  auto entry_of = [&](uint32_t t) -> const FwdEntry& {
+    return list[(size_t)((t / T) & 1u) * NG * T + my_group * T + (t % T)];
+  };
+  // Starts the copies of step t: the rows that the groups sum in that step.  Always one commit group.
+  auto issue = [&](uint32_t t) {
+    if (t < my_len) {
+      const FwdEntry& e = entry_of(t);
+      if (!(e.meta & kEntSkip)) {
+        const int vpr = (int)(s_tv[e.meta & 31u] >> 16);
+        const float4* src = reinterpret_cast<const float4*>(e.src);
+        const uint32_t dst = ring_base + (t % R) * kStepBytes + (uint32_t)lane * 16u;
+#pragma unroll
+        for (int k = 0; k < K; ++k) {
+          const int c = gl + k * Gc;
+          if (c < vpr) cp_async16(dst + k * 512, src + c);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+  float4 acc[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto consume = [&](uint32_t t) {
+    if (t >= my_len) return;
+    const FwdEntry e = entry_of(t);
+    const int vpr = (int)(s_tv[e.meta & 31u] >> 16);
+    if (!(e.meta & kEntSkip)) {
+      const uint32_t slot = ring_base + (t % R) * kStepBytes + (uint32_t)lane * 16u;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        if (gl + k * Gc < vpr) {
+          const float4 x = lds128(slot + k * 512);
+          acc[k].x = acc[k].x + e.gain * x.x; acc[k].y = acc[k].y + e.gain * x.y;
+          acc[k].z = acc[k].z + e.gain * x.z; acc[k].w = acc[k].w + e.gain * x.w;
+        }
+      }
+    }
+    if (e.meta & kEntEnds) {
+      float4* dst = reinterpret_cast<float4*>(s_act[e.meta & 31u]);
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const int c = gl + k * Gc;
+        if (c < vpr) dst[c] = acc[k];
+        acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+  };
+
+  build_list(0);
+  __syncwarp();
+#pragma unroll
+  for (int a = 0; a < A; ++a) issue((uint32_t)a);
+  for (uint32_t t = 0; t < max_len; ++t) {
+    // The list of the next tile is needed by the copies issued A steps ahead; its buffer was last
+    // read in the previous tile.
+    if (t % T == 0 && t + T < max_len) {
+      __syncwarp();  // every lane is done with step t - 1, the last reader of that buffer
+      build_list(t / T + 1);
+      __syncwarp();
+    }
+    issue(t + A);
+    cp_async_wait<A>();  // this lane's copies of step t have landed
+    __syncwarp();        // ... and every other lane's
+    consume(t);
+  }
+  cp_async_wait<0>();
 }
 
 // ------------------------------------------------------------------------ backward
@@ -859,14 +1109,6 @@ __global__ void __launch_bounds__(kBlock) bwd_main_kernel(const TableDesc* __res
 
 // ---- cp.async pipeline variant of the update kernel
 
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(__cvta_generic_to_global(src)) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 constexpr int kPipeBlock = 128;
 constexpr int kPipeWarps = kPipeBlock / 32;
 constexpr int kPipeAhead = 2;  // batches in flight while one is consumed
@@ -916,11 +1158,6 @@ __device__ __forceinline__ float apply_opt_fast(const OptParams& o, bool clipped
   return clipped ? clip(nw, o.lo, o.hi) : nw;
 }
 
-__device__ __forceinline__ float4 lds128(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
-}
 
 // Same contract as bwd_main_kernel, for rows of `dim` floats with dim % 4 == 0 and 16-byte aligned
 // tables, slot variables and gradients.  A warp owns 32 consecutive entries.  Lane j describes
@@ -1503,11 +1740,39 @@ bool pick_group_shape(int dim, int* w, int* k, int* g) {
   return true;
 }
 
-template <int W, int K, int G>
-int launch_fwd(const TableDesc* tabs, int count, uint32_t total_act, const uint32_t* offsets, const uint32_t* slots,
-               cudaStream_t st) {
+template <int K, int NG>
+int launch_fwd_ring(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
+  const size_t smem = (size_t)kFwdWarps * fwd_ring_warp_bytes(K, NG);
+  SC_CUDA_OK(cudaFuncSetAttribute(fwd_ring_kernel<K, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SC_CUDA_OK(cudaFuncSetAttribute(fwd_ring_kernel<K, NG>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  (int)cudaSharedmemCarveoutMaxShared));
   const unsigned warps = (unsigned)ceil_div(total_act, 32);
-  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act, offsets, slots);
+  fwd_ring_kernel<K, NG><<<(unsigned)ceil_div(warps, kFwdWarps), kFwdBlock, smem, st>>>(tabs, count, total_act);
+  SC_LAUNCH_OK("fwd_ring_kernel");
+  return SC_OK;
+}
+
+// Gather with the cp.async ring; the longest row of the group picks the shape.
+inline int dispatch_fwd_ring(const TableDesc* tabs, int count, uint32_t total_act, int max_dim, cudaStream_t st) {
+  const int vecs = max_dim / 4;
+  if (vecs <= 8) return launch_fwd_ring<1, 4>(tabs, count, total_act, st);
+  if (vecs <= 16) return launch_fwd_ring<1, 2>(tabs, count, total_act, st);
+  if (vecs <= 32) return launch_fwd_ring<1, 1>(tabs, count, total_act, st);
+  if (vecs <= 64) return launch_fwd_ring<2, 1>(tabs, count, total_act, st);
+  if (vecs <= 128) return launch_fwd_ring<4, 1>(tabs, count, total_act, st);
+  return launch_fwd_ring<8, 1>(tabs, count, total_act, st);
+}
+
+// The cp.async ring is the default gather; SC_FWD_KERNEL=groups selects the register-only kernel.
+inline bool fwd_ring_enabled() {
+  static const bool on = [] { const char* e = getenv("SC_FWD_KERNEL"); return !(e && strcmp(e, "groups") == 0); }();
+  return on;
+}
+
+template <int W, int K, int G>
+int launch_fwd(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
+  const unsigned warps = (unsigned)ceil_div(total_act, 32);
+  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act);
   SC_LAUNCH_OK("fwd_gather_kernel");
   return SC_OK;
 }
@@ -1651,25 +1916,39 @@ SideStream* side_stream() {
   return &streams[dev];
 }
 
+// Where the forward's plan (per activation row, its slots in ascending order) comes from.
+enum FwdPlanMode {
+  kPlanGiven = 0,   // every item brings the plan that preprocessing emitted
+  kPlanSingle = 1,  // every item promises at most one id per sample: bags by one scatter, no list
+  kPlanBuild = 2,   // counting sort of the slots by activation row, here
+};
+
 struct FwdPlan {
   std::vector<CsrView> views;
+  int mode = kPlanBuild;
   uint64_t total_slots = 0, total_act = 0;
   uint64_t remote_floats = 0;  // staging space for rows of remote shards (tables with local_shard >= 0)
   int total_shards = 0;
-  int w = 0, k = 0, g = 0;
+  int w = 0, k = 0, g = 0, max_dim = 0;
 };
 
 int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
   if (!items || count <= 0) SC_FAIL(SC_INVALID_ARGUMENT, "empty forward group");
   p->views.resize(count);
+  bool given = true, single = true;
   for (int i = 0; i < count; ++i) {
     int st = make_view(&items[i].csr, &p->views[i]);
     if (st != SC_OK) return st;
+    if ((items[i].plan_slots == nullptr) != (items[i].plan_bags == nullptr))
+      SC_FAIL(SC_INVALID_ARGUMENT, "plan_slots and plan_bags must be given together");
+    given = given && items[i].plan_bags != nullptr;
+    single = single && items[i].csr.max_ids_per_sample == 1;
     int w, k, g;
     if (!pick_group_shape(p->views[i].dim, &w, &k, &g)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the gather kernel", p->views[i].dim);
     if (i == 0) { p->w = w; p->k = k; p->g = g; }
     if (w != p->w || k != p->k || g != p->g) SC_FAIL(SC_INVALID_ARGUMENT, "tables of one group must share the row length class (dim %d vs %d)",
                                        p->views[i].dim, p->views[0].dim);
+    p->max_dim = p->views[i].dim > p->max_dim ? p->views[i].dim : p->max_dim;
     p->total_slots += (uint64_t)p->views[i].coo;
     p->total_act += (uint64_t)p->views[i].bdev;
     p->total_shards += p->views[i].P;
@@ -1677,6 +1956,7 @@ int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
     if (items[i].local_shard >= 0 && p->views[i].P > 1) p->remote_floats += (uint64_t)p->views[i].coo * (uint64_t)p->views[i].dim;
   }
   if (p->total_slots >= 0xffffffffull || p->total_act >= 0xffffffffull) SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
+  p->mode = given ? kPlanGiven : single ? kPlanSingle : kPlanBuild;
   return SC_OK;
 }
 
@@ -1687,6 +1967,7 @@ struct FwdScratch {
   uint32_t* list;       // [slots] slots ordered by (activation row, slot)
   uint32_t* scratch;    // [slots] second buffer of the long-row sort
   uint32_t* offsets;    // [act + 2] counts, then their exclusive scan; the last word counts the long rows
+  uint32_t* bags;       // [2 * act] (begin, end) of every activation row inside `list`
   uint32_t* scan_temp;
   uint32_t* big_rows;   // [slots / kSerialSortLimit + 1]
   uint32_t* run_ord;    // [slots] index of a remote slot's row in remote_rows (remote shards only)
@@ -1699,13 +1980,15 @@ struct FwdScratch {
 bool carve_fwd(Workspace& ws, const FwdPlan& p, int count, FwdScratch* s) {
   const size_t slots = (size_t)p.total_slots, act = (size_t)p.total_act;
   s->image = ws.take<char>(image_bytes(count, p.total_shards));
-  s->keys = ws.take<uint32_t>(slots);
-  s->ranks = ws.take<uint32_t>(slots);
-  s->list = ws.take<uint32_t>(slots);
-  s->scratch = ws.take<uint32_t>(slots);
-  s->offsets = ws.take<uint32_t>(act + 2);
-  s->scan_temp = ws.take<uint32_t>(scan_temp_elems(act + 1));
-  s->big_rows = ws.take<uint32_t>(slots / kSerialSortLimit + 1);
+  const bool build = p.mode == kPlanBuild;
+  s->keys = ws.take<uint32_t>(build ? slots : 0);
+  s->ranks = ws.take<uint32_t>(build ? slots : 0);
+  s->list = ws.take<uint32_t>(build ? slots : 0);
+  s->scratch = ws.take<uint32_t>(build ? slots : 0);
+  s->offsets = ws.take<uint32_t>(build ? act + 2 : 0);
+  s->bags = ws.take<uint32_t>(p.mode == kPlanGiven ? 0 : 2 * act);
+  s->scan_temp = ws.take<uint32_t>(build ? scan_temp_elems(act + 1) : 0);
+  s->big_rows = ws.take<uint32_t>(build ? slots / kSerialSortLimit + 1 : 0);
   s->run_ord = ws.take<uint32_t>(p.remote_floats ? slots : 0);
   s->heads = ws.take<uint32_t>(p.remote_floats ? slots : 0);
   s->heads_temp = ws.take<uint32_t>(p.remote_floats ? scan_temp_elems(slots) + 1 : 0);
@@ -1846,8 +2129,10 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   std::vector<int> pool_index;
   uint32_t slot_base = 0, act_base = 0;
   size_t remote_base = 0;
+  bool ring = p.w == 4 && fwd_ring_enabled();  // 16-byte asynchronous copies need aligned rows
   for (int i = 0; i < count; ++i) {
     if (!items[i].shard_tables || !items[i].activations) SC_FAIL(SC_INVALID_ARGUMENT, "null table or activation pointer");
+    ring = ring && aligned16(items[i].activations);
     TableDesc td;
     memset(&td, 0, sizeof td);
     td.v = p.views[i];
@@ -1859,10 +2144,20 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
       td.remote_rows = s.remote_rows + remote_base;
       remote_base += (size_t)td.v.coo * (size_t)td.v.dim;
     }
+    if (p.mode == kPlanGiven) {
+      td.plan = items[i].plan_slots;
+      td.bags = items[i].plan_bags;
+      td.plan_bias = 0;
+    } else {
+      td.plan = p.mode == kPlanBuild ? s.list : nullptr;
+      td.bags = s.bags + 2 * (size_t)act_base;
+      td.plan_bias = slot_base;
+    }
     slot_base += (uint32_t)td.v.coo; act_base += (uint32_t)td.v.bdev;
     pool_index.push_back((int)img.pool.size()); pool_index.push_back(-1); pool_index.push_back(-1);
     for (int g = 0; g < td.v.P; ++g) {
       if (!items[i].shard_tables[g]) SC_FAIL(SC_INVALID_ARGUMENT, "shard %d has no table pointer", g);
+      ring = ring && aligned16(items[i].shard_tables[g]);
       img.pool.push_back(const_cast<float*>(items[i].shard_tables[g]));
     }
     img.tabs.push_back(td);
@@ -1891,21 +2186,30 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
     SC_LAUNCH_OK("fwd_fetch_kernel");
     SC_CUDA_OK(cudaEventRecord(side->join, fs));
   }
-  uint32_t* big_count = s.offsets + total_act + 1;
-  SC_CUDA_OK(cudaMemsetAsync(s.offsets, 0, ((size_t)total_act + 2) * sizeof(uint32_t), cs));
-  const unsigned slot_blocks = (unsigned)ceil_div(total_slots, kBlock);
-  fwd_count_kernel<<<slot_blocks, kBlock, 0, cs>>>(tabs, count, total_slots, total_act, s.keys, s.ranks, s.offsets);
-  SC_LAUNCH_OK("fwd_count_kernel");
-  SC_CUDA_OK(exclusive_scan<uint32_t>(s.offsets, s.offsets, (size_t)total_act + 1, s.scan_temp, nullptr, cs));
-  fwd_place_kernel<<<slot_blocks, kBlock, 0, cs>>>(s.keys, s.ranks, s.offsets, total_slots, total_act, s.list);
-  SC_LAUNCH_OK("fwd_place_kernel");
-  fwd_rowsort_kernel<<<(unsigned)ceil_div(total_act, kBlock), kBlock, 0, cs>>>(s.offsets, total_act, s.list, s.big_rows, big_count);
-  SC_LAUNCH_OK("fwd_rowsort_kernel");
-  fwd_bigrow_kernel<<<(unsigned)sm_count(), kBlock, 0, cs>>>(s.offsets, s.list, s.scratch, s.big_rows, big_count,
-                                                             bit_width_u32(total_slots));
-  SC_LAUNCH_OK("fwd_bigrow_kernel");
+  if (p.mode == kPlanSingle) {
+    SC_CUDA_OK(cudaMemsetAsync(s.bags, 0, (size_t)total_act * 2 * sizeof(uint32_t), cs));
+    fwd_single_bags_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, cs>>>(tabs, count, total_slots,
+                                                                                      reinterpret_cast<uint2*>(s.bags));
+    SC_LAUNCH_OK("fwd_single_bags_kernel");
+  } else if (p.mode == kPlanBuild) {
+    uint32_t* big_count = s.offsets + total_act + 1;
+    SC_CUDA_OK(cudaMemsetAsync(s.offsets, 0, ((size_t)total_act + 2) * sizeof(uint32_t), cs));
+    const unsigned slot_blocks = (unsigned)ceil_div(total_slots, kBlock);
+    fwd_count_kernel<<<slot_blocks, kBlock, 0, cs>>>(tabs, count, total_slots, total_act, s.keys, s.ranks, s.offsets);
+    SC_LAUNCH_OK("fwd_count_kernel");
+    SC_CUDA_OK(exclusive_scan<uint32_t>(s.offsets, s.offsets, (size_t)total_act + 1, s.scan_temp, nullptr, cs));
+    fwd_place_kernel<<<slot_blocks, kBlock, 0, cs>>>(s.keys, s.ranks, s.offsets, total_slots, total_act, s.list);
+    SC_LAUNCH_OK("fwd_place_kernel");
+    fwd_rowsort_kernel<<<(unsigned)ceil_div(total_act, kBlock), kBlock, 0, cs>>>(s.offsets, total_act, s.list, s.big_rows, big_count,
+                                                                                s.bags);
+    SC_LAUNCH_OK("fwd_rowsort_kernel");
+    fwd_bigrow_kernel<<<(unsigned)sm_count(), kBlock, 0, cs>>>(s.offsets, s.list, s.scratch, s.big_rows, big_count,
+                                                               bit_width_u32(total_slots), 1);
+    SC_LAUNCH_OK("fwd_bigrow_kernel");
+  }
   if (side != nullptr) SC_CUDA_OK(cudaStreamWaitEvent(cs, side->join, 0));  // the gather reads the fetched rows
-#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, s.offsets, s.list, cs)
+  if (ring) return dispatch_fwd_ring(tabs, count, total_act, p.max_dim, cs);
+#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, cs)
   SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL);
 #undef SC_FWD_CALL
 }
@@ -2017,10 +2321,10 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
                                                    s.sort.vals[0]);
     SC_LAUNCH_OK("bwd_place_kernel");
     fwd_rowsort_kernel<<<(unsigned)ceil_div(total_rows, kBlock), kBlock, 0, cs>>>(s.counts, total_rows, s.sort.vals[0], s.big_rows,
-                                                                                big_count);
+                                                                                big_count, nullptr);
     SC_LAUNCH_OK("fwd_rowsort_kernel");
     fwd_bigrow_kernel<<<(unsigned)sm_count(), kBlock, 0, cs>>>(s.counts, s.sort.vals[0], s.sort.vals[1], s.big_rows, big_count,
-                                                               bit_width_u32(total_ent));
+                                                               bit_width_u32(total_ent), 1);
     SC_LAUNCH_OK("fwd_bigrow_kernel");
     bwd_ranges_from_offsets_kernel<<<(unsigned)ceil_div(count + 1, kBlock), kBlock, 0, cs>>>(tabs, count, s.counts, invalid,
                                                                                            s.ranges);
@@ -2222,14 +2526,14 @@ extern "C" size_t sc_sparse_dense_matmul_fwd_workspace_bytes(const sc_csr_t* csr
   if (!csr) return 0;
   float* dummy_ptrs[SC_MAX_SHARDS];
   for (int i = 0; i < SC_MAX_SHARDS; ++i) dummy_ptrs[i] = reinterpret_cast<float*>(256);
-  sc_fwd_item_t item = {*csr, dummy_ptrs, reinterpret_cast<float*>(256), -1};
+  sc_fwd_item_t item = {*csr, dummy_ptrs, reinterpret_cast<float*>(256), -1, nullptr, nullptr};
   return sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(&item, 1);
 }
 
 extern "C" int32_t sc_sparse_dense_matmul_fwd(const sc_csr_t* csr, const float* const* shard_tables, float* activations,
                                               void* workspace, size_t workspace_bytes, sc_stream_t stream) {
   if (!csr) SC_FAIL(SC_INVALID_ARGUMENT, "csr descriptor is null");
-  sc_fwd_item_t item = {*csr, shard_tables, activations, -1};
+  sc_fwd_item_t item = {*csr, shard_tables, activations, -1, nullptr, nullptr};
   return sc_sparse_dense_matmul_fwd_grouped(&item, 1, workspace, workspace_bytes, stream);
 }
 

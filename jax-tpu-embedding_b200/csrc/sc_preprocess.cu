@@ -17,7 +17,10 @@
 //             the rank of every pair and of every unique row inside its partition; the
 //             sequential drop rules of the reference reduce to "keep a prefix of each partition";
 //   pack      per-partition 8-aligned offsets, row pointers, padding, duplicate gains summed
-//             left to right in float32.
+//             left to right in float32;
+//   plan      (optional) the sample-major view the forward needs: the input is sample-major and
+//             every kept entry knows its slot, so the slot is scattered back to the entry's input
+//             position and each sample's slots are put in ascending order.
 #include <math.h>
 
 #include <vector>
@@ -30,6 +33,8 @@ namespace {
 
 constexpr int kBlock = 256;
 constexpr int kMaxPartitions = 4 * SC_MAX_SHARDS;  // local SparseCores x shards of one table
+constexpr uint32_t kNoSlot = 0xffffffffu;          // forward plan: input position whose id was merged or dropped
+constexpr uint32_t kSerialBagLimit = 64;           // longer bags are ordered by a whole warp
 
 // One stacked table of a grouped call (device memory).
 struct PreTable {
@@ -41,6 +46,8 @@ struct PreTable {
   int32_t* out_sids;
   float* out_gains;
   int32_t* stats;
+  uint32_t* plan_slots;     // [nnz] forward plan (nullptr: not wanted)
+  uint32_t* plan_bags;      // [2 * rows]
   int32_t S, P, C;          // SparseCores per device, shards, devices
   int32_t pbits, lbits;     // bits of the shard id and of the row inside a shard
   int32_t bslice;           // samples per SparseCore slice (ceil(batch / S))
@@ -110,6 +117,7 @@ __global__ void extract_kernel(PreGroup g, uint32_t* __restrict__ keys, int32_t*
     e = p.offsets[r + 1];
   }
   const int cnt = e - b;
+  if (p.plan_bags != nullptr) reinterpret_cast<uint2*>(p.plan_bags)[row_id] = make_uint2((uint32_t)b, (uint32_t)e);
   const int32_t* ids = p.ids;
   const float* weights = p.weights;
   float divisor = 1.0f;
@@ -147,6 +155,7 @@ __global__ void extract_kernel(PreGroup g, uint32_t* __restrict__ keys, int32_t*
     keys[p.id_base + i] = key_hi | (shard << p.lbits) | local;
     row_of[p.id_base + i] = row_id;
     if (p.has_weights) gain_of[p.id_base + i] = weights[i] / divisor;
+    if (p.plan_slots != nullptr) p.plan_slots[i] = kNoSlot;
   }
 }
 
@@ -324,6 +333,73 @@ __global__ void pack_kernel(PreGroup g, uint32_t n, const uint32_t* __restrict__
   p.out_ids[slot] = (int32_t)(local_key & ((1u << p.lbits) - 1u));
   p.out_sids[slot] = row % p.bslice;
   p.out_gains[slot] = gain;
+  if (p.plan_slots != nullptr) p.plan_slots[vals[pos] - p.id_base] = (uint32_t)slot;
+}
+
+// Forward plan, last step.  Thread per sample row: the row's input positions now hold the slots of
+// its kept entries (kNoSlot elsewhere); they are put in ascending order, kNoSlot last, and the bag
+// is shortened to the kept ones.  Slots are unique, so the result does not depend on the order in
+// which pack_kernel ran.  Bags longer than kSerialBagLimit go to plan_bigrow_kernel.
+__global__ void plan_sort_kernel(PreGroup g, uint32_t* __restrict__ big_rows, uint32_t* __restrict__ big_count) {
+  const uint32_t gr = blockIdx.x * blockDim.x + threadIdx.x;
+  if (gr >= g.total_rows) return;
+  const int t = find_table(g.count, gr, [&](int i) { return g.tabs[i].row_base; });
+  const PreTable& p = g.tabs[t];
+  if (p.plan_bags == nullptr) return;
+  uint2* bag = reinterpret_cast<uint2*>(p.plan_bags) + (gr - p.row_base);
+  const uint32_t b = bag->x, n = bag->y - b;
+  uint32_t* a = p.plan_slots + b;
+  if (n > kSerialBagLimit) {
+    big_rows[atomicAdd(big_count, 1u)] = gr;
+    return;
+  }
+  uint32_t kept = 0;
+  for (uint32_t i = 0; i < n; ++i) {
+    const uint32_t x = a[i];
+    if (x == kNoSlot) continue;
+    uint32_t j = kept++;
+    while (j > 0 && a[j - 1] > x) { a[j] = a[j - 1]; --j; }
+    a[j] = x;
+  }
+  bag->y = b + kept;
+}
+
+// Warp per long bag: rank sort.  The bag is copied to `scratch` (indexed like the group's id array);
+// the rank of a kept slot is the number of smaller kept slots.
+__global__ void __launch_bounds__(kBlock) plan_bigrow_kernel(PreGroup g, const uint32_t* __restrict__ big_rows,
+                                                             const uint32_t* __restrict__ big_count,
+                                                             uint32_t* __restrict__ scratch) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t warps = gridDim.x * (kBlock / 32);
+  const uint32_t todo = *big_count;
+  for (uint32_t w = blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5); w < todo; w += warps) {
+    const uint32_t gr = big_rows[w];
+    const int t = find_table(g.count, gr, [&](int i) { return g.tabs[i].row_base; });
+    const PreTable& p = g.tabs[t];
+    uint2* bag = reinterpret_cast<uint2*>(p.plan_bags) + (gr - p.row_base);
+    const uint32_t b = bag->x, n = bag->y - b;
+    uint32_t* a = p.plan_slots + b;
+    uint32_t* tmp = scratch + p.id_base + b;
+    uint32_t kept = 0;
+    for (uint32_t i = lane; i < n; i += 32) {
+      const uint32_t x = a[i];
+      tmp[i] = x;
+      kept += x != kNoSlot ? 1u : 0u;
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) kept += __shfl_xor_sync(0xffffffffu, kept, d);
+    __syncwarp();
+    for (uint32_t i = lane; i < n; i += 32) {
+      const uint32_t x = tmp[i];
+      if (x == kNoSlot) continue;
+      uint32_t rank = 0;
+      for (uint32_t j = 0; j < n; ++j) rank += tmp[j] < x ? 1u : 0u;
+      a[rank] = x;
+    }
+    __syncwarp();
+    if (lane == 0) bag->y = b + kept;
+    __syncwarp();
+  }
 }
 
 // ---- host side ---------------------------------------------------------------------------
@@ -356,6 +432,7 @@ struct PrePlan {
   uint64_t total_ids = 0, total_rows = 0, total_slots = 0, total_parts = 0, total_gain = 0;
   int key_bits = 0;  // bits of the per-table part of the key
   int tshift = 0, total_bits = 0;
+  bool any_plan = false;
 };
 
 int plan(const sc_preprocess_item_t* items, int count, PrePlan* pl) {
@@ -403,6 +480,10 @@ int plan(const sc_preprocess_item_t* items, int count, PrePlan* pl) {
     p.ids = it.ids; p.offsets = it.row_offsets; p.weights = it.weights;
     p.row_pointers = it.row_pointers; p.out_ids = it.embedding_ids; p.out_sids = it.sample_ids; p.out_gains = it.gains;
     p.stats = it.stats;
+    if ((it.plan_slots == nullptr) != (it.plan_bags == nullptr))
+      SC_FAIL(SC_INVALID_ARGUMENT, "plan_slots and plan_bags must be given together");
+    p.plan_slots = it.plan_slots; p.plan_bags = it.plan_bags;
+    pl->any_plan = pl->any_plan || it.plan_bags != nullptr;
     p.S = S; p.P = P; p.C = C;
     p.pbits = bit_width_u32((uint32_t)P - 1);
     p.lbits = bit_width_u32((uint32_t)(o->stack_vocab_size / P) - 1);
@@ -446,6 +527,7 @@ struct PreScratch {
   int32_t* part_start;
   int32_t* part_written;
   int32_t* error_flags;
+  uint32_t* big_rows;  // forward plan: rows with long bags, then their count
 };
 
 bool carve(Workspace& ws, const PrePlan& pl, int count, PreScratch* s) {
@@ -466,6 +548,7 @@ bool carve(Workspace& ws, const PrePlan& pl, int count, PreScratch* s) {
   s->part_start = ws.take<int32_t>((size_t)pl.total_parts + 1);
   s->part_written = ws.take<int32_t>((size_t)pl.total_parts + 1);
   s->error_flags = ws.take<int32_t>((size_t)count);
+  s->big_rows = ws.take<uint32_t>(pl.any_plan ? n / kSerialBagLimit + 2 : 0);
   return ws.ok();
 }
 
@@ -530,6 +613,15 @@ extern "C" int32_t sc_preprocess_grouped(const sc_preprocess_item_t* items, int3
     pack_kernel<<<(unsigned)ceil_div(n, kBlock), kBlock, 0, cs>>>(g, n, keys, vals, s.row_sorted, s.gain_of, s.row_gain, s.cnt,
                                                                 s.bounds, s.part_start, s.part_written);
     SC_LAUNCH_OK("pack_kernel");
+  }
+  if (pl.any_plan) {
+    uint32_t* big_count = s.big_rows + n / kSerialBagLimit + 1;
+    SC_CUDA_OK(cudaMemsetAsync(big_count, 0, sizeof(uint32_t), cs));
+    plan_sort_kernel<<<(unsigned)ceil_div(g.total_rows, kBlock), kBlock, 0, cs>>>(g, s.big_rows, big_count);
+    SC_LAUNCH_OK("plan_sort_kernel");
+    // The sort buffer that does not hold the sorted keys is free by now.
+    plan_bigrow_kernel<<<(unsigned)sm_count(), kBlock, 0, cs>>>(g, s.big_rows, big_count, s.sort.keys[1 - res]);
+    SC_LAUNCH_OK("plan_bigrow_kernel");
   }
   return SC_OK;
 }

@@ -43,7 +43,8 @@ class PreprocessOptions(ctypes.Structure):
 class PreprocessItem(ctypes.Structure):
   _fields_ = [("ids", c_vp), ("row_offsets", c_vp), ("weights", c_vp), ("nnz", c_i64), ("total_rows", c_i64),
               ("features", ctypes.POINTER(FeatureDesc)), ("num_features", c_i32), ("options", PreprocessOptions),
-              ("row_pointers", c_vp), ("embedding_ids", c_vp), ("sample_ids", c_vp), ("gains", c_vp), ("stats", c_vp)]
+              ("row_pointers", c_vp), ("embedding_ids", c_vp), ("sample_ids", c_vp), ("gains", c_vp), ("stats", c_vp),
+              ("plan_slots", c_vp), ("plan_bags", c_vp)]
 
 
 class Csr(ctypes.Structure):
@@ -58,7 +59,8 @@ class Optimizer(ctypes.Structure):
 
 
 class FwdItem(ctypes.Structure):
-  _fields_ = [("csr", Csr), ("shard_tables", ctypes.POINTER(c_vp)), ("activations", c_vp), ("local_shard", ctypes.c_int32)]
+  _fields_ = [("csr", Csr), ("shard_tables", ctypes.POINTER(c_vp)), ("activations", c_vp), ("local_shard", ctypes.c_int32),
+              ("plan_slots", c_vp), ("plan_bags", c_vp)]
 
 
 class PullSource(ctypes.Structure):

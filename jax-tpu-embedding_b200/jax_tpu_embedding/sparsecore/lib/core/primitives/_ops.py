@@ -138,7 +138,7 @@ class ForwardRequest:
   """One stacked table of a grouped forward call (operands already validated)."""
 
   def __init__(self, rp, ids, sids, gains, table, *, device_batch_size, num_sc_per_device=None,
-               global_device_count=None, local_device_count=None, max_ids_per_sample=0):
+               global_device_count=None, local_device_count=None, max_ids_per_sample=0, forward_plan=None):
     torch = _native.require_cuda()
     self.rp, self.ids, self.sids, self.gains = _device_operands(rp, ids, sids, gains)
     self.table = _native.as_device(table, torch.float32, "embedding_table")
@@ -148,6 +148,14 @@ class ForwardRequest:
     self.act = torch.empty(out_shape, dtype=torch.float32, device=self.table.device)
     self.csr = self.geo.csr(self.rp, self.ids, self.sids, self.gains, max_ids_per_sample)
     self.ptrs = self.geo.shard_pointers(self.table)
+    # (plan_slots, plan_bags) emitted by this package's preprocessing for exactly these buffers.
+    self.plan = None
+    if forward_plan is not None and self.geo.l == 1:
+      slots, bags = forward_plan
+      if (slots.dtype != torch.int32 or bags.dtype != torch.int32 or not slots.is_cuda or not bags.is_cuda
+          or bags.numel() != 2 * self.geo.batch):
+        raise ValueError("forward_plan does not belong to these buffers")
+      self.plan = (slots, bags)
     self.local_shard = -1
     if self.geo.l != self.geo.c:  # one process per GPU: the other shards are peer mappings
       from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
@@ -177,6 +185,9 @@ class ForwardGroupCall:
         items[j].shard_tables = r.ptrs
         items[j].activations = r.act.data_ptr()
         items[j].local_shard = r.local_shard
+        if r.plan is not None:
+          items[j].plan_slots = r.plan[0].data_ptr()
+          items[j].plan_bags = r.plan[1].data_ptr()
       nbytes = lib.sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(items, len(idxs))
       if nbytes == 0:
         _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), None, 0, None))

@@ -19,7 +19,7 @@ def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lh
           max_ids_per_partition: int, max_unique_ids_per_partition: int, sharding_strategy: int = 1,
           quantization_config: tuple[float, float, int] | None = None, enable_minibatching: bool = False,
           num_sc_per_device: int | None = None, global_device_count: int | None = None,
-          local_device_count: int | None = None, max_ids_per_sample: int = 0):
+          local_device_count: int | None = None, max_ids_per_sample: int = 0, forward_plan=None):
   embedding_dim = utils.get_embedding_dim(embedding_table)
   utils.validate_abstract_eval_params(
       lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains,
@@ -39,7 +39,7 @@ def _prepare(lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lh
       lhs_row_pointers, lhs_local_embedding_ids, lhs_local_sample_ids, lhs_gains, embedding_table,
       device_batch_size=device_batch_size, num_sc_per_device=num_sc_per_device,
       global_device_count=global_device_count, local_device_count=local_device_count,
-      max_ids_per_sample=max_ids_per_sample)
+      max_ids_per_sample=max_ids_per_sample, forward_plan=forward_plan)
 
 
 tpu_sparse_dense_matmul_csr_primitive = _ops.Primitive("sparse_dense_matmul_csr", _prepare, _ops.run_forward_group)

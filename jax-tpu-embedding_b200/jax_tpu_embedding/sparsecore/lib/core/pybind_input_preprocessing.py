@@ -320,9 +320,11 @@ class BufferDict(dict):
   """
 
   token = None
+  forward_plans = None  # on the row-pointer dict: {stack name: (plan_slots, plan_bags)} for the forward
 
   def _changed(self):
     self.token = None
+    self.forward_plans = None
 
   def __setitem__(self, k, v):
     self._changed()
@@ -409,6 +411,14 @@ class _DensePlan:
         self.int_sizes.append(size)
         self.int_offsets.append(pos * 4)
         pos += size
+    # ... followed by the forward plan of every stack: [slots (one per input id) | bags (two per row)].
+    self.plan_sizes, self.plan_offsets = [], []
+    for si in range(n):
+      for size in (int(self.items[si].nnz), 2 * int(self.items[si].total_rows)):
+        pos = (pos + 3) // 4 * 4  # 16-byte aligned
+        self.plan_sizes.append(size)
+        self.plan_offsets.append(pos * 4)
+        pos += size
     self.int_total = pos
     self.float_offsets = [4 * sum(self.coos[:i]) for i in range(n)]
     self.float_total = sum(self.coos)
@@ -461,6 +471,11 @@ class _DensePlan:
       it.sample_ids = ibase + self.int_offsets[3 * si + 2]
       it.gains = fbase + self.float_offsets[si]
       it.stats = sbase + si * self.stats_size * 4
+      if device_output:
+        it.plan_slots = ibase + self.plan_offsets[2 * si]
+        it.plan_bags = ibase + self.plan_offsets[2 * si + 1]
+      else:
+        it.plan_slots = it.plan_bags = None
     stream = _native.current_stream_ptr()
     if self.groups is None:
       self._size_groups()
@@ -476,7 +491,7 @@ class _DensePlan:
     if status.any():
       si = int(np.flatnonzero(status)[0])
       _raise_for_status(host[si], p, s, self.names[si], *self.limits[si])
-    int_views = ints.split(self.int_sizes)
+    int_views = ints[:sum(self.int_sizes)].split(self.int_sizes)
     float_views = floats.split(self.coos)
     out_rp, out_ids, out_sids, out_gains = BufferDict(), BufferDict(), BufferDict(), BufferDict()
     stats = SparseDenseMatmulInputStats()
@@ -498,6 +513,10 @@ class _DensePlan:
       token = (ints.data_ptr(), floats.data_ptr(), id(self), bool(has_leading_dimension))
       for i, d in enumerate((out_rp, out_ids, out_sids, out_gains)):
         d.token = token + (i,)
+      out_rp.forward_plans = {
+          name: (ints[self.plan_offsets[2 * si] // 4:self.plan_offsets[2 * si] // 4 + self.plan_sizes[2 * si]],
+                 ints[self.plan_offsets[2 * si + 1] // 4:self.plan_offsets[2 * si + 1] // 4 + self.plan_sizes[2 * si + 1]])
+          for si, name in enumerate(self.names)}
     return out_rp, out_ids, out_sids, out_gains, 1, stats
 
 
@@ -574,7 +593,7 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
   plan = _dense_plan(features, feature_weights, feature_specs, l, global_device_count, s, allow_id_dropping)
   if plan is not None:
     return plan.run(features, feature_weights, has_leading_dimension, device_output)
-  out_rp, out_ids, out_sids, out_gains = {}, {}, {}, {}
+  out_rp, out_ids, out_sids, out_gains = BufferDict(), BufferDict(), BufferDict(), BufferDict()
   stats = SparseDenseMatmulInputStats()
   stacks = list(_group_by_stack(feature_specs).items())
   rp_size = max(p, 8) * s
@@ -584,14 +603,24 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
     stacked = members[0][1].table_spec.stacked_table_spec
     coos.append(_coo_buffer_size(stacked.max_ids_per_partition, global_device_count, s,
                                  stacked.suggested_coo_buffer_size_per_device))
-  # One int32 buffer holds [row pointers | embedding ids | sample ids] of every stack and device,
-  # one float32 buffer the gains, one int32 buffer the statistics.
+  batches = [[_DeviceBatch(members, features, feature_weights, d, l) for d in range(l)] for _, members in stacks]
+  # One int32 buffer holds [row pointers | embedding ids | sample ids] of every stack and device (and, for a
+  # single device with device output, the forward plan of every stack), one float32 buffer the gains, one
+  # int32 buffer the statistics.
+  with_plan = device_output and l == 1
   int_total = sum(l * (rp_size + 2 * c) for c in coos)
+  plan_offsets = []
+  if with_plan:
+    for (batch,) in batches:
+      for size in (batch.nnz, 2 * batch.total_rows):
+        int_total = (int_total + 3) // 4 * 4
+        plan_offsets.append((int_total, size))
+        int_total += size
   ints = torch.empty(int_total, dtype=torch.int32, device="cuda")
   floats = torch.empty(sum(l * c for c in coos), dtype=torch.float32, device="cuda")
   stats_dev = torch.empty((len(stacks), l, stats_size), dtype=torch.int32, device="cuda")
   items = (_native.PreprocessItem * (len(stacks) * l))()
-  keep, views = [], []
+  keep, views = batches, []
   ipos = fpos = 0
   for si, ((stack_name, members), coo) in enumerate(zip(stacks, coos)):
     stacked = members[0][1].table_spec.stacked_table_spec
@@ -604,8 +633,7 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
                                     int(stacked.max_ids_per_partition), int(stacked.max_unique_ids_per_partition),
                                     int(bool(allow_id_dropping)), int(coo), int(stacked.stack_vocab_size))
     for d in range(l):
-      batch = _DeviceBatch(members, features, feature_weights, d, l)
-      keep.append(batch)
+      batch = batches[si][d]
       it = items[si * l + d]
       it.ids = batch.ids.data_ptr()
       it.row_offsets = None if batch.offsets is None else batch.offsets.data_ptr()
@@ -619,6 +647,9 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
       it.sample_ids = sid_v[d].data_ptr()
       it.gains = gain_v[d].data_ptr()
       it.stats = stats_dev[si, d].data_ptr()
+      if with_plan:
+        it.plan_slots = ints.data_ptr() + 4 * plan_offsets[2 * si][0]
+        it.plan_bags = ints.data_ptr() + 4 * plan_offsets[2 * si + 1][0]
   # Groups are bounded by the 32-bit sort key: split greedily when a group does not fit.
   start, count = 0, len(items)
   stream = _native.current_stream_ptr()
@@ -652,6 +683,14 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
     if not device_output:
       arrays = tuple(t.cpu().numpy() for t in arrays)
     out_rp[stack_name], out_ids[stack_name], out_sids[stack_name], out_gains[stack_name] = arrays
+  if with_plan:
+    # The arrays keep the buffers alive; addresses plus layout identify every array of the call.
+    token = (ints.data_ptr(), floats.data_ptr(), tuple(coos), tuple(plan_offsets), rp_size, bool(has_leading_dimension))
+    for i, d in enumerate((out_rp, out_ids, out_sids, out_gains)):
+      d.token = token + (i,)
+    out_rp.forward_plans = {
+        name: tuple(ints[off:off + size] for off, size in plan_offsets[2 * si:2 * si + 2])
+        for si, (name, _) in enumerate(stacks)}
   return out_rp, out_ids, out_sids, out_gains, 1, stats
 
 

@@ -89,10 +89,12 @@ class SparseDenseMatmulInputStats:
   up to 8; id_drop_counters[table]: ids dropped by the limits or by a full buffer.
   """
 
-  max_ids_per_partition: dict[str, np.ndarray]
-  max_unique_ids_per_partition: dict[str, np.ndarray]
-  required_buffer_size_per_sc: dict[str, np.ndarray] = dataclasses.field(default_factory=dict)
-  id_drop_counters: dict[str, int] = dataclasses.field(default_factory=dict)
+  # The suffix names the field in the files of the FDO clients (lib/fdo): "<table><suffix>".
+  max_ids_per_partition: dict[str, np.ndarray] = dataclasses.field(metadata={"suffix": "_max_ids"})
+  max_unique_ids_per_partition: dict[str, np.ndarray] = dataclasses.field(metadata={"suffix": "_max_unique_ids"})
+  required_buffer_size_per_sc: dict[str, np.ndarray] = dataclasses.field(
+      metadata={"suffix": "_required_buffer_size"}, default_factory=dict)
+  id_drop_counters: dict[str, int] = dataclasses.field(metadata={"suffix": "_id_drop_counters"}, default_factory=dict)
 
   @classmethod
   def from_cc(cls, stats) -> "SparseDenseMatmulInputStats":
@@ -490,6 +492,15 @@ def _csr_key(rps, eids, sids, gains, names):
   return tuple((x.data_ptr(), tuple(x.shape), x.dtype) for x in arrays)
 
 
+def _forward_plans(rps, eids, sids, gains):
+  """{stack name: (plan_slots, plan_bags)} if the four dicts are the untouched output of ONE call of this
+  package's preprocessing (which emits the forward's sample-major plan with the buffers), else None."""
+  tokens = [getattr(d, "token", None) for d in (rps, eids, sids, gains)]
+  if any(t is None for t in tokens) or len({t[:-1] for t in tokens}) != 1:
+    return None
+  return getattr(rps, "forward_plans", None)
+
+
 def _tensor_key(tensors):
   if not all(_is_cuda_tensor(x) for x in tensors):
     return None
@@ -531,6 +542,8 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
   cached = _CALL_CACHE.get(key) if key is not None else None
   if cached is None:
     requests, local = [], 1
+    # Sample-major plans that this package's preprocessing emitted together with these buffers.
+    plans = _forward_plans(rps, eids, sids, gains)
     for name, stacked in stacked_table_specs.items():
       local = _local_devices(rps[name], global_device_count, num_sc_per_device)
       q = stacked.quantization_config
@@ -547,6 +560,7 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
           global_device_count=global_device_count,
           local_device_count=local,
           max_ids_per_sample=info.max_ids_per_sample[name],
+          forward_plan=plans.get(name) if plans else None,
       ))
     cached = (_ops.ForwardGroupCall(requests), local)
     if key is not None:
