@@ -7,7 +7,9 @@
  * memory.  No entry point allocates: scratch memory is a caller-owned device
  * workspace whose size comes from the matching *_workspace_bytes query.  Work is
  * enqueued on the given stream (a cudaStream_t passed as void*; NULL = default
- * stream) and is asynchronous unless stated otherwise.
+ * stream) and is asynchronous unless stated otherwise.  The lookup / update entry points copy
+ * their descriptors from host memory that does not outlive the call, so none of them may be called
+ * on a stream that is being captured into a CUDA graph; such calls fail without enqueuing work.
  *
  * Each declaration cites the interface of the reference project
  * (jax-ml/jax-tpu-embedding, paths relative to jax_tpu_embedding/sparsecore/)
@@ -46,6 +48,14 @@ const char* sc_status_name(int32_t status);
 int32_t sc_last_error(char* buffer, int32_t buffer_bytes);
 /* Number of CUDA kernels this library has launched in the process so far. */
 int64_t sc_launch_count(void);
+/* Stages.  Every call brackets its stages with NVTX ranges named after the reference's trace
+ * annotations (tsl::profiler::TraceMe in lib/core/input_preprocessing.cc:210-214, 413-417, 632-636:
+ * "ExtractCooTensors", "SortAndGroup", "FillBuffer"; @jax.named_call in lib/nn/embedding.py:1047, 1297).
+ * sc_phase_timing(1) additionally records a pair of CUDA events per stage on the call's stream and
+ * clears earlier records; sc_phase_report waits for them and writes "name=total_ms/count;..." in
+ * first-seen order, then clears; sc_phase_timing(0) stops recording.  Meant for benchmarks. */
+int32_t sc_phase_timing(int32_t enable);
+int32_t sc_phase_report(char* buffer, int32_t buffer_bytes);
 
 /* ---------------------------------------------------------------- buffer sizing
  * Replaces ComputeCooBufferSizePerDevice / GetRowPointersSizePerDevice
@@ -276,11 +286,12 @@ int32_t sc_ipc_release(void* peer_pointer);
  * SC_STATIC_SCRATCH_BYTES array built into the library image, so the call performs no
  * cudaMalloc / cudaFree and takes no workspace.  Limits: one shard and one SparseCore per buffer
  * (num_scs == num_sc_per_device == 1) and
- *   512 + chunks * (8 * dim + 1) + ceil(chunks / 32) * (4 * dim + 1)  <=  SC_STATIC_SCRATCH_BYTES
+ *   768 + chunks * (8 * dim + 1) + ceil(chunks / 32) * (4 * dim + 1)  <=  SC_STATIC_SCRATCH_BYTES
  * with chunks = ceil(coo_buffer_size / 32),
  * e.g. 65536 slots at dim 128; larger inputs are rejected with SC_WORKSPACE_TOO_SMALL.
  * The first call on each device resolves the address of the array (cudaGetSymbolAddress); make
- * that first call before any stream capture begins.  All calls on a device share the one array:
+ * that first call before any stream capture begins (a call on a capturing stream is rejected with
+ * SC_UNSUPPORTED).  All calls on a device share the one array:
  * the call overwrites every scratch word it later reads, so nothing needs clearing, but two
  * calls that overlap on the GPU (different streams) race and must be serialised by the caller. */
 #define SC_STATIC_SCRATCH_BYTES (2 * 1024 * 1024 + 64 * 1024)

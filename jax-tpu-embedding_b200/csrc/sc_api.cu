@@ -3,7 +3,13 @@
 #include <stdarg.h>
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <string>
 #include <string.h>
+#include <vector>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "sc_common.cuh"
 
@@ -34,7 +40,74 @@ int sm_count() {
   return cached[dev];
 }
 
+// ---- phases ------------------------------------------------------------------------------------
+namespace {
+struct PhaseRecord {
+  const char* name;
+  cudaEvent_t begin, end;
+};
+std::mutex g_phase_mutex;
+std::vector<PhaseRecord> g_phases;
+std::atomic<int> g_phase_timing{0};
+}  // namespace
+
+PhaseScope::PhaseScope(const char* name, cudaStream_t stream) : stream_(stream), slot_(-1) {
+  nvtxRangePushA(name);
+  if (!g_phase_timing.load(std::memory_order_relaxed)) return;
+  PhaseRecord r;
+  r.name = name;
+  if (cudaEventCreate(&r.begin) != cudaSuccess || cudaEventCreate(&r.end) != cudaSuccess) return;
+  cudaEventRecord(r.begin, stream);
+  std::lock_guard<std::mutex> lock(g_phase_mutex);
+  slot_ = (int)g_phases.size();
+  g_phases.push_back(r);
+}
+
+PhaseScope::~PhaseScope() {
+  if (slot_ >= 0) {
+    std::lock_guard<std::mutex> lock(g_phase_mutex);
+    if (slot_ < (int)g_phases.size()) cudaEventRecord(g_phases[slot_].end, stream_);
+  }
+  nvtxRangePop();
+}
+
 }  // namespace sc
+
+extern "C" int32_t sc_phase_timing(int32_t enable) {
+  std::lock_guard<std::mutex> lock(sc::g_phase_mutex);
+  for (auto& r : sc::g_phases) { cudaEventDestroy(r.begin); cudaEventDestroy(r.end); }
+  sc::g_phases.clear();
+  sc::g_phase_timing.store(enable ? 1 : 0);
+  return SC_OK;
+}
+
+extern "C" int32_t sc_phase_report(char* buffer, int32_t buffer_bytes) {
+  if (!buffer || buffer_bytes <= 0) SC_FAIL(SC_INVALID_ARGUMENT, "no buffer for the phase report");
+  std::lock_guard<std::mutex> lock(sc::g_phase_mutex);
+  std::map<std::string, std::pair<double, int>> total;
+  std::vector<std::string> order;
+  for (auto& r : sc::g_phases) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(r.end) == cudaSuccess && cudaEventElapsedTime(&ms, r.begin, r.end) == cudaSuccess) {
+      if (!total.count(r.name)) order.push_back(r.name);
+      total[r.name].first += ms;
+      total[r.name].second += 1;
+    }
+    cudaEventDestroy(r.begin);
+    cudaEventDestroy(r.end);
+  }
+  cudaGetLastError();
+  sc::g_phases.clear();
+  std::string out;
+  for (auto& name : order) {
+    char item[160];
+    snprintf(item, sizeof item, "%s%s=%.6f/%d", out.empty() ? "" : ";", name.c_str(), total[name].first, total[name].second);
+    out += item;
+  }
+  strncpy(buffer, out.c_str(), (size_t)buffer_bytes - 1);
+  buffer[buffer_bytes - 1] = '\0';
+  return SC_OK;
+}
 
 extern "C" int32_t sc_version(void) { return 100; }
 

@@ -67,5 +67,22 @@ void count_launch(int n = 1);
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// A named stage of a call: an NVTX range on the host thread (free when no tool listens) and, while
+// sc_phase_timing(1) is in effect, a pair of CUDA events on `stream` whose distance sc_phase_report
+// adds up per name.  Names follow the reference's trace annotations where it has them
+// (tsl::profiler::TraceMe in lib/core/input_preprocessing.cc:210-214, 413-417, 632-636;
+// @jax.named_call in lib/nn/embedding.py:1047, 1297).
+class PhaseScope {
+ public:
+  PhaseScope(const char* name, cudaStream_t stream);
+  ~PhaseScope();
+  PhaseScope(const PhaseScope&) = delete;
+  PhaseScope& operator=(const PhaseScope&) = delete;
+
+ private:
+  cudaStream_t stream_;
+  int slot_;
+};
+
 }  // namespace sc
 #endif  // SC_COMMON_CUH_

@@ -28,6 +28,7 @@
 // compiled with -fmad=false) so that sequential sums match a float32 CPU loop.
 #include <math.h>
 
+#include <mutex>
 #include <vector>
 
 #include "sc_common.cuh"
@@ -459,6 +460,14 @@ __global__ void fwd_single_bags_kernel(const TableDesc* __restrict__ tabs, int c
   if (sid >= 0 && sid < v.bsc) bags[tabs[t].act_base + (uint32_t)(s * v.bsc + sid)] = make_uint2(gq, gq + 1u);
 }
 
+// Asks L2 for the `bytes` of a table row that a later instruction of this warp will load.  The
+// request holds no register, so a lane can have the rows of many entries on their way while the
+// warp is still summing earlier ones.
+__device__ __forceinline__ void prefetch_row(const float* row, int bytes) {
+  const char* p = reinterpret_cast<const char*>(row);
+  for (int off = 0; off < bytes; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + off));
+}
+
 // What a forward warp knows about one of its 32 activation rows.
 struct RowMeta {
   const float* src;  // table row of the first entry, nullptr if it contributes nothing
@@ -467,18 +476,19 @@ struct RowMeta {
   float gain;
 };
 
-// One warp per 32 consecutive global activation rows.  Lane l first reads the bag of row r0 + l and
-// resolves its first entry, so the dependent index loads of 32 rows overlap.  The warp is then
-// split into 32 / G groups of G lanes; a group owns every (32 / G)-th row and covers one table row
-// with K vectors of width W per lane.  The lanes of a group resolve G entries of the bag at a
-// time (and the next G while these are summed); the table rows of up to U entries are loaded before
-// the first of them is added, in bag order, so 32 / G * U rows are in flight per warp.  Every
-// activation row is written exactly once; the sum runs in ascending slot order.
+// One warp per 32 consecutive global activation rows.  Lane l first reads the bag of row r0 + l,
+// resolves its first entry and asks L2 for that table row, so the dependent index loads of 32 rows
+// overlap and their rows are on their way before the first sum starts.  The warp is then split
+// into 32 / G groups of G lanes; a group owns every (32 / G)-th row and covers one table row with
+// K vectors of width W per lane.  The lanes of a group resolve G entries of the bag at a time -
+// the next G (with an L2 prefetch of their rows) while these are summed - and the table rows of U
+// entries are loaded before the first of them is added, in bag order.  Every activation row is
+// written exactly once; the sum runs in ascending slot order.
 template <int W, int K, int G>
-__global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
+__global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : 3) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
-  constexpr int U = K >= 4 ? 4 : 8;
+  constexpr int U = K >= 4 ? 2 : K == 2 ? 4 : 8;  // rows in registers per group: 8 vectors per lane
   __shared__ RowMeta s_meta[kWarpsPerBlock][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + wib) * 32u;
@@ -493,7 +503,10 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
       const uint2 bag = reinterpret_cast<const uint2*>(td.bags)[my_r - td.act_base];
       m.begin = bag.x;
       m.end = bag.y;
-      if (m.end > m.begin) m.src = resolve_entry(td, m.begin, &m.gain);
+      if (m.end > m.begin) {
+        m.src = resolve_entry(td, m.begin, &m.gain);
+        if (m.src != nullptr) prefetch_row(m.src, td.v.dim * 4);
+      }
     }
     s_meta[wib][lane] = m;
   }
@@ -532,12 +545,18 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_kernel(const TableDesc* __r
       const float* c_ptr = nullptr;
       float c_gain = 0.f;
       if (gl == 0) { c_ptr = m.src; c_gain = m.gain; }
-      else if (base + gl < m.end) c_ptr = resolve_entry(td, base + gl, &c_gain);
+      else if (base + gl < m.end) {
+        c_ptr = resolve_entry(td, base + gl, &c_gain);
+        if (c_ptr != nullptr) prefetch_row(c_ptr, dim * 4);
+      }
       for (;;) {
         const uint32_t nbase = base + G;
         const float* n_ptr = nullptr;
         float n_gain = 0.f;
-        if (nbase + gl < m.end) n_ptr = resolve_entry(td, nbase + gl, &n_gain);
+        if (nbase + gl < m.end) {
+          n_ptr = resolve_entry(td, nbase + gl, &n_gain);
+          if (n_ptr != nullptr) prefetch_row(n_ptr, dim * 4);
+        }
         const int cnt = (int)min((uint32_t)G, m.end - base);
         for (int i0 = 0; i0 < cnt; i0 += U) {
           VT x[U][K];
@@ -1698,6 +1717,11 @@ struct GroupImage {
 
 // Copies the image to `dst` (device) after pointing every table at its slice of the pool.
 cudaError_t upload(GroupImage& g, char* dst, const std::vector<int>& pool_index, cudaStream_t cs) {
+  {  // the copy below reads host memory that does not outlive this call
+    cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(cs, &status) == cudaSuccess && status != cudaStreamCaptureStatusNone)
+      return cudaErrorStreamCaptureUnsupported;
+  }
   float** pool_dev = reinterpret_cast<float**>(dst + g.pool_offset());
   for (size_t i = 0; i < g.tabs.size(); ++i) {
     const int P = g.tabs[i].v.P;
@@ -1763,9 +1787,9 @@ inline int dispatch_fwd_ring(const TableDesc* tabs, int count, uint32_t total_ac
   return launch_fwd_ring<8, 1>(tabs, count, total_act, st);
 }
 
-// The cp.async ring is the default gather; SC_FWD_KERNEL=groups selects the register-only kernel.
+// The register kernel with L2 prefetch is the default gather; SC_FWD_KERNEL=ring selects the cp.async ring.
 inline bool fwd_ring_enabled() {
-  static const bool on = [] { const char* e = getenv("SC_FWD_KERNEL"); return !(e && strcmp(e, "groups") == 0); }();
+  static const bool on = [] { const char* e = getenv("SC_FWD_KERNEL"); return e && strcmp(e, "ring") == 0; }();
   return on;
 }
 
@@ -2166,6 +2190,7 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
   const uint32_t total_slots = (uint32_t)p.total_slots, total_act = (uint32_t)p.total_act;
 
+  PhaseScope whole("tpu_sparse_dense_matmul", cs);
   SideStream* side = nullptr;
   if (p.remote_floats > 0) {
     // Rows of remote shards: fetch each distinct row once, then gather from the local copies.  The
@@ -2175,6 +2200,7 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
     SC_CUDA_OK(cudaEventRecord(side->fork, cs));
     SC_CUDA_OK(cudaStreamWaitEvent(side->stream, side->fork, 0));
     cudaStream_t fs = side->stream;
+    PhaseScope phase("FetchRemoteRows", fs);
     fwd_remote_heads_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, fs>>>(tabs, count, total_slots, s.heads);
     SC_LAUNCH_OK("fwd_remote_heads_kernel");
     uint32_t* total_jobs = s.heads_temp + scan_temp_elems((size_t)total_slots);
@@ -2187,11 +2213,13 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
     SC_CUDA_OK(cudaEventRecord(side->join, fs));
   }
   if (p.mode == kPlanSingle) {
+    PhaseScope phase("ForwardPlan", cs);
     SC_CUDA_OK(cudaMemsetAsync(s.bags, 0, (size_t)total_act * 2 * sizeof(uint32_t), cs));
     fwd_single_bags_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, cs>>>(tabs, count, total_slots,
                                                                                       reinterpret_cast<uint2*>(s.bags));
     SC_LAUNCH_OK("fwd_single_bags_kernel");
   } else if (p.mode == kPlanBuild) {
+    PhaseScope phase("ForwardPlan", cs);
     uint32_t* big_count = s.offsets + total_act + 1;
     SC_CUDA_OK(cudaMemsetAsync(s.offsets, 0, ((size_t)total_act + 2) * sizeof(uint32_t), cs));
     const unsigned slot_blocks = (unsigned)ceil_div(total_slots, kBlock);
@@ -2208,6 +2236,7 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
     SC_LAUNCH_OK("fwd_bigrow_kernel");
   }
   if (side != nullptr) SC_CUDA_OK(cudaStreamWaitEvent(cs, side->join, 0));  // the gather reads the fetched rows
+  PhaseScope phase("GatherCombine", cs);
   if (ring) return dispatch_fwd_ring(tabs, count, total_act, p.max_dim, cs);
 #define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, cs)
   SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL);
@@ -2293,6 +2322,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     }
     img.tabs.push_back(td);
   }
+  PhaseScope whole("tpu_sparse_dense_matmul_grad", cs);
   const uint32_t total_ent = (uint32_t)p.total_ent, invalid = (uint32_t)p.total_rows;
   if (total_ent > 0) {
     // The sorted list lives in one of the two sort buffers; which one is known before launching.
@@ -2307,6 +2337,8 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     SC_CUDA_OK(cudaMemcpyAsync(s.pull, pull_host.data(), pull_host.size() * sizeof(PullSrc), cudaMemcpyHostToDevice, cs));
   SC_CUDA_OK(upload(img, s.image, pool_index, cs));
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
+  {
+  PhaseScope order_phase("OrderEntries", cs);
   if (total_ent > 0 && p.counting) {
     // Entries of several SparseCores / shards / devices: order them by global row first, entries of
     // one row in entry order (source, sample): counting sort on the row, one for all tables.
@@ -2342,6 +2374,8 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
                                                                               s.ranges);
     SC_LAUNCH_OK("bwd_ranges_kernel");
   }
+  }
+  PhaseScope update_phase("ReduceAndUpdate", cs);
   const uint32_t total_chunks = (uint32_t)p.total_chunks;
   if (ring) return dispatch_bwd_pipe(tabs, count, total_chunks, s.update, p.max_slots, p.kind >= SC_OPT_ADAGRAD_MOMENTUM, p.max_dim, cs);
 #define SC_BWD_CALL(W, K, G) launch_bwd<W, K, G>(tabs, count, total_chunks, s.update, p.max_slots, cs)
@@ -2452,6 +2486,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_stage(const sc_grad_item_t* items
   StageScratch s;
   if (!carve_stage(ws, p, &s)) SC_FAIL(SC_WORKSPACE_TOO_SMALL, "staging needs %zu workspace bytes, got %zu", ws.used(), workspace_bytes);
   cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  PhaseScope whole("StageGradients", cs);
 
   std::vector<CopyJob> jobs;
   GroupImage img;
@@ -2567,6 +2602,21 @@ static __device__ __align__(256) unsigned char g_static_scratch[SC_STATIC_SCRATC
 namespace {
 // Device address of g_static_scratch per device ordinal, resolved on first use.
 void* g_static_scratch_ptr[64] = {nullptr};
+std::mutex g_static_scratch_mutex;
+// The documented size limit counts 512 bytes for the descriptor and 256 for the three pointers.
+static_assert(sizeof(TableDesc) <= 512, "update the limit documented for sc_sparse_dense_matmul_grad_static");
+constexpr size_t kStaticImageBytes = 512 + 256;
+
+// True while `stream` records into a CUDA graph.  The descriptors of a call travel by copies from
+// host memory that is gone when a graph replays, so such calls are refused.
+bool stream_is_capturing(cudaStream_t stream) {
+  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &status) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return status != cudaStreamCaptureStatusNone;
+}
 }  // namespace
 
 extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const float* activation_grad,
@@ -2591,7 +2641,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
   if (!pick_group_shape(v.dim, &w, &k, &g)) SC_FAIL(SC_UNSUPPORTED, "dim %d is too large for the update kernel", v.dim);
 
   // Layout inside the static array: [TableDesc | 3 shard pointers | partial sums | group sums | chunk flags | group flags].
-  const size_t image = align_up(sizeof(TableDesc), 256) + align_up(3 * sizeof(float*), 256);
+  const size_t image = kStaticImageBytes;
   const uint32_t chunks = (uint32_t)ceil_div(v.coo, 32);
   const size_t partial_bytes = (size_t)2 * chunks * (size_t)v.dim * sizeof(float);
   const size_t groups = update_groups(chunks);
@@ -2603,24 +2653,31 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_static(const sc_csr_t* csr, const
             "holds %d; use sc_sparse_dense_matmul_grad with a caller workspace instead", need, v.coo, v.dim,
             (int)SC_STATIC_SCRATCH_BYTES);
 
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (stream_is_capturing(cs))
+    SC_FAIL(SC_UNSUPPORTED, "the allocation-free update copies its descriptor from the caller's stack and cannot be recorded "
+                            "into a CUDA graph");
   int dev = 0;
   SC_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) SC_FAIL(SC_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (g_static_scratch_ptr[dev] == nullptr) {
-    // In host code the array name is only a handle; the kernels need its device address.
-    void* ptr = nullptr;
-    SC_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));
-    g_static_scratch_ptr[dev] = ptr;
+  char* base;
+  {
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+      // In host code the array name is only a handle; the kernels need its device address.
+      void* ptr = nullptr;
+      SC_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+      g_static_scratch_ptr[dev] = ptr;
+    }
+    base = static_cast<char*>(g_static_scratch_ptr[dev]);
   }
-  char* base = static_cast<char*>(g_static_scratch_ptr[dev]);
-  float** pool_dev = reinterpret_cast<float**>(base + align_up(sizeof(TableDesc), 256));
+  float** pool_dev = reinterpret_cast<float**>(base + 512);
   UpdateScratch u;
   u.partial = reinterpret_cast<float*>(base + image);
   u.group_partial = reinterpret_cast<float*>(base + image + partial_bytes);
   u.flags = reinterpret_cast<uint8_t*>(base + image + partial_bytes + group_bytes);
   u.group_flags = u.flags + chunks;
   u.pstride = v.dim;
-  cudaStream_t cs = static_cast<cudaStream_t>(stream);
 
   struct { TableDesc td; } host;
   memset(&host, 0, sizeof host);

@@ -591,30 +591,43 @@ extern "C" int32_t sc_preprocess_grouped(const sc_preprocess_item_t* items, int3
   g.total_slots = (uint32_t)pl.total_slots; g.total_parts = (uint32_t)pl.total_parts;
   const uint32_t n = g.total_ids;
 
-  extract_kernel<<<(unsigned)ceil_div(g.total_rows, kBlock), kBlock, 0, cs>>>(g, s.sort.keys[0], s.row_of, s.gain_of, s.row_gain,
-                                                                            s.error_flags);
-  SC_LAUNCH_OK("extract_kernel");
-  int res = 0;
-  SC_CUDA_OK(radix_sort_pairs(s.sort, (size_t)n, pl.total_bits, true, &res, cs));
-  const uint32_t* keys = s.sort.keys[res];
-  const uint32_t* vals = s.sort.vals[res];
-  if (n > 0) {
-    flags_kernel<<<(unsigned)ceil_div(n, kBlock), kBlock, 0, cs>>>(n, keys, vals, s.row_of, s.row_sorted, s.cnt);
-    SC_LAUNCH_OK("flags_kernel");
+  PhaseScope whole("jax_sc_embedding::PreprocessSparseDenseMatmulInput", cs);
+  {
+    PhaseScope phase("ExtractCooTensors", cs);
+    extract_kernel<<<(unsigned)ceil_div(g.total_rows, kBlock), kBlock, 0, cs>>>(g, s.sort.keys[0], s.row_of, s.gain_of, s.row_gain,
+                                                                              s.error_flags);
+    SC_LAUNCH_OK("extract_kernel");
   }
-  SC_CUDA_OK(exclusive_scan<uint64_t>(s.cnt, s.cnt, (size_t)n, s.scan_temp, s.cnt + n, cs));
-  bounds_kernel<<<(unsigned)ceil_div((int64_t)g.total_parts + count, kBlock), kBlock, 0, cs>>>(g, n, keys, s.bounds);
-  SC_LAUNCH_OK("bounds_kernel");
-  layout_kernel<<<count, kMaxPartitions, 0, cs>>>(g, s.cnt, s.bounds, s.part_start, s.part_written, s.error_flags);
-  SC_LAUNCH_OK("layout_kernel");
-  fill_kernel<<<(unsigned)ceil_div(g.total_slots, kBlock), kBlock, 0, cs>>>(g);
-  SC_LAUNCH_OK("fill_kernel");
-  if (n > 0) {
-    pack_kernel<<<(unsigned)ceil_div(n, kBlock), kBlock, 0, cs>>>(g, n, keys, vals, s.row_sorted, s.gain_of, s.row_gain, s.cnt,
-                                                                s.bounds, s.part_start, s.part_written);
-    SC_LAUNCH_OK("pack_kernel");
+  int res = 0;
+  const uint32_t* keys = nullptr;
+  const uint32_t* vals = nullptr;
+  {
+    PhaseScope phase("SortAndGroup", cs);
+    SC_CUDA_OK(radix_sort_pairs(s.sort, (size_t)n, pl.total_bits, true, &res, cs));
+    keys = s.sort.keys[res];
+    vals = s.sort.vals[res];
+    if (n > 0) {
+      flags_kernel<<<(unsigned)ceil_div(n, kBlock), kBlock, 0, cs>>>(n, keys, vals, s.row_of, s.row_sorted, s.cnt);
+      SC_LAUNCH_OK("flags_kernel");
+    }
+    SC_CUDA_OK(exclusive_scan<uint64_t>(s.cnt, s.cnt, (size_t)n, s.scan_temp, s.cnt + n, cs));
+    bounds_kernel<<<(unsigned)ceil_div((int64_t)g.total_parts + count, kBlock), kBlock, 0, cs>>>(g, n, keys, s.bounds);
+    SC_LAUNCH_OK("bounds_kernel");
+    layout_kernel<<<count, kMaxPartitions, 0, cs>>>(g, s.cnt, s.bounds, s.part_start, s.part_written, s.error_flags);
+    SC_LAUNCH_OK("layout_kernel");
+  }
+  {
+    PhaseScope phase("FillBuffer", cs);
+    fill_kernel<<<(unsigned)ceil_div(g.total_slots, kBlock), kBlock, 0, cs>>>(g);
+    SC_LAUNCH_OK("fill_kernel");
+    if (n > 0) {
+      pack_kernel<<<(unsigned)ceil_div(n, kBlock), kBlock, 0, cs>>>(g, n, keys, vals, s.row_sorted, s.gain_of, s.row_gain, s.cnt,
+                                                                  s.bounds, s.part_start, s.part_written);
+      SC_LAUNCH_OK("pack_kernel");
+    }
   }
   if (pl.any_plan) {
+    PhaseScope phase("ForwardPlan", cs);
     uint32_t* big_count = s.big_rows + n / kSerialBagLimit + 1;
     SC_CUDA_OK(cudaMemsetAsync(big_count, 0, sizeof(uint32_t), cs));
     plan_sort_kernel<<<(unsigned)ceil_div(g.total_rows, kBlock), kBlock, 0, cs>>>(g, s.big_rows, big_count);

@@ -102,6 +102,10 @@ def lib() -> ctypes.CDLL:
     l.sc_status_name.argtypes = [c_i32]
     l.sc_last_error.restype = c_i32
     l.sc_last_error.argtypes = [ctypes.c_char_p, c_i32]
+    l.sc_phase_timing.restype = c_i32
+    l.sc_phase_timing.argtypes = [c_i32]
+    l.sc_phase_report.restype = c_i32
+    l.sc_phase_report.argtypes = [ctypes.c_char_p, c_i32]
     l.sc_compute_theoretical_max_coo_buffer_size.restype = c_i64
     l.sc_compute_theoretical_max_coo_buffer_size.argtypes = [c_i32, c_i32, c_i32]
     l.sc_compute_coo_buffer_size_per_device.restype = c_i64
@@ -163,6 +167,24 @@ def last_error() -> str:
   return buf.value.decode("utf-8", "replace")
 
 
+def phase_timing(enable: bool) -> None:
+  """Starts (and clears) or stops the per-stage CUDA-event timing of the library."""
+  lib().sc_phase_timing(1 if enable else 0)
+
+
+def phase_report() -> dict:
+  """{stage name: (total milliseconds, count)} since phase_timing(True); clears the records."""
+  buf = ctypes.create_string_buffer(8192)
+  check(lib().sc_phase_report(buf, 8192))
+  out = {}
+  for item in buf.value.decode().split(";"):
+    if "=" in item:
+      name, rest = item.split("=")
+      ms, count = rest.split("/")
+      out[name] = (float(ms), int(count))
+  return out
+
+
 def check(status: int) -> None:
   """Raises ValueError for invalid arguments / id-limit violations, RuntimeError otherwise."""
   if status == SC_OK:
@@ -205,6 +227,11 @@ def workspace(nbytes: int, tag: str = "default"):
     buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device="cuda")
     _workspaces[key] = buf
   return buf
+
+
+def clear_workspaces() -> None:
+  """Drops the cached workspace buffers (they are re-created on demand)."""
+  _workspaces.clear()
 
 
 def as_device(x, dtype, name: str):

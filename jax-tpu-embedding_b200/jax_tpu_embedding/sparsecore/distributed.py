@@ -144,11 +144,38 @@ def shard_pointers(tensor, geo):
   return arr
 
 
-def stream_barrier() -> None:
+_barrier_events: list | None = None  # (name, begin event, end event) while barrier timing is on
+
+
+def time_barriers(enable: bool) -> None:
+  """Starts (and clears) or stops recording a pair of CUDA events around every stream barrier."""
+  global _barrier_events
+  _barrier_events = [] if enable else None
+
+
+def barrier_times() -> dict:
+  """{barrier name: total milliseconds} since time_barriers(True); clears the records."""
+  out: dict = {}
+  if _barrier_events:
+    torch = _native.torch_mod()
+    torch.cuda.synchronize()
+    for name, begin, end in _barrier_events:
+      out[name] = out.get(name, 0.0) + begin.elapsed_time(end)
+    _barrier_events.clear()
+  return out
+
+
+def stream_barrier(name: str = "Barrier") -> None:
   """All work enqueued so far on every rank's current stream completes before any rank continues."""
   torch = _native.torch_mod()
   if is_active():
+    if _barrier_events is not None:
+      begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+      begin.record()
     torch.distributed.all_reduce(_ctx.token, group=_ctx.group)
+    if _barrier_events is not None:
+      end.record()
+      _barrier_events.append((name, begin, end))
     _ctx.peers_may_read_exchange = False
     _ctx.peers_may_write_tables = False
 
@@ -156,13 +183,13 @@ def stream_barrier() -> None:
 def barrier_before_lookup() -> None:
   """Remote rows are about to be read: needed only if a peer may still be updating its shard."""
   if is_active() and _ctx.peers_may_write_tables:
-    stream_barrier()
+    stream_barrier("BarrierBeforeLookup")
 
 
 def barrier_before_staging() -> None:
   """The exchange buffers are about to be overwritten: needed only if a peer may still read them."""
   if is_active() and _ctx.peers_may_read_exchange:
-    stream_barrier()
+    stream_barrier("BarrierBeforeStaging")
 
 
 def note_update_launched() -> None:
@@ -170,6 +197,38 @@ def note_update_launched() -> None:
   if _ctx is not None:
     _ctx.peers_may_read_exchange = True
     _ctx.peers_may_write_tables = True
+
+
+def release_all() -> None:
+  """Collective: frees every peer-visible allocation of this process and unmaps the peers' ones.
+
+  Tensors returned by `alloc` (tables, slot variables, exchange buffers) must not be used afterwards.  All
+  ranks finish their work and drop their mappings before any rank frees its memory.
+  """
+  if _ctx is None:
+    return
+  torch = _native.torch_mod()
+  lib = _native.lib()
+  torch.cuda.synchronize()
+  torch.distributed.barrier(group=_ctx.group)
+  for a in _ctx.allocations:
+    for r, base in enumerate(a.peer_bases):
+      if r != _ctx.rank:
+        _native.check(lib.sc_ipc_release(_native.c_vp(base)))
+  torch.distributed.barrier(group=_ctx.group)
+  for a in _ctx.allocations:
+    _native.check(lib.sc_peer_free(_native.c_vp(a.base)))
+  _ctx.allocations.clear()
+  _ctx.exchange.clear()
+  _ctx.peers_may_read_exchange = False
+  _ctx.peers_may_write_tables = True
+
+
+def shutdown() -> None:
+  """release_all() and forget the process group (call before destroying it)."""
+  global _ctx
+  release_all()
+  _ctx = None
 
 
 def exchange_buffers(key, rp_size: int, coo: int, batch: int, dim: int):

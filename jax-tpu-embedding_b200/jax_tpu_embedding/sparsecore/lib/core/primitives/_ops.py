@@ -336,7 +336,7 @@ class GradGroupCall:
       for items, idxs, nbytes in self.groups:
         ws = _native.workspace(nbytes, "lookup")
         _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
-      distributed.stream_barrier()  # every peer's exchange buffers are complete
+      distributed.stream_barrier("BarrierAfterStaging")  # every peer's exchange buffers are complete
     for items, idxs, nbytes in self.groups:
       ws = _native.workspace(nbytes, "lookup")
       _native.check(lib.sc_sparse_dense_matmul_grad_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))

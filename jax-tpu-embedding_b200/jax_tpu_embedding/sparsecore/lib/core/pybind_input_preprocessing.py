@@ -523,6 +523,11 @@ class _DensePlan:
 _DENSE_PLANS: dict = {}
 
 
+def clear_caches() -> None:
+  """Forgets the cached per-spec preprocessing plans."""
+  _DENSE_PLANS.clear()
+
+
 def _dense_plan(features, feature_weights, feature_specs, local_device_count, global_device_count, s, allow_id_dropping):
   """The cached _DensePlan of this call, or None if the inputs do not qualify."""
   torch = _native.torch_mod()

@@ -507,6 +507,16 @@ def _tensor_key(tensors):
   return tuple((x.data_ptr(), tuple(x.shape)) for x in tensors)
 
 
+def clear_caches() -> None:
+  """Forgets the cached launch descriptors and spec facts (they hold addresses of tables and buffers).
+
+  Call it after freeing or replacing embedding variables whose addresses may be reused by new ones.
+  """
+  _CALL_CACHE.clear()
+  _SPEC_INFO.clear()
+  pybind_input_preprocessing.clear_caches()
+
+
 def _cache_put(key, value):
   if len(_CALL_CACHE) > 32:
     _CALL_CACHE.clear()

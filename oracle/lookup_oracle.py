@@ -25,8 +25,11 @@ Everything is float32; sums run in buffer order (device, SparseCore, partition,
 slot), which is ascending table row per sample and ascending sample per row.
 Only the touched rows change ("lazy" update).
 
-Parity status: pinned for the arithmetic by the integer-valued fixtures restated
-in tests/test_oracle_lookup.py.  One behaviour is unpinned in the reference: how
+Parity status: pinned.  tests/test_golden.py checks forward, SGD and Adagrad against
+tests/golden/lookup_known_answers.npz and Adam (textbook form with bias-corrected moments),
+AdagradMomentum, FTRL, LaProp and F2A against tests/golden/optimizer_known_answers.npz; both files
+hold float64 results of the formulas that the reference's primitive tests state, computed without
+this module (tests/golden/make_fixtures.py).  One behaviour is unpinned in the reference: how
 the device orders a non-linear optimizer when one row is hit from several source
 SparseCores.  The contract here is: reduce every contribution first, apply once.
 """

@@ -12,6 +12,9 @@
    sparse_dense_matmul_grad_with_sgd_test.py:100-163, sparse_dense_matmul_grad_with_adagrad_test.py:330-400):
    inputs restated from those files, expected values computed by the dense formulas the tests
    state, independently of the oracle's CSR walk.
+3. optimizer_known_answers.npz - one weighted multi-hot batch updated by Adam (textbook form with
+   bias-corrected moments) and by AdagradMomentum / FTRL / LaProp / F2A, in float64, from the
+   formulas of the reference's primitive tests (cited at known_answer_optimizer_cases).
 """
 
 from __future__ import annotations
@@ -150,9 +153,96 @@ def known_answer_lookup_cases():
   print(f"lookup_known_answers.npz: {len(cases)} cases")
 
 
+def known_answer_optimizer_cases():
+  """Known answers for Adam and the four two-slot optimizers, in float64, from the formulas that the
+  reference's own tests state INDEPENDENTLY of the primitives' operand conventions:
+
+  * Adam: the textbook form with bias-corrected m_hat, v_hat
+    (primitives/tests/sparse_dense_matmul_grad_with_adam_test.py:403-411), while the primitive receives
+    alpha_t and epsilon_hat (:540-542);
+  * FTRL: sign / threshold form (..._ftrl_test.py:235-320);
+  * AdagradMomentum (..._adagrad_momentum_test.py:274-318), LaProp (..._laprop_test.py:483-489),
+    F2A (..._f2a_test.py:589-617).
+
+  One multi-hot weighted batch; the table gradient is the dense definition sum_w w * activation_grad.
+  """
+  vocab, dim, batch = 32, 8, 16
+  rng = np.random.default_rng(4321)
+  ids = rng.integers(0, vocab, size=(batch, 4)).astype(np.int32)
+  weights = rng.choice([0.5, 1.0, 2.0], size=(batch, 4)).astype(np.float32)
+  table = rng.normal(0.0, 0.5, size=(vocab, dim)).astype(np.float32)
+  act_grad = (rng.normal(size=(batch, dim)) * 0.05).astype(np.float32)
+  slot_a = rng.uniform(0.05, 0.3, size=(vocab, dim)).astype(np.float32)   # accumulator / mu / momentum
+  slot_b = rng.uniform(0.01, 0.2, size=(vocab, dim)).astype(np.float32)   # velocity / linear / nu / momentum
+  steps = np.floor(rng.uniform(0.0, 5.0, size=(vocab, dim))).astype(np.float32)  # F2A local step
+  g = np.zeros((vocab, dim), np.float64)
+  for s in range(batch):
+    for j in range(4):
+      g[ids[s, j]] += float(weights[s, j]) * act_grad[s].astype(np.float64)
+  touched = np.zeros(vocab, bool)
+  touched[np.unique(ids)] = True
+  w = table.astype(np.float64)
+  a64, b64, st64 = slot_a.astype(np.float64), slot_b.astype(np.float64), steps.astype(np.float64)
+  arrays = dict(ids=ids, weights=weights, table=table, grad=act_grad, slot_a=slot_a, slot_b=slot_b, steps=steps)
+  cases = []
+
+  def add(name, kind, hyper, flags, slots_in, outs):
+    keep = lambda new, old: np.where(touched[:, None], new, old).astype(np.float32)
+    olds = [w] + [arrays[k].astype(np.float64) for k in slots_in]
+    for i, (new, old) in enumerate(zip(outs, olds)):
+      arrays[f"{name}_out{i}"] = keep(new, old)
+    cases.append(dict(name=name, kind=kind, hyper=[float(h) for h in hyper], flags=flags, slots=slots_in))
+
+  # Adam, textbook: t is the number of steps taken before this one.
+  for t in (0, 7):
+    lr, b1, b2, eps = 1e-2, 0.9, 0.999, 1e-8
+    m = b1 * a64 + (1 - b1) * g
+    v = b2 * b64 + (1 - b2) * g * g
+    m_hat, v_hat = m / (1 - b1 ** (t + 1)), v / (1 - b2 ** (t + 1))
+    add(f"adam_step{t}", "adam", (lr, b1, b2, eps, t), {}, ["slot_a", "slot_b"],
+        [w - lr * m_hat / (np.sqrt(v_hat) + eps), m, v])
+  # Adagrad momentum.
+  for tag, (lr, mom, beta2, eps, k, nesterov) in (("plain", (0.05, 0.9, 1.0, 1e-10, 2.0, False)),
+                                                    ("nesterov_ema", (0.05, 0.8, 0.95, 1e-6, 3.0, True))):
+    a_n = a64 + g * g if beta2 == 1.0 else beta2 * a64 + (1 - beta2) * g * g
+    g_hat = (a_n + eps) ** (-1.0 / k) * g
+    m_n = mom * b64 + g_hat
+    delta = lr * (mom * m_n + g_hat) if nesterov else lr * m_n
+    add(f"adagrad_momentum_{tag}", "adagrad_momentum", (lr, mom, beta2, eps, k), {"use_nesterov": nesterov},
+        ["slot_a", "slot_b"], [w - delta, a_n, m_n])
+  # FTRL.
+  for tag, (lr, power, l1, l2, beta, mlr) in (("plain", (0.05, -0.5, 0.0, 0.0, 0.0, False)),
+                                               ("regularised_mlr", (0.05, -0.5, 0.02, 0.01, 0.1, True)),
+                                               ("l1_only", (0.05, -0.4, 0.05, 0.0, 0.0, False))):
+    a_new = a64 + g * g
+    p_old, p_new = a64 ** (-power), a_new ** (-power)  # the exponent is the negative of lr_power
+    delta_p = p_new - p_old
+    lin = b64 + lr * g - delta_p * w if mlr else b64 + g - (delta_p / lr) * w
+    thr = lr * l1 if mlr else l1
+    denom = p_new + 2 * lr * l2 + beta if mlr else (p_new + beta) / lr + 2 * l2
+    w_new = np.where(np.abs(lin) > thr, (np.sign(lin) * thr - lin) / denom, 0.0)
+    add(f"ftrl_{tag}", "ftrl", (lr, power, l1, l2, beta), {"multiply_linear_by_learning_rate": mlr},
+        ["slot_a", "slot_b"], [w_new, a_new, lin])
+  # LaProp.
+  lr, b1, decay, eps = 0.01, 0.9, 0.73, 1e-12
+  nu_new = decay * b64 + (1 - decay) * (g * g + eps)
+  mu_new = b1 * a64 + np.sqrt(1 - b1 ** 2) * (g / np.sqrt(nu_new))
+  add("laprop", "laprop", (lr, b1, decay, eps), {}, ["slot_a", "slot_b"], [w - lr * mu_new, mu_new, nu_new])
+  # F2A.
+  lr, rho, l1, l2, cap, gstep = 0.05, 0.5, 0.001, 0.002, 3.0, 40.0
+  l_new = st64 + 1.0
+  fa = np.minimum((max(gstep, 1.0) / l_new) ** rho, cap)
+  a_new = a64 + g * g
+  update = fa * g / np.sqrt(a_new) + l1 * np.sign(w) + l2 * w
+  add("f2a", "f2a", (lr, rho, l1, l2, cap, gstep), {}, ["slot_a", "steps"], [w - lr * update, a_new, l_new])
+  fio.save(os.path.join(HERE, "optimizer_known_answers.npz"), dict(cases=cases, vocab=vocab), arrays)
+  print(f"optimizer_known_answers.npz: {len(cases)} cases")
+
+
 if __name__ == "__main__":
   ap = argparse.ArgumentParser()
   ap.add_argument("--reference", default=os.environ.get("SC_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference")))
   args = ap.parse_args()
   known_answer_lookup_cases()
+  known_answer_optimizer_cases()
   record_reference_preprocessing(args.reference)
