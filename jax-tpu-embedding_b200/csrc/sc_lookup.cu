@@ -599,6 +599,68 @@ __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : 3) fwd_gather_kernel(cons
   }
 }
 
+// Gather for bags of at most one entry (single-valent features): no entry walk, so the kernel needs
+// few registers and more warps fit an SM.  Same warp / group layout as fwd_gather_kernel; a group
+// keeps the table rows of two of its activation rows in flight.  Rows without an entry are zeroed.
+template <int W, int K, int G>
+__global__ void __launch_bounds__(kBlock) fwd_gather_single_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
+  using VT = typename Vec<W>::T;
+  constexpr int NG = 32 / G;
+  struct Meta {
+    const float* src;
+    float* dst;
+    float gain;
+    int32_t vec_per_row;
+  };
+  __shared__ Meta s_meta[kWarpsPerBlock][32];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + wib) * 32u;
+  if (r0 >= total_act) return;
+  {
+    Meta m;
+    m.src = nullptr; m.dst = nullptr; m.gain = 0.f; m.vec_per_row = 0;
+    const uint32_t my_r = r0 + lane;
+    if (my_r < total_act) {
+      const int t = find_table(count, my_r, [&](int i) { return tabs[i].act_base; });
+      const TableDesc& td = tabs[t];
+      const uint32_t lr = my_r - td.act_base;
+      const uint2 bag = reinterpret_cast<const uint2*>(td.bags)[lr];
+      m.dst = td.act + (int64_t)lr * td.v.dim;
+      m.vec_per_row = td.v.dim / W;
+      if (bag.y > bag.x) {
+        m.src = resolve_entry(td, bag.x, &m.gain);
+        if (m.src != nullptr) prefetch_row(m.src, td.v.dim * 4);
+      }
+    }
+    s_meta[wib][lane] = m;
+  }
+  __syncwarp();
+  const int group = lane / G, gl = lane % G;
+  const int rows_here = (int)min(32u, total_act - r0);
+  for (int j = group; j < rows_here; j += 2 * NG) {
+    const Meta a = s_meta[wib][j];
+    const bool two = j + NG < rows_here;
+    Meta b = a;
+    if (two) b = s_meta[wib][j + NG];
+    VT xa[K], xb[K];
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = gl + k * G;
+      xa[k] = (a.src != nullptr && c < a.vec_per_row) ? __ldg(reinterpret_cast<const VT*>(a.src) + c) : Vec<W>::zero();
+      xb[k] = (two && b.src != nullptr && c < b.vec_per_row) ? __ldg(reinterpret_cast<const VT*>(b.src) + c) : Vec<W>::zero();
+    }
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+      const int c = gl + k * G;
+      VT ya = Vec<W>::zero(), yb = Vec<W>::zero();
+      Vec<W>::axpy(ya, a.gain, xa[k]);
+      Vec<W>::axpy(yb, b.gain, xb[k]);
+      if (c < a.vec_per_row) reinterpret_cast<VT*>(a.dst)[c] = ya;
+      if (two && c < b.vec_per_row) reinterpret_cast<VT*>(b.dst)[c] = yb;
+    }
+  }
+}
+
 // ---- cp.async pipeline variant of the gather
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -1794,6 +1856,14 @@ inline bool fwd_ring_enabled() {
 }
 
 template <int W, int K, int G>
+int launch_fwd_single(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
+  const unsigned warps = (unsigned)ceil_div(total_act, 32);
+  fwd_gather_single_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act);
+  SC_LAUNCH_OK("fwd_gather_single_kernel");
+  return SC_OK;
+}
+
+template <int W, int K, int G>
 int launch_fwd(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
   const unsigned warps = (unsigned)ceil_div(total_act, 32);
   fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act);
@@ -1950,6 +2020,7 @@ enum FwdPlanMode {
 struct FwdPlan {
   std::vector<CsrView> views;
   int mode = kPlanBuild;
+  bool single_valent = false;  // every item promises at most one id per sample
   uint64_t total_slots = 0, total_act = 0;
   uint64_t remote_floats = 0;  // staging space for rows of remote shards (tables with local_shard >= 0)
   int total_shards = 0;
@@ -1981,6 +2052,7 @@ int plan_fwd(const sc_fwd_item_t* items, int count, FwdPlan* p) {
   }
   if (p->total_slots >= 0xffffffffull || p->total_act >= 0xffffffffull) SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
   p->mode = given ? kPlanGiven : single ? kPlanSingle : kPlanBuild;
+  p->single_valent = single;
   return SC_OK;
 }
 
@@ -2238,6 +2310,11 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   if (side != nullptr) SC_CUDA_OK(cudaStreamWaitEvent(cs, side->join, 0));  // the gather reads the fetched rows
   PhaseScope phase("GatherCombine", cs);
   if (ring) return dispatch_fwd_ring(tabs, count, total_act, p.max_dim, cs);
+  if (p.single_valent) {
+#define SC_FWD_SINGLE_CALL(W, K, G) launch_fwd_single<W, K, G>(tabs, count, total_act, cs)
+    SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_SINGLE_CALL);
+#undef SC_FWD_SINGLE_CALL
+  }
 #define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, cs)
   SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL);
 #undef SC_FWD_CALL
