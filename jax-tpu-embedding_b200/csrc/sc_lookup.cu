@@ -1216,6 +1216,13 @@ constexpr uint32_t kRowApply = 32;   // the last of the 1 + NS table / slot rows
 constexpr uint32_t kRowReduce = 64;  // reduce-only mode: store acc at red[chunk start + bits 8..12]
 
 __device__ __forceinline__ float fast_axpy(float a, float g, float x) { return __fmaf_rn(g, x, a); }
+// Hardware square root (one special-function instruction, relative error about 1e-7) instead of the
+// multi-instruction IEEE sequence.
+__device__ __forceinline__ float fast_sqrt(float x) {
+  float r;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 
 // Optimizer step of the pipelined kernel: fused multiply-adds and the hardware reciprocal square
 // root (2 ulp) instead of IEEE sqrt + divide; within 1e-6 relative of apply_opt.
@@ -1231,7 +1238,7 @@ __device__ __forceinline__ float apply_opt_fast(const OptParams& o, bool clipped
   } else if (!EXTRA) {
     s0 = __fmaf_rn(1.0f - o.h1, g - s0, s0);
     s1 = __fmaf_rn(1.0f - o.h2, g * g - s1, s1);
-    nw = w - __fdividef(o.h0 * s0, sqrtf(s1) + o.h3);
+    nw = w - __fdividef(o.h0 * s0, fast_sqrt(s1) + o.h3);
   } else {
     const float3 r = apply_opt_two_slots(o, w, g, s0, s1);
     nw = r.x; s0 = r.y; s1 = r.z;
@@ -1445,6 +1452,197 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
 #pragma unroll
     for (int i = 0; i < B; ++i) consume_row(b * B + i);
     __syncwarp();                 // all lanes are done with the slots that the next batch recycles
+  }
+  cp_async_wait<0>();
+}
+
+// ---- the same pipeline for rows of at most 64 floats: several rows per warp instruction
+// Step slots of 512 bytes in a warp's ring and steps in flight while one is consumed: 16 rows in flight.
+__host__ __device__ constexpr int group_ring_steps(int NG) { return NG >= 4 ? 8 : 16; }
+__host__ __device__ constexpr int group_ahead(int NG) { return NG >= 4 ? 4 : 8; }
+__host__ __device__ constexpr int group_list_rows(int NS) { return 32 * (2 + NS) + 4; }
+__host__ __device__ constexpr size_t group_pipe_warp_bytes(int NG, int NS) {
+  return (size_t)group_ring_steps(NG) * 512 + (size_t)group_list_rows(NS) * 16;
+}
+
+// Same contract and the same row descriptors as bwd_pipe_kernel, for rows that fill only a part
+// of a warp (dim <= 64).  The warp's 32 lanes form NG groups of 32 / NG lanes (4 groups for rows of
+// up to 32 floats, 2 up to 64).  Every run of the chunk belongs to the group in whose window of
+// 32 / NG entries it starts, so the runs - and with them the table rows to update - are dealt to
+// the groups in contiguous, roughly equal shares; each group gets its own part of the row list.
+// All groups then advance in lockstep: in step t every group streams and executes the t-th row
+// of its part, 16 bytes per lane, through a ring of 512-byte step slots (kGroupAhead steps in
+// flight).  One warp instruction therefore moves or sums NG rows, where bwd_pipe_kernel would
+// use a quarter or half of its lanes.  Sums still run in entry order inside a run.
+template <int NG, int NS, bool REDUCE, bool EXTRA>
+__global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableDesc* __restrict__ tabs, int count,
+                                                                   uint32_t total_chunks, float* __restrict__ partial,
+                                                                   uint8_t* __restrict__ chunk_flags, int pstride) {
+  constexpr int Gc = 32 / NG;
+  constexpr int R = group_ring_steps(NG), A = group_ahead(NG);
+  constexpr int kListRows = group_list_rows(NS);
+  static_assert(A + 1 + NS < R, "a step being applied must not be overwritten by the copies issued ahead");
+  extern __shared__ __align__(128) unsigned char pipe_smem[];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const uint32_t gchunk = blockIdx.x * kPipeWarps + wib;
+  if (gchunk >= total_chunks) return;
+  const int t = warp_find_table(count, gchunk, lane, [&](int i) { return tabs[i].chunk_base; });
+  const TableDesc& td = tabs[t];
+  const CsrView& v = td.v;
+  const int n = entry_count(td);
+  const int e0 = (int)(gchunk - td.chunk_base) * 32;
+  if (e0 >= n) {
+    if (lane == 0) chunk_flags[gchunk] = 0;
+    return;
+  }
+  const RowCtx ctx = make_ctx(td);
+  const int dim = ctx.dim;
+  const int vec_per_row = dim >> 2;
+  unsigned char* mine = pipe_smem + (size_t)wib * group_pipe_warp_bytes(NG, NS);
+  const uint32_t ring_base = smem_addr(mine);
+  unsigned char* list = mine + (size_t)R * 512;
+  const float** rowaddr = reinterpret_cast<const float**>(list);
+  uint32_t* rowdesc = reinterpret_cast<uint32_t*>(list + kListRows * 8);
+  float* rowgain = reinterpret_cast<float*>(list + kListRows * 12);
+
+  const int e = e0 + lane;
+  const uint32_t my_row = entry_row(td, e, n);
+  uint32_t prev_row = __shfl_up_sync(0xffffffffu, my_row, 1);
+  if (lane == 0) prev_row = entry_row(td, e0 - 1, n);
+  const uint32_t next_row = entry_row(td, e0 + 32, n);  // row after the chunk
+  const bool valid = my_row != kNoRow;
+  const float* my_src = nullptr;
+  float my_gain = 0.f;
+  const float* any_grad = td.grad;  // a readable address for entries without a gradient row
+  if (valid) {
+    const int q = td.indirect == 1 ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
+    if (td.pull != nullptr) {
+      const int s = q / td.pull_cap;
+      const PullSrc& src = td.pull[s];
+      const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
+      const int sid = src.sids[slot];
+      my_gain = src.gains[slot];
+      any_grad = src.grad;
+      if (sid >= 0 && sid < td.pull_rows) my_src = src.grad + (int64_t)sid * dim;
+    } else {
+      const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
+      const int sid = v.sids[q];
+      my_gain = v.gains[q];
+      if (sid >= 0 && sid < v.bsc) my_src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
+    }
+  }
+  const uint32_t lt = (1u << lane) - 1u;
+  const uint32_t heads = __ballot_sync(0xffffffffu, valid && my_row != prev_row);
+  const uint32_t valids = __ballot_sync(0xffffffffu, valid);
+  if (valids == 0) {
+    if (lane == 0) chunk_flags[gchunk] = 0;
+    return;
+  }
+  const uint32_t starts = heads | (valids & 1u);
+  const int run_start = 31 - __clz(starts & (lt | (1u << lane)));
+  const bool head_run = valid && ((heads >> run_start) & 1u);
+  const bool is_end = valid && (lane == 31 || (((starts | ~valids) >> (lane + 1)) & 1u));
+  const bool goes_on = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
+  const bool w_end = is_end && head_run && !goes_on;                // apply the optimizer here
+  const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
+  if (lane == 31)
+    chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
+  constexpr int kExtra = REDUCE ? 0 : 1 + NS;
+  // Deal the runs to the groups and lay the groups' parts of the list out one after the other.
+  const int grp = valid ? run_start / Gc : NG;
+  int my_part_base = 0, my_part_rows = 0;  // part of the group this lane CONSUMES for
+  int o = 0;                               // list position of this lane's entry
+  int max_rows = 0;
+  {
+    int base = 0;
+#pragma unroll
+    for (int g = 0; g < NG; ++g) {
+      const uint32_t gm = __ballot_sync(0xffffffffu, grp == g);
+      const int rows = __popc(gm) + kExtra * __popc(wendmask & gm);
+      if (grp == g) o = base + __popc(gm & lt) + kExtra * __popc(wendmask & gm & lt);
+      if (lane / Gc == g) { my_part_base = base; my_part_rows = rows; }
+      max_rows = max(max_rows, rows);
+      base += rows;
+    }
+  }
+  if (valid) {
+    rowaddr[o] = my_src != nullptr ? my_src : any_grad;
+    rowdesc[o] = kRowGrad | (((starts >> lane) & 1u) ? kRowZero : 0u) | (my_src == nullptr ? kRowIgnore : 0u) |
+                 ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u) |
+                 ((REDUCE && w_end) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u);
+    rowgain[o] = my_gain;
+    if (!REDUCE && w_end) {
+      float *pw, *pa, *pb;
+      row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
+      rowaddr[++o] = pw;
+      rowdesc[o] = NS == 0 ? kRowApply : 0u;
+      if (NS >= 1) { rowaddr[++o] = pa; rowdesc[o] = NS == 1 ? kRowApply : 0u; }
+      if (NS >= 2) { rowaddr[++o] = pb; rowdesc[o] = kRowApply; }
+    }
+  }
+  __syncwarp();
+
+  const int gl = lane % Gc;
+  const bool in_row = gl < vec_per_row;
+  const uint32_t lane_off = (uint32_t)lane * 16u;
+  // Starts the copies of step t: the t-th row of every group's part.  Always one commit group.
+  auto issue = [&](int t) {
+    if (t < my_part_rows && in_row)
+      cp_async16(ring_base + (uint32_t)(t & (R - 1)) * 512u + lane_off,
+                 reinterpret_cast<const float4*>(rowaddr[my_part_base + t]) + gl);
+    cp_async_commit();
+  };
+  const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto consume = [&](int t) {
+    if (t >= my_part_rows) return;
+    const int r = my_part_base + t;
+    const uint32_t d = rowdesc[r];
+    const uint32_t slot_addr = ring_base + (uint32_t)(t & (R - 1)) * 512u + lane_off;
+    if (d & kRowGrad) {
+      if (d & kRowZero) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (!(d & kRowIgnore) && in_row) {
+        const float gain = rowgain[r];
+        const float4 x = lds128(slot_addr);
+        acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
+        acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
+      }
+      if (REDUCE && (d & kRowReduce)) {
+        if (in_row) reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((d >> 8) & 31u)) * dim)[gl] = acc;
+      }
+      if (d & kRowPartial) {
+        if (in_row)
+          reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * pstride)[gl] = acc;
+      }
+    } else if (!REDUCE && (d & kRowApply)) {
+      // Steps t - NS .. t of this group hold the table row and the slot rows.
+      if (in_row) {
+        float* pw = const_cast<float*>(rowaddr[r - NS]);
+        float* pa = NS >= 1 ? const_cast<float*>(rowaddr[r - NS + (NS >= 1 ? 1 : 0)]) : nullptr;
+        float* pb = NS >= 2 ? const_cast<float*>(rowaddr[r]) : nullptr;
+        float4 w = lds128(ring_base + (uint32_t)((t - NS) & (R - 1)) * 512u + lane_off);
+        float4 x0 = NS >= 1 ? lds128(ring_base + (uint32_t)((t - NS + 1) & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 x1 = NS >= 2 ? lds128(slot_addr) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float* wf = reinterpret_cast<float*>(&w);
+        float* af = reinterpret_cast<float*>(&x0);
+        float* bf = reinterpret_cast<float*>(&x1);
+        const float* gf = reinterpret_cast<const float*>(&acc);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast<NS, EXTRA>(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
+        reinterpret_cast<float4*>(pw)[gl] = w;
+        if (NS >= 1) reinterpret_cast<float4*>(pa)[gl] = x0;
+        if (NS >= 2) reinterpret_cast<float4*>(pb)[gl] = x1;
+      }
+    }
+  };
+
+#pragma unroll
+  for (int a = 0; a < A; ++a) issue(a);
+  for (int step = 0; step < max_rows; ++step) {
+    issue(step + A);
+    cp_async_wait<A>();  // this lane's copies of `step` have landed
+    __syncwarp();        // ... and every other lane's
+    consume(step);
   }
   cp_async_wait<0>();
 }
@@ -1927,8 +2125,45 @@ int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, con
   return launch_fixup<4, K32>(tabs, count, total_chunks, u, extra, st);
 }
 
+template <int NG, int NS, bool REDUCE = false, bool EXTRA = false>
+int launch_group_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
+  const size_t smem = (size_t)kPipeWarps * group_pipe_warp_bytes(NG, NS);
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SC_CUDA_OK(cudaFuncSetAttribute(bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  (int)cudaSharedmemCarveoutMaxShared));
+  const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
+  bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
+  SC_LAUNCH_OK("bwd_group_pipe_kernel");
+  return SC_OK;
+}
+
+// Rows of at most 64 floats: NG rows per warp instruction.
+template <int NG>
+int launch_bwd_group_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
+                          bool extra, cudaStream_t st) {
+  int rc;
+  if (num_slots == kReduceOnly) rc = launch_group_pipe_ns<NG, 0, true>(tabs, count, total_chunks, u, st);
+  else if (num_slots == 0) rc = launch_group_pipe_ns<NG, 0>(tabs, count, total_chunks, u, st);
+  else if (num_slots == 1) rc = launch_group_pipe_ns<NG, 1>(tabs, count, total_chunks, u, st);
+  else if (!extra) rc = launch_group_pipe_ns<NG, 2>(tabs, count, total_chunks, u, st);
+  else rc = launch_group_pipe_ns<NG, 2, false, true>(tabs, count, total_chunks, u, st);
+  if (rc != SC_OK) return rc;
+  return launch_fixup<4, 1>(tabs, count, total_chunks, u, extra, st);
+}
+
+// SC_BWD_GROUPS=off keeps short rows on the one-row-per-instruction kernel.
+inline bool group_pipe_enabled() {
+  static const bool on = [] { const char* e = getenv("SC_BWD_GROUPS"); return !(e && strcmp(e, "off") == 0); }();
+  return on;
+}
+
 inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u,
                              int num_slots, bool extra, int max_dim, cudaStream_t st) {
+  static const int forced_groups = [] { const char* e = getenv("SC_BWD_GROUPS"); return e ? atoi(e) : 0; }();
+  if (group_pipe_enabled() && (max_dim <= 32 || (forced_groups == 4 && max_dim <= 32)))
+    return launch_bwd_group_pipe<4>(tabs, count, total_chunks, u, num_slots, extra, st);
+  if (group_pipe_enabled() && forced_groups == 2 && max_dim <= 64)
+    return launch_bwd_group_pipe<2>(tabs, count, total_chunks, u, num_slots, extra, st);
   const int vecs = (max_dim / 4 + 31) / 32;
   if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
   if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
