@@ -613,6 +613,7 @@ class Run:
       dense_all = torch.cat([p.reshape(-1) for p in pinned]).pin_memory()
     main_stream = torch.cuda.current_stream()
     side_stream = torch.cuda.Stream()
+    rows_1024 = max(1, 1024 // self.specs[0].output_shape[-1])
 
     def prepare_batch():
       with torch.cuda.stream(side_stream):
@@ -626,7 +627,10 @@ class Run:
             dev_feats.append(embedding.RaggedInput(p.values.cuda(non_blocking=True), p.row_splits,
                                                    None if p.weights is None else p.weights.cuda(non_blocking=True)))
         dev_w = None if pinned_w is None else [w.cuda(non_blocking=True) for w in pinned_w]
-        p2, _ = embedding.preprocess_sparse_dense_matmul_input(dev_feats, dev_w, specs, 1, world, num_sc_per_device=1)
+        # sync_stats=False: the statistics stay on their way to the host until somebody reads them (an FDO client
+        # would, every few hundred steps); the call does not wait for the GPU.
+        p2, _ = embedding.preprocess_sparse_dense_matmul_input(dev_feats, dev_w, specs, 1, world, num_sc_per_device=1,
+                                                               sync_stats=False)
         done = torch.cuda.Event()
         done.record(side_stream)
       # The buffers were allocated on the side stream and are read on the main one.
@@ -642,7 +646,7 @@ class Run:
       acts = embedding.tpu_sparse_dense_matmul(p2, self.variables, specs, global_device_count=world, num_sc_per_device=1)
       # The step's result read back by the host: a checksum over the first 1024 values of every feature's
       # activations; the activations themselves stay on the device for the dense part of a model.
-      checksum = torch.cat([a.reshape(-1)[:1024] for a in acts]).sum()
+      checksum = torch.cat([a[:rows_1024] for a in acts]).sum()
       embedding.tpu_sparse_dense_matmul_grad(self.grads, p2, self.variables, specs, global_device_count=world,
                                              num_sc_per_device=1, step=0)
       nxt = prepare_batch()  # overlaps the kernels just launched
@@ -659,8 +663,9 @@ class Run:
     ms = self.max_over_ranks((time.perf_counter() - t0) / steps * 1e3)
     return {"value": self.wl["batch"] * world / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 + 4 * sum(2 * 1 + 1 + 3 for _ in self.stacked),
-            "read_back": "a 4-byte checksum of 1024 activations per feature and the preprocessing statistics; the "
-                         "activations stay on the device",
+            "host": "one Python thread issues everything",
+            "read_back": "a 4-byte checksum of 1024 activations per feature; the activations stay on the device and the "
+                         "preprocessing statistics are copied to pinned memory without a wait (sync_stats=False)",
             "pipeline": "copy + preprocessing of batch i+1 on a second stream while batch i is looked up and updated"}
 
   def release(self):

@@ -2024,12 +2024,25 @@ bool pick_group_shape(int dim, int* w, int* k, int* g) {
   return true;
 }
 
+// Lets `Kernel` use `smem` bytes of dynamic shared memory.  The driver calls are repeated only when a
+// launch needs more than any earlier launch of the same kernel on the same device.
+template <auto Kernel>
+int configure_smem(size_t smem) {
+  static size_t configured[64] = {};
+  int dev = 0;
+  SC_CUDA_OK(cudaGetDevice(&dev));
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && configured[dev] >= smem) return SC_OK;
+  SC_CUDA_OK(cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  SC_CUDA_OK(cudaFuncSetAttribute(Kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+  if (tracked) configured[dev] = smem;
+  return SC_OK;
+}
+
 template <int K, int NG>
 int launch_fwd_ring(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
   const size_t smem = (size_t)kFwdWarps * fwd_ring_warp_bytes(K, NG);
-  SC_CUDA_OK(cudaFuncSetAttribute(fwd_ring_kernel<K, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  SC_CUDA_OK(cudaFuncSetAttribute(fwd_ring_kernel<K, NG>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                  (int)cudaSharedmemCarveoutMaxShared));
+  if (int rc = configure_smem<fwd_ring_kernel<K, NG>>(smem)) return rc;
   const unsigned warps = (unsigned)ceil_div(total_act, 32);
   fwd_ring_kernel<K, NG><<<(unsigned)ceil_div(warps, kFwdWarps), kFwdBlock, smem, st>>>(tabs, count, total_act);
   SC_LAUNCH_OK("fwd_ring_kernel");
@@ -2101,9 +2114,7 @@ int launch_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, cons
                    cudaStream_t st) {
   const int ring_floats = pipe_ring_rows(K, NS) * max_dim;
   const size_t smem = (size_t)kPipeWarps * ((size_t)ring_floats * 4 + pipe_list_bytes(K, NS));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_pipe_kernel<K, NS, REDUCE, EXTRA>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                  (int)cudaSharedmemCarveoutMaxShared));
+  if (int rc = configure_smem<bwd_pipe_kernel<K, NS, REDUCE, EXTRA>>(smem)) return rc;
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
   bwd_pipe_kernel<K, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, ring_floats,
                                                                           u.pstride);
@@ -2128,9 +2139,7 @@ int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, con
 template <int NG, int NS, bool REDUCE = false, bool EXTRA = false>
 int launch_group_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
   const size_t smem = (size_t)kPipeWarps * group_pipe_warp_bytes(NG, NS);
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  SC_CUDA_OK(cudaFuncSetAttribute(bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                  (int)cudaSharedmemCarveoutMaxShared));
+  if (int rc = configure_smem<bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>>(smem)) return rc;
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
   bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
   SC_LAUNCH_OK("bwd_group_pipe_kernel");

@@ -312,6 +312,106 @@ def _raise_for_status(stats_host: np.ndarray, p: int, s: int, table: str, max_id
       "feature row offsets do not match the batch.")
 
 
+class _DeferredStats:
+  """The statistics block of one call while it travels to the host (pinned buffer + CUDA event).
+
+  `resolve()` waits for the copy, raises the ValueError of a violated limit or invalid input exactly as
+  the synchronous path does, and returns the four per-table dicts.  It runs at most once.
+  """
+
+  def __init__(self, pinned, event, names, limits, p, s):
+    self.pinned, self.event, self.names, self.limits, self.p, self.s = pinned, event, names, limits, p, s
+    self.fields = None
+    self.error = None
+
+  def resolve(self):
+    if self.fields is None and self.error is None:
+      self.event.synchronize()
+      host = self.pinned.numpy().copy()
+      self.pinned = None
+      p, s = self.p, self.s
+      try:
+        status = host[:, 2 * p + s + 1]
+        if status.any():
+          si = int(np.flatnonzero(status)[0])
+          _raise_for_status(host[si], p, s, self.names[si], *self.limits[si])
+      except ValueError as e:
+        self.error = e
+      fields = ({}, {}, {}, {})
+      for si, name in enumerate(self.names):
+        fields[0][name] = host[si, :p].copy()
+        fields[1][name] = host[si, p:2 * p].copy()
+        fields[2][name] = host[si, 2 * p:2 * p + s].copy()
+        fields[3][name] = int(host[si, 2 * p + s])
+      self.fields = fields
+    if self.error is not None:
+      raise self.error
+    return self.fields
+
+
+class LazyStatsDict(dict):
+  """One per-table statistics dict that is filled from a _DeferredStats on first use."""
+
+  def __init__(self, *args, deferred=None, field=0, **kw):
+    super().__init__(*args, **kw)
+    self._deferred, self._field = deferred, field
+
+  def _fill(self):
+    if self._deferred is not None:
+      deferred, self._deferred = self._deferred, None
+      super().update(deferred.resolve()[self._field])
+
+  def __getitem__(self, k):
+    self._fill()
+    return super().__getitem__(k)
+
+  def __iter__(self):
+    self._fill()
+    return super().__iter__()
+
+  def __len__(self):
+    self._fill()
+    return super().__len__()
+
+  def __contains__(self, k):
+    self._fill()
+    return super().__contains__(k)
+
+  def __repr__(self):
+    self._fill()
+    return super().__repr__()
+
+  def __eq__(self, other):
+    self._fill()
+    return super().__eq__(other)
+
+  __hash__ = None
+
+  def keys(self):
+    self._fill()
+    return super().keys()
+
+  def values(self):
+    self._fill()
+    return super().values()
+
+  def items(self):
+    self._fill()
+    return super().items()
+
+  def get(self, k, default=None):
+    self._fill()
+    return super().get(k, default)
+
+  def __setitem__(self, k, v):
+    self._fill()
+    super().__setitem__(k, v)
+
+  def copy(self):
+    self._fill()
+    return dict(self)
+
+
 class BufferDict(dict):
   """dict of output arrays that remembers which device buffers all its values are views of.
 
@@ -423,6 +523,8 @@ class _DensePlan:
     self.float_offsets = [4 * sum(self.coos[:i]) for i in range(n)]
     self.float_total = sum(self.coos)
     self.groups = None  # launch groups and workspace sizes, sized on the first run (needs real addresses)
+    self.deferred = [None] * 4  # statistics of the last calls made with sync_stats=False (ring)
+    self.deferred_next = 0
 
   def _size_groups(self):
     """Launch groups (bounded by the 32-bit sort key) and their workspace sizes."""
@@ -442,10 +544,15 @@ class _DensePlan:
       self.groups.append((sub, m, nbytes))
       start += m
 
-  def run(self, features, feature_weights, has_leading_dimension: bool, device_output: bool):
+  def run(self, features, feature_weights, has_leading_dimension: bool, device_output: bool, sync_stats: bool = True):
     torch = _native.torch_mod()
     lib = _native.lib()
     n = len(self.stacks)
+    if not sync_stats:
+      # The statistics of the previous deferred call have long arrived: a violated limit surfaces here.
+      previous = self.deferred[(self.deferred_next - 1) % len(self.deferred)]
+      if previous is not None and previous.fields is None and previous.error is None and previous.event.query():
+        previous.resolve()
     ints = torch.empty(self.int_total, dtype=torch.int32, device="cuda")
     floats = torch.empty(self.float_total, dtype=torch.float32, device="cuda")
     stats_dev = torch.empty((n, self.stats_size), dtype=torch.int32, device="cuda")
@@ -484,19 +591,42 @@ class _DensePlan:
         _native.check(lib.sc_preprocess_grouped(sub, m, None, 0, None))
       ws = _native.workspace(nbytes, "preprocess")
       _native.check(lib.sc_preprocess_grouped(sub, m, ws.data_ptr(), ws.numel(), stream))
-    host = stats_dev.cpu().numpy()  # the only synchronisation of the call
-    del keep
     p, s = self.p, self.s
-    status = host[:, 2 * p + s + 1]
-    if status.any():
-      si = int(np.flatnonzero(status)[0])
-      _raise_for_status(host[si], p, s, self.names[si], *self.limits[si])
+    stats = SparseDenseMatmulInputStats()
+    host = None
+    if sync_stats:
+      host = stats_dev.cpu().numpy()  # the only synchronisation of the call
+      status = host[:, 2 * p + s + 1]
+      if status.any():
+        si = int(np.flatnonzero(status)[0])
+        _raise_for_status(host[si], p, s, self.names[si], *self.limits[si])
+      max_ids, max_unique = host[:, :p].copy(), host[:, p:2 * p].copy()
+      required, dropped = host[:, 2 * p:2 * p + s].copy(), host[:, 2 * p + s]
+    else:
+      # No synchronisation: the block is copied to pinned memory behind the kernels; the dicts of `stats` fetch
+      # it (and raise for a violated limit) when they are first read.
+      slot = self.deferred_next % len(self.deferred)
+      old = self.deferred[slot]
+      if old is not None and old.fields is None and old.error is None:
+        try:
+          old.resolve()  # its pinned buffer is about to be recycled
+        except ValueError:
+          pass
+      pinned = torch.empty((n, self.stats_size), dtype=torch.int32, pin_memory=True)
+      pinned.copy_(stats_dev, non_blocking=True)
+      event = torch.cuda.Event()
+      event.record()
+      deferred = _DeferredStats(pinned, event, list(self.names), list(self.limits), p, s)
+      self.deferred[slot] = deferred
+      self.deferred_next += 1
+      stats.max_ids_per_partition = LazyStatsDict(deferred=deferred, field=0)
+      stats.max_unique_ids_per_partition = LazyStatsDict(deferred=deferred, field=1)
+      stats.required_buffer_sizes = LazyStatsDict(deferred=deferred, field=2)
+      stats.dropped_id_count = LazyStatsDict(deferred=deferred, field=3)
+    del keep
     int_views = ints[:sum(self.int_sizes)].split(self.int_sizes)
     float_views = floats.split(self.coos)
     out_rp, out_ids, out_sids, out_gains = BufferDict(), BufferDict(), BufferDict(), BufferDict()
-    stats = SparseDenseMatmulInputStats()
-    max_ids, max_unique = host[:, :p].copy(), host[:, p:2 * p].copy()
-    required, dropped = host[:, 2 * p:2 * p + s].copy(), host[:, 2 * p + s]
     for si, name in enumerate(self.names):
       arrays = (int_views[3 * si], int_views[3 * si + 1], int_views[3 * si + 2], float_views[si])
       if has_leading_dimension:
@@ -504,10 +634,11 @@ class _DensePlan:
       if not device_output:
         arrays = tuple(t.cpu().numpy() for t in arrays)
       out_rp[name], out_ids[name], out_sids[name], out_gains[name] = arrays
-      stats.max_ids_per_partition[name] = max_ids[si]
-      stats.max_unique_ids_per_partition[name] = max_unique[si]
-      stats.required_buffer_sizes[name] = required[si]
-      stats.dropped_id_count[name] = int(dropped[si])
+      if host is not None:
+        stats.max_ids_per_partition[name] = max_ids[si]
+        stats.max_unique_ids_per_partition[name] = max_unique[si]
+        stats.required_buffer_sizes[name] = required[si]
+        stats.dropped_id_count[name] = int(dropped[si])
     if device_output:
       # The arrays keep the two buffers alive, so the addresses identify the contents' location.
       token = (ints.data_ptr(), floats.data_ptr(), id(self), bool(has_leading_dimension))
@@ -560,9 +691,13 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
                                          sharding_strategy: ShardingStrategy = ShardingStrategy.MOD,
                                          has_leading_dimension: bool = False, allow_id_dropping: bool = False,
                                          batch_number: int = 0, enable_minibatching: bool = False,
-                                         all_reduce_interface=None, device_output: bool = False):
+                                         all_reduce_interface=None, device_output: bool = False,
+                                         sync_stats: bool = True):
   """Flat lists of features / weights / specs -> (row_pointers, embedding_ids, sample_ids, gains,
-  num_minibatches, stats), the first four being dicts keyed by stacked table name."""
+  num_minibatches, stats), the first four being dicts keyed by stacked table name.
+
+  sync_stats=False (dense device inputs only) returns without waiting for the GPU: the statistics arrive when
+  they are first read, and a violated id limit raises then, or at the next call, instead of at this one."""
   del batch_number, all_reduce_interface
   _reject_minibatching(enable_minibatching)
   if int(sharding_strategy) != int(ShardingStrategy.MOD):
@@ -597,7 +732,7 @@ def preprocess_sparse_dense_matmul_input(features, feature_weights, feature_spec
   l, s = local_device_count, num_sc_per_device
   plan = _dense_plan(features, feature_weights, feature_specs, l, global_device_count, s, allow_id_dropping)
   if plan is not None:
-    return plan.run(features, feature_weights, has_leading_dimension, device_output)
+    return plan.run(features, feature_weights, has_leading_dimension, device_output, sync_stats and True)
   out_rp, out_ids, out_sids, out_gains = BufferDict(), BufferDict(), BufferDict(), BufferDict()
   stats = SparseDenseMatmulInputStats()
   stacks = list(_group_by_stack(feature_specs).items())

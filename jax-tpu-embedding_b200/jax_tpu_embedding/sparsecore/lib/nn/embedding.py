@@ -47,11 +47,25 @@ def _is_array(x) -> bool:
   return isinstance(x, np.ndarray) or type(x).__module__.startswith("torch")
 
 
+def _flat_leaves(tree) -> bool:
+  """True for the common case: a plain list or tuple whose elements are all leaves."""
+  if type(tree) is not list and type(tree) is not tuple:
+    return False
+  for x in tree:
+    if not _is_feature_leaf(x):
+      return False
+  return True
+
+
 def _leaves(tree):
+  if _flat_leaves(tree):
+    return list(tree)
   return _tree.leaves(tree, is_leaf=_is_feature_leaf)
 
 
 def _assert_same_structure(a, b, a_name: str = "a", b_name: str = "b"):
+  if _flat_leaves(a) and _flat_leaves(b) and type(a) is type(b) and len(a) == len(b):
+    return
   a_paths = [p for p, _ in _tree.leaves_with_path(a, is_leaf=_is_feature_leaf)]
   b_paths = [p for p, _ in _tree.leaves_with_path(b, is_leaf=_is_feature_leaf)]
   if a_paths != b_paths:
@@ -275,13 +289,15 @@ def preprocess_sparse_dense_matmul_input(features, features_weights, feature_spe
                                          sharding_strategy: str = "MOD", has_leading_dimension: bool = False,
                                          allow_id_dropping: bool = False, batch_number: int = 0,
                                          enable_minibatching: bool = False, all_reduce_interface=None,
-                                         device_output: bool = True
+                                         device_output: bool = True, sync_stats: bool = True
                                          ) -> tuple[PreprocessedInput, SparseDenseMatmulInputStats]:
   """Turns raw feature ids (and weights) into the CSR-wrapped COO buffers the lookup consumes.
 
   Each feature leaf is a 2-D int array [batch, valency], a 1-D object array of id arrays
   (ragged), or a `RaggedInput`.  With `device_output` (default) the buffers stay on the GPU as
-  torch tensors; with False they are numpy arrays like the reference's.
+  torch tensors; with False they are numpy arrays like the reference's.  `sync_stats=False` (honoured
+  for dense int32 device inputs) does not wait for the GPU: the statistics are fetched when first
+  read, and a violated id limit raises then or at the next call.
   """
   num_sc_per_device = _get_num_sc_per_device(num_sc_per_device)
   _assert_same_structure(features, feature_specs, "features", "feature_specs")
@@ -303,6 +319,7 @@ def preprocess_sparse_dense_matmul_input(features, features_weights, feature_spe
       enable_minibatching=enable_minibatching,
       all_reduce_interface=all_reduce_interface,
       device_output=device_output,
+      sync_stats=sync_stats,
   )
   minibatches = np.full(local_device_count, num_minibatches)
   if has_leading_dimension:
@@ -453,6 +470,7 @@ class _SpecInfo:
           and f.table_spec.embedding_dim == self.stacked[name].stack_embedding_dim
           and f.output_shape[0] == self.stacked[name].total_sample_count)
     self.all_trivial = all(self.trivial.values())
+    self.hypers: dict = {}  # step -> {stack: optimizer hyper-parameters as floats}
     self.keep = feature_specs  # keeps the ids in the cache key alive
 
 
@@ -502,9 +520,12 @@ def _forward_plans(rps, eids, sids, gains):
 
 
 def _tensor_key(tensors):
-  if not all(_is_cuda_tensor(x) for x in tensors):
+  """((address, shape), ...) of contiguous CUDA tensors, or None if any element is something else."""
+  try:
+    key = tuple((x.data_ptr(), x.shape) for x in tensors if x.is_cuda and x.is_contiguous())
+  except AttributeError:
     return None
-  return tuple((x.data_ptr(), tuple(x.shape)) for x in tensors)
+  return key if len(key) == len(tensors) else None
 
 
 def clear_caches() -> None:
@@ -669,7 +690,15 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
   assert rps.keys() == gradients.keys()
   strategy = int(sharding_strategy_to_enum(sharding_strategy))
 
-  hypers = {n: tuple(float(h) for h in st.optimizer.get_hyperparameters(step)) for n, st in stacked_table_specs.items()}
+  # Hyper-parameters per stack; they depend on the specs and on `step` only.
+  step_key = step if step is None or isinstance(step, int) else None
+  hypers = info.hypers.get(step_key) if (step is None or step_key is not None) else None
+  if hypers is None:
+    hypers = {n: tuple(float(h) for h in st.optimizer.get_hyperparameters(step)) for n, st in stacked_table_specs.items()}
+    if step is None or step_key is not None:
+      if len(info.hypers) > 8:
+        info.hypers.clear()
+      info.hypers[step_key] = hypers
   limits = None if embedding_var_limits is None else tuple(
       tuple(embedding_var_limits[n]) for n in stacked_table_specs)
   key = None

@@ -154,3 +154,43 @@ def test_sparse_coo_input_equals_ragged_input():
   with pytest.raises(ValueError, match="row-major"):
     pip.preprocess_sparse_dense_matmul_sparse_coo_input([indices[0][::-1]], [values[0]], [shapes[0]],
                                                         case.feature_specs[:1], 1, 1, **kw)
+
+
+def test_deferred_statistics_equal_the_synchronous_ones_and_raise_late():
+  """sync_stats=False: same buffers and statistics, no wait inside the call; a violated limit raises when the
+  statistics are read, or at the next call."""
+  import torch
+
+  case = cases.make_case("deferred", seed=21, batch=512, tables=[
+      dict(vocab=5000, dim=16, features=[dict(kind="dense", valency=3, dist="zipf")]),
+      dict(vocab=300, dim=16, features=[dict(kind="dense", valency=1)])])
+  feats = [torch.from_numpy(f).cuda() for f in case.features]
+  want, want_stats = embedding.preprocess_sparse_dense_matmul_input(feats, None, case.feature_specs, 1, 1, num_sc_per_device=1)
+  got, got_stats = embedding.preprocess_sparse_dense_matmul_input(feats, None, case.feature_specs, 1, 1, num_sc_per_device=1,
+                                                                  sync_stats=False)
+  for a, b in zip(got.sparse_dense_matmul_input, want.sparse_dense_matmul_input):
+    for name in b:
+      assert torch.equal(a[name].view(torch.int32), b[name].view(torch.int32))
+  assert set(got_stats.max_ids_per_partition) == set(want_stats.max_ids_per_partition)
+  for name in want_stats.max_ids_per_partition:
+    np.testing.assert_array_equal(got_stats.max_ids_per_partition[name], want_stats.max_ids_per_partition[name])
+    np.testing.assert_array_equal(got_stats.max_unique_ids_per_partition[name], want_stats.max_unique_ids_per_partition[name])
+    np.testing.assert_array_equal(got_stats.required_buffer_size_per_sc[name], want_stats.required_buffer_size_per_sc[name])
+    assert got_stats.id_drop_counters[name] == want_stats.id_drop_counters[name]
+  # A limit below what the batch needs: the synchronous call raises at once, the deferred one when asked.
+  tight = cases.make_case("deferred_tight", seed=21, batch=512, max_ids=16, max_unique=16, tables=[
+      dict(vocab=5000, dim=16, features=[dict(kind="dense", valency=3, dist="zipf")])])
+  tfeats = [torch.from_numpy(f).cuda() for f in tight.features]
+  with pytest.raises(ValueError, match="max ids per partition"):
+    embedding.preprocess_sparse_dense_matmul_input(tfeats, None, tight.feature_specs, 1, 1, num_sc_per_device=1)
+  _, late = embedding.preprocess_sparse_dense_matmul_input(tfeats, None, tight.feature_specs, 1, 1, num_sc_per_device=1,
+                                                           sync_stats=False)
+  with pytest.raises(ValueError, match="max ids per partition"):
+    len(late.max_ids_per_partition)
+  _, late2 = embedding.preprocess_sparse_dense_matmul_input(tfeats, None, tight.feature_specs, 1, 1, num_sc_per_device=1,
+                                                            sync_stats=False)
+  torch.cuda.synchronize()
+  with pytest.raises(ValueError, match="max ids per partition"):  # the previous call's violation surfaces here
+    embedding.preprocess_sparse_dense_matmul_input(tfeats, None, tight.feature_specs, 1, 1, num_sc_per_device=1,
+                                                   sync_stats=False)
+  del late2
