@@ -640,8 +640,20 @@ class Run:
           break
       return p2, done
 
+    # The input pipeline runs in a second host thread, as a data loader would: it issues the copy and the
+    # preprocessing of batch i + 1 while this thread issues lookup, read-back and update of batch i.
+    import concurrent.futures
+
+    pool = concurrent.futures.ThreadPoolExecutor(max_workers=1)
+    device = torch.cuda.current_device()
+
+    def prepare_in_worker():
+      torch.cuda.set_device(device)
+      return prepare_batch()
+
     def lookup_update_step(batch):
       p2, done = batch
+      nxt = pool.submit(prepare_in_worker)
       main_stream.wait_event(done)
       acts = embedding.tpu_sparse_dense_matmul(p2, self.variables, specs, global_device_count=world, num_sc_per_device=1)
       # The step's result read back by the host: a checksum over the first 1024 values of every feature's
@@ -649,8 +661,7 @@ class Run:
       checksum = torch.cat([a[:rows_1024] for a in acts]).sum()
       embedding.tpu_sparse_dense_matmul_grad(self.grads, p2, self.variables, specs, global_device_count=world,
                                              num_sc_per_device=1, step=0)
-      nxt = prepare_batch()  # overlaps the kernels just launched
-      return float(checksum.item()), nxt
+      return float(checksum.item()), nxt.result()
 
     batch = prepare_batch()
     for _ in range(2):
@@ -660,10 +671,11 @@ class Run:
     for _ in range(steps):
       _, batch = lookup_update_step(batch)
     self.barrier()
+    pool.shutdown()
     ms = self.max_over_ranks((time.perf_counter() - t0) / steps * 1e3)
     return {"value": self.wl["batch"] * world / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 + 4 * sum(2 * 1 + 1 + 3 for _ in self.stacked),
-            "host": "one Python thread issues everything",
+            "host": "two Python threads: one issues copy + preprocessing of the next batch, one lookup, read-back and update",
             "read_back": "a 4-byte checksum of 1024 activations per feature; the activations stay on the device and the "
                          "preprocessing statistics are copied to pinned memory without a wait (sync_stats=False)",
             "pipeline": "copy + preprocessing of batch i+1 on a second stream while batch i is looked up and updated"}

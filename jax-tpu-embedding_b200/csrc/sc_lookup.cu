@@ -109,6 +109,7 @@ struct TableDesc {
   int32_t pull_shard;
   int32_t num_sources;
   int32_t pull_rows;    // rows of a source's gradient buffer (samples, or slots when it holds reduced runs)
+  uint32_t src_base;    // index of this table's first source among the sources of all tables of the call
   // Reduce-only mode (opt.kind == kReduceOnly, indirect == 2): the entry list is this device's own
   // CSR buffer (entry e = slot e, rows[e] = shard * rows_per_shard + id or kNoRow) and the sum of
   // every run is stored at red[first slot of the run] instead of being applied to a table.
@@ -1854,6 +1855,105 @@ __global__ void bwd_keys_kernel(const TableDesc* __restrict__ tabs, int count, u
   if (counts != nullptr && key != invalid) ranks[ge] = atomicAdd(&counts[key], 1u);
 }
 
+// ---- pull mode: the sources' partitions are already ordered by row, so the entry list is a MERGE
+//
+// pull_compact_kernel  block per (table, source): the valid entries of the source's partition - run heads when
+//                      the sources exchange reduced runs, with padding slots between them - are compacted in
+//                      order: ckeys = row inside the shard, cidx = position inside the partition; lens = count
+// pull_ranges_kernel   ranges[t] = valid entries of the tables before t (one block)
+// pull_merge_kernel    position of compact entry c of source s = c + sum over the other sources o of the number
+//                      of their keys that sort before it (smaller row; equal row and o < s): binary searches in
+//                      the compact lists.  Equal rows keep source order, then position: the order of a stable
+//                      sort by row, without counters or sorting passes.
+__global__ void __launch_bounds__(kScanThreads) pull_compact_kernel(const TableDesc* __restrict__ tabs, int count,
+                                                                    uint32_t* __restrict__ ckeys, uint32_t* __restrict__ cidx,
+                                                                    uint32_t* __restrict__ lens, uint32_t* __restrict__ table_counts) {
+  __shared__ uint32_t s_done;
+  const uint32_t b = blockIdx.x;
+  const int t = find_table(count, b, [&](int i) { return tabs[i].src_base; });
+  const TableDesc& td = tabs[t];
+  const int s = (int)(b - td.src_base);
+  const PullSrc& src = td.pull[s];
+  const int g = td.pull_shard;
+  const int begin = g == 0 ? 0 : ((src.row_pointers[g - 1] + kAlign - 1) & ~(kAlign - 1));
+  const int end = min(src.row_pointers[g], begin + td.pull_cap);
+  uint32_t* out_k = ckeys + td.ent_base + (uint32_t)s * (uint32_t)td.pull_cap;
+  uint32_t* out_i = cidx + td.ent_base + (uint32_t)s * (uint32_t)td.pull_cap;
+  if (threadIdx.x == 0) {
+    td.pull_begin[s] = begin;
+    s_done = 0;
+  }
+  __syncthreads();
+  for (int j0 = begin; j0 < end; j0 += kScanThreads) {
+    const int j = j0 + (int)threadIdx.x;
+    int id = -1;
+    if (j < end) id = src.ids[j];
+    const bool valid = id >= 0 && (int64_t)id < td.v.rows_per_shard;
+    uint32_t total;
+    const uint32_t before = block_exclusive_scan<uint32_t>(valid ? 1u : 0u, &total);
+    if (valid) {
+      const uint32_t c = s_done + before;
+      out_k[c] = (uint32_t)id;
+      out_i[c] = (uint32_t)(j - begin);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_done += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    lens[b] = s_done;
+    atomicAdd(&table_counts[t], s_done);
+  }
+}
+
+__global__ void pull_ranges_kernel(int count, const uint32_t* __restrict__ table_counts, uint32_t* __restrict__ ranges) {
+  __shared__ uint32_t s_base;
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (int t0 = 0; t0 < count; t0 += kScanThreads) {
+    const int t = t0 + (int)threadIdx.x;
+    const uint32_t mine = t < count ? table_counts[t] : 0u;
+    uint32_t total;
+    const uint32_t before = block_exclusive_scan<uint32_t>(mine, &total);
+    if (t < count) ranges[t] = s_base + before;
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) ranges[count] = s_base;
+}
+
+__global__ void pull_merge_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_ent,
+                                  const uint32_t* __restrict__ ckeys, const uint32_t* __restrict__ cidx,
+                                  const uint32_t* __restrict__ lens, const uint32_t* __restrict__ ranges,
+                                  uint32_t* __restrict__ rows_sorted, uint32_t* __restrict__ list) {
+  const uint32_t ge = blockIdx.x * blockDim.x + threadIdx.x;
+  if (ge >= total_ent) return;
+  const int t = find_table(count, ge, [&](int i) { return tabs[i].ent_base; });
+  const TableDesc& td = tabs[t];
+  const uint32_t cap = (uint32_t)td.pull_cap;
+  const uint32_t q = ge - td.ent_base;
+  const uint32_t s = q / cap, c = q - s * cap;
+  if (c >= lens[td.src_base + s]) return;
+  const uint32_t key = ckeys[ge];
+  uint32_t pos = c;
+  for (uint32_t o = 0; o < (uint32_t)td.num_sources; ++o) {
+    if (o == s) continue;
+    const uint32_t* other = ckeys + td.ent_base + o * cap;
+    // Keys of source o that sort before this entry: row < key, and row == key when o < s.
+    const uint32_t bound = o < s ? key + 1u : key;
+    uint32_t lo = 0, hi = lens[td.src_base + o];
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if (other[mid] < bound) lo = mid + 1; else hi = mid;
+    }
+    pos += lo;
+  }
+  const uint32_t at = ranges[t] + pos;
+  rows_sorted[at] = td.row_base + key;
+  list[at] = td.ent_base + s * cap + cidx[ge];
+}
+
 // ranges[t] = first sorted position whose key is >= row_base of table t; ranges[count] = number of
 // valid entries.  Table t's entries are [ranges[t], ranges[t + 1]).
 __global__ void bwd_ranges_kernel(const TableDesc* __restrict__ tabs, int count, const uint32_t* __restrict__ keys, uint32_t n,
@@ -2347,6 +2447,7 @@ struct BwdPlan {
   int total_shards = 0, total_sources = 0;
   int w = 0, k = 0, g = 0, max_dim = 0, kind = 0, max_slots = 0;
   bool counting = false;  // order the indirect entries by a counting sort on the row instead of a radix sort
+  bool merge = false;     // every indirect table is a pull table: merge the sources' sorted partitions instead
 };
 
 int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
@@ -2403,7 +2504,11 @@ int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
     SC_FAIL(SC_UNSUPPORTED, "group too large for 32-bit indices");
   // One counter per row pays off while the rows are not much more numerous than the entries
   // (measured on 26 tables, 1.9 M entries: 30 M rows lose to the radix sort, 7 M rows win).
-  p->counting = p->total_ent > 0 && p->total_rows <= 4 * p->total_ent && counting_sort_enabled();
+  bool all_pull = p->total_ent > 0;
+  for (int i = 0; i < count; ++i) all_pull = all_pull && items[i].sources != nullptr;
+  static const bool merge_enabled = [] { const char* e = getenv("SC_BWD_SORT"); return e == nullptr || strcmp(e, "merge") == 0; }();
+  p->merge = all_pull && merge_enabled;
+  p->counting = !p->merge && p->total_ent > 0 && p->total_rows <= 4 * p->total_ent && counting_sort_enabled();
   return SC_OK;
 }
 
@@ -2423,7 +2528,15 @@ struct BwdScratch {
 
 bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
   s->image = ws.take<char>(image_bytes(count, p.total_shards));
-  if (p.total_ent > 0) carve_sort(ws, (size_t)p.total_ent, &s->sort);
+  if (p.total_ent > 0 && !p.merge) carve_sort(ws, (size_t)p.total_ent, &s->sort);
+  if (p.merge) {
+    s->sort.keys[0] = ws.take<uint32_t>((size_t)p.total_ent);  // compact keys per (table, source)
+    s->sort.keys[1] = ws.take<uint32_t>((size_t)p.total_ent);  // their positions inside the partition
+    s->sort.vals[0] = ws.take<uint32_t>((size_t)p.total_ent);  // merged entry list
+    s->rows_sorted = ws.take<uint32_t>((size_t)p.total_ent);
+    s->counts = ws.take<uint32_t>((size_t)count + 1);          // valid keys per table
+    s->count_temp = ws.take<uint32_t>((size_t)p.total_sources + 1);  // valid keys per (table, source)
+  }
   if (p.counting) {
     s->rows_sorted = ws.take<uint32_t>((size_t)p.total_ent);
     s->counts = ws.take<uint32_t>((size_t)p.total_rows + 2);
@@ -2617,6 +2730,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     }
     if (pull) {
       td.pull = s.pull + source_base;
+      td.src_base = (uint32_t)source_base;
       td.pull_begin = s.pull_begin + source_base;
       td.pull_cap = items[i].partition_capacity;
       td.pull_shard = items[i].shard;
@@ -2650,8 +2764,8 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     const int passes = (bit_width_u32(invalid) + kRadixBits - 1) / kRadixBits;
     const int res_index = passes & 1;
     for (auto& td : img.tabs) {
-      td.rows = p.counting ? s.rows_sorted : s.sort.keys[res_index];
-      td.slots = p.counting ? s.sort.vals[0] : s.sort.vals[res_index];
+      td.rows = (p.counting || p.merge) ? s.rows_sorted : s.sort.keys[res_index];
+      td.slots = (p.counting || p.merge) ? s.sort.vals[0] : s.sort.vals[res_index];
     }
   }
   if (!pull_host.empty())
@@ -2660,7 +2774,18 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
   const TableDesc* tabs = reinterpret_cast<const TableDesc*>(s.image);
   {
   PhaseScope order_phase("OrderEntries", cs);
-  if (total_ent > 0 && p.counting) {
+  if (total_ent > 0 && p.merge) {
+    // Row-sharded tables: every source's partition is ordered by row already; merge them.
+    SC_CUDA_OK(cudaMemsetAsync(s.counts, 0, ((size_t)count + 1) * sizeof(uint32_t), cs));
+    pull_compact_kernel<<<(unsigned)p.total_sources, kScanThreads, 0, cs>>>(tabs, count, s.sort.keys[0], s.sort.keys[1],
+                                                                           s.count_temp, s.counts);
+    SC_LAUNCH_OK("pull_compact_kernel");
+    pull_ranges_kernel<<<1, kScanThreads, 0, cs>>>(count, s.counts, s.ranges);
+    SC_LAUNCH_OK("pull_ranges_kernel");
+    pull_merge_kernel<<<(unsigned)ceil_div(total_ent, kBlock), kBlock, 0, cs>>>(tabs, count, total_ent, s.sort.keys[0], s.sort.keys[1],
+                                                                               s.count_temp, s.ranges, s.rows_sorted, s.sort.vals[0]);
+    SC_LAUNCH_OK("pull_merge_kernel");
+  } else if (total_ent > 0 && p.counting) {
     // Entries of several SparseCores / shards / devices: order them by global row first, entries of
     // one row in entry order (source, sample): counting sort on the row, one for all tables.
     const uint32_t total_rows = invalid;
