@@ -109,7 +109,8 @@ struct TableDesc {
   int32_t pull_shard;
   int32_t num_sources;
   int32_t pull_rows;    // rows of a source's gradient buffer (samples, or slots when it holds reduced runs)
-  uint32_t src_base;    // index of this table's first source among the sources of all tables of the call
+  uint32_t tile_base;   // merge of the sources' partitions: first compaction tile of this table ...
+  uint32_t tiles_per_list;  // ... and tiles per (table, source) partition
   // Reduce-only mode (opt.kind == kReduceOnly, indirect == 2): the entry list is this device's own
   // CSR buffer (entry e = slot e, rows[e] = shard * rows_per_shard + id or kNoRow) and the sum of
   // every run is stored at red[first slot of the run] instead of being applied to a table.
@@ -1857,84 +1858,111 @@ __global__ void bwd_keys_kernel(const TableDesc* __restrict__ tabs, int count, u
 
 // ---- pull mode: the sources' partitions are already ordered by row, so the entry list is a MERGE
 //
-// pull_compact_kernel  block per (table, source): the valid entries of the source's partition - run heads when
-//                      the sources exchange reduced runs, with padding slots between them - are compacted in
-//                      order: ckeys = row inside the shard, cidx = position inside the partition; lens = count
-// pull_ranges_kernel   ranges[t] = valid entries of the tables before t (one block)
-// pull_merge_kernel    position of compact entry c of source s = c + sum over the other sources o of the number
-//                      of their keys that sort before it (smaller row; equal row and o < s): binary searches in
-//                      the compact lists.  Equal rows keep source order, then position: the order of a stable
-//                      sort by row, without counters or sorting passes.
-__global__ void __launch_bounds__(kScanThreads) pull_compact_kernel(const TableDesc* __restrict__ tabs, int count,
-                                                                    uint32_t* __restrict__ ckeys, uint32_t* __restrict__ cidx,
-                                                                    uint32_t* __restrict__ lens, uint32_t* __restrict__ table_counts) {
-  __shared__ uint32_t s_done;
-  const uint32_t b = blockIdx.x;
-  const int t = find_table(count, b, [&](int i) { return tabs[i].src_base; });
-  const TableDesc& td = tabs[t];
-  const int s = (int)(b - td.src_base);
-  const PullSrc& src = td.pull[s];
+// The valid entries of a source's partition (run heads when the sources exchange reduced runs, with
+// padding slots between them) are first compacted, in order, tile by tile:
+//   pull_tile_count_kernel    valid entries per tile of kPullTile partition slots
+//   exclusive scan            over all tiles (ordered by table, source, position): offsets of the tiles,
+//                             and with them the length of every compact list and the range of every table
+//   pull_tile_scatter_kernel  ckeys = row inside the shard, cidx = position inside the partition
+// and then merged:
+//   pull_merge_kernel         position of compact entry c of source s = c + sum over the other sources o of
+//                             the number of their keys that sort before it (smaller row; equal row and o < s),
+//                             by binary search.  Equal rows keep source order, then position: the order of a
+//                             stable sort by row, without counters or sorting passes.
+constexpr int kPullItems = 8;
+constexpr int kPullTile = kScanThreads * kPullItems;  // 2048
+
+// The partition slots [first, last) of the tile and where its source's partition starts.
+struct PullTile {
+  int t, s;
+  int begin;        // first slot of the partition in the source buffer
+  int first, last;  // positions inside the partition
+};
+
+__device__ __forceinline__ PullTile pull_tile_of(const TableDesc* __restrict__ tabs, int count, uint32_t tile) {
+  PullTile p;
+  p.t = find_table(count, tile, [&](int i) { return tabs[i].tile_base; });
+  const TableDesc& td = tabs[p.t];
+  const uint32_t local = tile - td.tile_base;
+  p.s = (int)(local / td.tiles_per_list);
+  const int k = (int)(local - (uint32_t)p.s * td.tiles_per_list);
+  const int32_t* rp = td.pull[p.s].row_pointers;
   const int g = td.pull_shard;
-  const int begin = g == 0 ? 0 : ((src.row_pointers[g - 1] + kAlign - 1) & ~(kAlign - 1));
-  const int end = min(src.row_pointers[g], begin + td.pull_cap);
-  uint32_t* out_k = ckeys + td.ent_base + (uint32_t)s * (uint32_t)td.pull_cap;
-  uint32_t* out_i = cidx + td.ent_base + (uint32_t)s * (uint32_t)td.pull_cap;
-  if (threadIdx.x == 0) {
-    td.pull_begin[s] = begin;
-    s_done = 0;
+  p.begin = g == 0 ? 0 : ((rp[g - 1] + kAlign - 1) & ~(kAlign - 1));
+  const int len = min(max(rp[g] - p.begin, 0), td.pull_cap);
+  p.first = min(k * kPullTile, len);
+  p.last = min(p.first + kPullTile, len);
+  return p;
+}
+
+__global__ void __launch_bounds__(kScanThreads) pull_tile_count_kernel(const TableDesc* __restrict__ tabs, int count,
+                                                                       uint32_t* __restrict__ tile_counts) {
+  const PullTile p = pull_tile_of(tabs, count, blockIdx.x);
+  const TableDesc& td = tabs[p.t];
+  const int32_t* ids = td.pull[p.s].ids + p.begin;
+  uint32_t mine = 0;
+  for (int j = p.first + (int)threadIdx.x; j < p.last; j += kScanThreads) {
+    const int id = ids[j];
+    mine += (id >= 0 && (int64_t)id < td.v.rows_per_shard) ? 1u : 0u;
   }
-  __syncthreads();
-  for (int j0 = begin; j0 < end; j0 += kScanThreads) {
-    const int j = j0 + (int)threadIdx.x;
-    int id = -1;
-    if (j < end) id = src.ids[j];
-    const bool valid = id >= 0 && (int64_t)id < td.v.rows_per_shard;
-    uint32_t total;
-    const uint32_t before = block_exclusive_scan<uint32_t>(valid ? 1u : 0u, &total);
-    if (valid) {
-      const uint32_t c = s_done + before;
-      out_k[c] = (uint32_t)id;
-      out_i[c] = (uint32_t)(j - begin);
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) s_done += total;
-    __syncthreads();
-  }
+  uint32_t total;
+  block_exclusive_scan<uint32_t>(mine, &total);
   if (threadIdx.x == 0) {
-    lens[b] = s_done;
-    atomicAdd(&table_counts[t], s_done);
+    tile_counts[blockIdx.x] = total;
+    if (p.first == 0) td.pull_begin[p.s] = p.begin;
   }
 }
 
-__global__ void pull_ranges_kernel(int count, const uint32_t* __restrict__ table_counts, uint32_t* __restrict__ ranges) {
-  __shared__ uint32_t s_base;
-  if (threadIdx.x == 0) s_base = 0;
-  __syncthreads();
-  for (int t0 = 0; t0 < count; t0 += kScanThreads) {
-    const int t = t0 + (int)threadIdx.x;
-    const uint32_t mine = t < count ? table_counts[t] : 0u;
-    uint32_t total;
-    const uint32_t before = block_exclusive_scan<uint32_t>(mine, &total);
-    if (t < count) ranges[t] = s_base + before;
-    __syncthreads();
-    if (threadIdx.x == 0) s_base += total;
-    __syncthreads();
+// offs = exclusive scan of the tile counts, offs[total_tiles] = grand total.
+__global__ void __launch_bounds__(kScanThreads) pull_tile_scatter_kernel(const TableDesc* __restrict__ tabs, int count,
+                                                                         uint32_t total_tiles, const uint32_t* __restrict__ offs,
+                                                                         uint32_t* __restrict__ ckeys, uint32_t* __restrict__ cidx,
+                                                                         uint32_t* __restrict__ ranges) {
+  const PullTile p = pull_tile_of(tabs, count, blockIdx.x);
+  const TableDesc& td = tabs[p.t];
+  const uint32_t list_first = td.tile_base + (uint32_t)p.s * td.tiles_per_list;
+  if (threadIdx.x == 0 && blockIdx.x == td.tile_base) {
+    ranges[p.t] = offs[blockIdx.x];
+    if (p.t == count - 1) ranges[count] = offs[total_tiles];
   }
-  if (threadIdx.x == 0) ranges[count] = s_base;
+  const int32_t* ids = td.pull[p.s].ids + p.begin;
+  // Thread i takes kPullItems consecutive slots, so the compact order is the slot order.
+  const int j0 = p.first + (int)threadIdx.x * kPullItems;
+  int id[kPullItems];
+  uint32_t mine = 0;
+#pragma unroll
+  for (int i = 0; i < kPullItems; ++i) {
+    id[i] = j0 + i < p.last ? ids[j0 + i] : -1;
+    if (id[i] >= 0 && (int64_t)id[i] >= td.v.rows_per_shard) id[i] = -1;
+    mine += id[i] >= 0 ? 1u : 0u;
+  }
+  uint32_t total;
+  uint32_t c = block_exclusive_scan<uint32_t>(mine, &total) + (offs[blockIdx.x] - offs[list_first]);
+  uint32_t* out_k = ckeys + td.ent_base + (uint32_t)p.s * (uint32_t)td.pull_cap;
+  uint32_t* out_i = cidx + td.ent_base + (uint32_t)p.s * (uint32_t)td.pull_cap;
+#pragma unroll
+  for (int i = 0; i < kPullItems; ++i) {
+    if (id[i] >= 0) {
+      out_k[c] = (uint32_t)id[i];
+      out_i[c] = (uint32_t)(j0 + i);
+      ++c;
+    }
+  }
 }
 
 __global__ void pull_merge_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_ent,
                                   const uint32_t* __restrict__ ckeys, const uint32_t* __restrict__ cidx,
-                                  const uint32_t* __restrict__ lens, const uint32_t* __restrict__ ranges,
-                                  uint32_t* __restrict__ rows_sorted, uint32_t* __restrict__ list) {
+                                  const uint32_t* __restrict__ offs, uint32_t* __restrict__ rows_sorted,
+                                  uint32_t* __restrict__ list) {
   const uint32_t ge = blockIdx.x * blockDim.x + threadIdx.x;
   if (ge >= total_ent) return;
   const int t = find_table(count, ge, [&](int i) { return tabs[i].ent_base; });
   const TableDesc& td = tabs[t];
-  const uint32_t cap = (uint32_t)td.pull_cap;
+  const uint32_t cap = (uint32_t)td.pull_cap, tpl = td.tiles_per_list;
   const uint32_t q = ge - td.ent_base;
   const uint32_t s = q / cap, c = q - s * cap;
-  if (c >= lens[td.src_base + s]) return;
+  const uint32_t* list_offs = offs + td.tile_base;  // compact list o holds offs[(o + 1) * tpl] - offs[o * tpl] keys
+  if (c >= list_offs[(s + 1) * tpl] - list_offs[s * tpl]) return;
   const uint32_t key = ckeys[ge];
   uint32_t pos = c;
   for (uint32_t o = 0; o < (uint32_t)td.num_sources; ++o) {
@@ -1942,14 +1970,14 @@ __global__ void pull_merge_kernel(const TableDesc* __restrict__ tabs, int count,
     const uint32_t* other = ckeys + td.ent_base + o * cap;
     // Keys of source o that sort before this entry: row < key, and row == key when o < s.
     const uint32_t bound = o < s ? key + 1u : key;
-    uint32_t lo = 0, hi = lens[td.src_base + o];
+    uint32_t lo = 0, hi = list_offs[(o + 1) * tpl] - list_offs[o * tpl];
     while (lo < hi) {
       const uint32_t mid = (lo + hi) >> 1;
       if (other[mid] < bound) lo = mid + 1; else hi = mid;
     }
     pos += lo;
   }
-  const uint32_t at = ranges[t] + pos;
+  const uint32_t at = list_offs[0] + pos;
   rows_sorted[at] = td.row_base + key;
   list[at] = td.ent_base + s * cap + cidx[ge];
 }
@@ -2443,7 +2471,7 @@ struct BwdPlan {
   std::vector<CsrView> views;
   std::vector<int> indirect;
   std::vector<uint32_t> n_ent;  // entry index space per table (0 for direct tables)
-  uint64_t total_chunks = 0, total_ent = 0, total_rows = 0;
+  uint64_t total_chunks = 0, total_ent = 0, total_rows = 0, total_tiles = 0;
   int total_shards = 0, total_sources = 0;
   int w = 0, k = 0, g = 0, max_dim = 0, kind = 0, max_slots = 0;
   bool counting = false;  // order the indirect entries by a counting sort on the row instead of a radix sort
@@ -2478,6 +2506,7 @@ int plan_bwd(const sc_grad_item_t* items, int count, BwdPlan* p) {
       }
       p->n_ent[i] = (uint32_t)((int64_t)v.P * items[i].partition_capacity);
       p->total_sources += v.P;
+      p->total_tiles += (uint64_t)v.P * (uint64_t)ceil_div(items[i].partition_capacity, kPullTile);
     } else {
       p->n_ent[i] = (v.S == 1 && v.P == 1) ? 0u : (uint32_t)v.coo;
     }
@@ -2534,8 +2563,8 @@ bool carve_bwd(Workspace& ws, const BwdPlan& p, int count, BwdScratch* s) {
     s->sort.keys[1] = ws.take<uint32_t>((size_t)p.total_ent);  // their positions inside the partition
     s->sort.vals[0] = ws.take<uint32_t>((size_t)p.total_ent);  // merged entry list
     s->rows_sorted = ws.take<uint32_t>((size_t)p.total_ent);
-    s->counts = ws.take<uint32_t>((size_t)count + 1);          // valid keys per table
-    s->count_temp = ws.take<uint32_t>((size_t)p.total_sources + 1);  // valid keys per (table, source)
+    s->counts = ws.take<uint32_t>((size_t)p.total_tiles + 1);  // valid keys per tile, then their exclusive scan
+    s->count_temp = ws.take<uint32_t>(scan_temp_elems((size_t)p.total_tiles));
   }
   if (p.counting) {
     s->rows_sorted = ws.take<uint32_t>((size_t)p.total_ent);
@@ -2699,7 +2728,7 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
   GroupImage img;
   std::vector<int> pool_index;
   std::vector<PullSrc> pull_host;
-  uint32_t chunk_base = 0, ent_base = 0, row_base = 0;
+  uint32_t chunk_base = 0, ent_base = 0, row_base = 0, tile_base = 0;
   int source_base = 0;
   bool ring = p.w == 4 && pipe_enabled();  // 16-byte asynchronous copies need aligned rows
   for (int i = 0; i < count; ++i) {
@@ -2730,7 +2759,9 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
     }
     if (pull) {
       td.pull = s.pull + source_base;
-      td.src_base = (uint32_t)source_base;
+      td.tiles_per_list = (uint32_t)ceil_div(items[i].partition_capacity, kPullTile);
+      td.tile_base = tile_base;
+      tile_base += (uint32_t)items[i].num_sources * td.tiles_per_list;
       td.pull_begin = s.pull_begin + source_base;
       td.pull_cap = items[i].partition_capacity;
       td.pull_shard = items[i].shard;
@@ -2776,14 +2807,15 @@ extern "C" int32_t sc_sparse_dense_matmul_grad_grouped(const sc_grad_item_t* ite
   PhaseScope order_phase("OrderEntries", cs);
   if (total_ent > 0 && p.merge) {
     // Row-sharded tables: every source's partition is ordered by row already; merge them.
-    SC_CUDA_OK(cudaMemsetAsync(s.counts, 0, ((size_t)count + 1) * sizeof(uint32_t), cs));
-    pull_compact_kernel<<<(unsigned)p.total_sources, kScanThreads, 0, cs>>>(tabs, count, s.sort.keys[0], s.sort.keys[1],
-                                                                           s.count_temp, s.counts);
-    SC_LAUNCH_OK("pull_compact_kernel");
-    pull_ranges_kernel<<<1, kScanThreads, 0, cs>>>(count, s.counts, s.ranges);
-    SC_LAUNCH_OK("pull_ranges_kernel");
+    const uint32_t total_tiles = (uint32_t)p.total_tiles;
+    pull_tile_count_kernel<<<total_tiles, kScanThreads, 0, cs>>>(tabs, count, s.counts);
+    SC_LAUNCH_OK("pull_tile_count_kernel");
+    SC_CUDA_OK(exclusive_scan<uint32_t>(s.counts, s.counts, (size_t)total_tiles, s.count_temp, s.counts + total_tiles, cs));
+    pull_tile_scatter_kernel<<<total_tiles, kScanThreads, 0, cs>>>(tabs, count, total_tiles, s.counts, s.sort.keys[0], s.sort.keys[1],
+                                                                  s.ranges);
+    SC_LAUNCH_OK("pull_tile_scatter_kernel");
     pull_merge_kernel<<<(unsigned)ceil_div(total_ent, kBlock), kBlock, 0, cs>>>(tabs, count, total_ent, s.sort.keys[0], s.sort.keys[1],
-                                                                               s.count_temp, s.ranges, s.rows_sorted, s.sort.vals[0]);
+                                                                               s.counts, s.rows_sorted, s.sort.vals[0]);
     SC_LAUNCH_OK("pull_merge_kernel");
   } else if (total_ent > 0 && p.counting) {
     // Entries of several SparseCores / shards / devices: order them by global row first, entries of
