@@ -326,10 +326,12 @@ struct Vec<1> {
 
 // flags[slot] = 1 where the slot starts a run of equal ids inside a partition of a REMOTE shard.
 // Entries of a partition are ordered by id, so a run is all lookups of one remote row.
-__global__ void fwd_remote_heads_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+// The kernels of the remote-row fetch work on the slots [first, first + total_slots) of the tables `tabs`
+// (a part of the call's tables); flags, before and run_ord are indexed by global slot.
+__global__ void fwd_remote_heads_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first, uint32_t total_slots,
                                         uint32_t* __restrict__ flags) {
-  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
-  if (gq >= total_slots) return;
+  const uint32_t gq = first + blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= first + total_slots) return;
   const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
   const TableDesc& td = tabs[t];
   const CsrView& v = td.v;
@@ -355,11 +357,11 @@ struct FetchJob {
 
 // `before` = exclusive scan of the head flags.  Thread per slot: writes run_ord for every slot of
 // a remote partition and, for run heads, the fetch job of the run's row.
-__global__ void fwd_fetch_plan_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_slots,
+__global__ void fwd_fetch_plan_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first, uint32_t total_slots,
                                       const uint32_t* __restrict__ before, uint32_t* __restrict__ run_ord,
                                       FetchJob* __restrict__ jobs) {
-  const uint32_t gq = blockIdx.x * blockDim.x + threadIdx.x;
-  if (gq >= total_slots) return;
+  const uint32_t gq = first + blockIdx.x * blockDim.x + threadIdx.x;
+  if (gq >= first + total_slots) return;
   const int t = find_table(count, gq, [&](int i) { return tabs[i].slot_base; });
   const TableDesc& td = tabs[t];
   const CsrView& v = td.v;
@@ -487,13 +489,14 @@ struct RowMeta {
 // entries are loaded before the first of them is added, in bag order.  Every activation row is
 // written exactly once; the sum runs in ascending slot order.
 template <int W, int K, int G>
-__global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : 3) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
+__global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : 3) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first_act,
+    uint32_t total_act) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
   constexpr int U = K >= 4 ? 2 : K == 2 ? 4 : 8;  // rows in registers per group: 8 vectors per lane
   __shared__ RowMeta s_meta[kWarpsPerBlock][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + wib) * 32u;
+  const uint32_t r0 = first_act + (blockIdx.x * kWarpsPerBlock + wib) * 32u;  // rows [first_act, total_act) of `tabs`
   if (r0 >= total_act) return;
   {
     RowMeta m;
@@ -605,7 +608,8 @@ __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : 3) fwd_gather_kernel(cons
 // few registers and more warps fit an SM.  Same warp / group layout as fwd_gather_kernel; a group
 // keeps the table rows of two of its activation rows in flight.  Rows without an entry are zeroed.
 template <int W, int K, int G>
-__global__ void __launch_bounds__(kBlock) fwd_gather_single_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
+__global__ void __launch_bounds__(kBlock) fwd_gather_single_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first_act,
+    uint32_t total_act) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
   struct Meta {
@@ -616,7 +620,7 @@ __global__ void __launch_bounds__(kBlock) fwd_gather_single_kernel(const TableDe
   };
   __shared__ Meta s_meta[kWarpsPerBlock][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const uint32_t r0 = (blockIdx.x * kWarpsPerBlock + wib) * 32u;
+  const uint32_t r0 = first_act + (blockIdx.x * kWarpsPerBlock + wib) * 32u;  // rows [first_act, total_act) of `tabs`
   if (r0 >= total_act) return;
   {
     Meta m;
@@ -710,7 +714,8 @@ constexpr uint32_t kEntSkip = 0x40000000u;  // contributes nothing
 // (rows without entries are zeroed by the warp); sums run in ascending slot order with separately
 // rounded multiply and add, so the result equals a sequential float32 loop bit for bit.
 template <int K, int NG>
-__global__ void __launch_bounds__(kFwdBlock) fwd_ring_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_act) {
+__global__ void __launch_bounds__(kFwdBlock) fwd_ring_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first_act,
+    uint32_t total_act) {
   constexpr int Gc = 32 / NG;           // lanes of a consumer group
   constexpr int RPG = 32 / NG;          // rows of a consumer group
   constexpr int R = fwd_ring_steps(K);
@@ -719,7 +724,7 @@ __global__ void __launch_bounds__(kFwdBlock) fwd_ring_kernel(const TableDesc* __
   constexpr uint32_t kStepBytes = (uint32_t)K * 512u;
   extern __shared__ __align__(128) unsigned char fwd_smem[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const uint32_t r0 = (blockIdx.x * kFwdWarps + wib) * 32u;
+  const uint32_t r0 = first_act + (blockIdx.x * kFwdWarps + wib) * 32u;  // rows [first_act, total_act) of `tabs`
   if (r0 >= total_act) return;
   unsigned char* mine = fwd_smem + (size_t)wib * fwd_ring_warp_bytes(K, NG);
   const uint32_t ring_base = smem_addr(mine);
@@ -2168,24 +2173,24 @@ int configure_smem(size_t smem) {
 }
 
 template <int K, int NG>
-int launch_fwd_ring(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
+int launch_fwd_ring(const TableDesc* tabs, int count, uint32_t first_act, uint32_t end_act, cudaStream_t st) {
   const size_t smem = (size_t)kFwdWarps * fwd_ring_warp_bytes(K, NG);
   if (int rc = configure_smem<fwd_ring_kernel<K, NG>>(smem)) return rc;
-  const unsigned warps = (unsigned)ceil_div(total_act, 32);
-  fwd_ring_kernel<K, NG><<<(unsigned)ceil_div(warps, kFwdWarps), kFwdBlock, smem, st>>>(tabs, count, total_act);
+  const unsigned warps = (unsigned)ceil_div(end_act - first_act, 32);
+  fwd_ring_kernel<K, NG><<<(unsigned)ceil_div(warps, kFwdWarps), kFwdBlock, smem, st>>>(tabs, count, first_act, end_act);
   SC_LAUNCH_OK("fwd_ring_kernel");
   return SC_OK;
 }
 
 // Gather with the cp.async ring; the longest row of the group picks the shape.
-inline int dispatch_fwd_ring(const TableDesc* tabs, int count, uint32_t total_act, int max_dim, cudaStream_t st) {
+inline int dispatch_fwd_ring(const TableDesc* tabs, int count, uint32_t first_act, uint32_t end_act, int max_dim, cudaStream_t st) {
   const int vecs = max_dim / 4;
-  if (vecs <= 8) return launch_fwd_ring<1, 4>(tabs, count, total_act, st);
-  if (vecs <= 16) return launch_fwd_ring<1, 2>(tabs, count, total_act, st);
-  if (vecs <= 32) return launch_fwd_ring<1, 1>(tabs, count, total_act, st);
-  if (vecs <= 64) return launch_fwd_ring<2, 1>(tabs, count, total_act, st);
-  if (vecs <= 128) return launch_fwd_ring<4, 1>(tabs, count, total_act, st);
-  return launch_fwd_ring<8, 1>(tabs, count, total_act, st);
+  if (vecs <= 8) return launch_fwd_ring<1, 4>(tabs, count, first_act, end_act, st);
+  if (vecs <= 16) return launch_fwd_ring<1, 2>(tabs, count, first_act, end_act, st);
+  if (vecs <= 32) return launch_fwd_ring<1, 1>(tabs, count, first_act, end_act, st);
+  if (vecs <= 64) return launch_fwd_ring<2, 1>(tabs, count, first_act, end_act, st);
+  if (vecs <= 128) return launch_fwd_ring<4, 1>(tabs, count, first_act, end_act, st);
+  return launch_fwd_ring<8, 1>(tabs, count, first_act, end_act, st);
 }
 
 // The register kernel with L2 prefetch is the default gather; SC_FWD_KERNEL=ring selects the cp.async ring.
@@ -2195,17 +2200,17 @@ inline bool fwd_ring_enabled() {
 }
 
 template <int W, int K, int G>
-int launch_fwd_single(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
-  const unsigned warps = (unsigned)ceil_div(total_act, 32);
-  fwd_gather_single_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act);
+int launch_fwd_single(const TableDesc* tabs, int count, uint32_t first_act, uint32_t end_act, cudaStream_t st) {
+  const unsigned warps = (unsigned)ceil_div(end_act - first_act, 32);
+  fwd_gather_single_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, first_act, end_act);
   SC_LAUNCH_OK("fwd_gather_single_kernel");
   return SC_OK;
 }
 
 template <int W, int K, int G>
-int launch_fwd(const TableDesc* tabs, int count, uint32_t total_act, cudaStream_t st) {
-  const unsigned warps = (unsigned)ceil_div(total_act, 32);
-  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_act);
+int launch_fwd(const TableDesc* tabs, int count, uint32_t first_act, uint32_t end_act, cudaStream_t st) {
+  const unsigned warps = (unsigned)ceil_div(end_act - first_act, 32);
+  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, first_act, end_act);
   SC_LAUNCH_OK("fwd_gather_kernel");
   return SC_OK;
 }
@@ -2363,9 +2368,11 @@ int launch_bwd(const TableDesc* tabs, int count, uint32_t total_chunks, const Up
 
 // A second stream per device for work that may overlap the caller's stream, with the two
 // events that fork it from and join it to that stream.  Created on first use, never destroyed.
+constexpr int kMaxFwdParts = 4;
 struct SideStream {
   cudaStream_t stream;
   cudaEvent_t fork, join;
+  cudaEvent_t part[kMaxFwdParts];  // the remote rows of part k of a forward call have arrived
 };
 
 SideStream* side_stream() {
@@ -2377,6 +2384,8 @@ SideStream* side_stream() {
     if (cudaStreamCreateWithFlags(&streams[dev].stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&streams[dev].fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&streams[dev].join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int k = 0; k < kMaxFwdParts; ++k)
+      if (cudaEventCreateWithFlags(&streams[dev].part[k], cudaEventDisableTiming) != cudaSuccess) return nullptr;
     ready[dev] = true;
   }
   return &streams[dev];
@@ -2459,7 +2468,7 @@ bool carve_fwd(Workspace& ws, const FwdPlan& p, int count, FwdScratch* s) {
   s->big_rows = ws.take<uint32_t>(build ? slots / kSerialSortLimit + 1 : 0);
   s->run_ord = ws.take<uint32_t>(p.remote_floats ? slots : 0);
   s->heads = ws.take<uint32_t>(p.remote_floats ? slots : 0);
-  s->heads_temp = ws.take<uint32_t>(p.remote_floats ? scan_temp_elems(slots) + 1 : 0);
+  s->heads_temp = ws.take<uint32_t>(p.remote_floats ? scan_temp_elems(slots) + kMaxFwdParts : 0);
   s->fetch_jobs = ws.take<FetchJob>(p.remote_floats ? slots : 0);
   s->remote_rows = ws.take<float>((size_t)p.remote_floats);
   return ws.ok();
@@ -2649,26 +2658,52 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
   const uint32_t total_slots = (uint32_t)p.total_slots, total_act = (uint32_t)p.total_act;
 
   PhaseScope whole("tpu_sparse_dense_matmul", cs);
+  // With remote shards the tables can be handled in up to kMaxFwdParts parts of about equal size, the remote
+  // rows of part k + 1 being fetched (side stream) while part k is gathered (this stream).  Measured on 2 GPUs
+  // (26 tables, 65536 single-hot lookups each) the parts LOSE, 0.54 ms against 0.44 ms: the gather fills every
+  // SM, so the fetch of the next part only runs in its tail, and every part pays the small planning kernels
+  // again.  One part is the default; SC_FWD_PARTS=2..4 selects the split.
+  static const int wanted_parts = [] {
+    const char* e = getenv("SC_FWD_PARTS");
+    const int v = e ? atoi(e) : 1;
+    return v < 1 ? 1 : v > kMaxFwdParts ? kMaxFwdParts : v;
+  }();
+  int part_begin[kMaxFwdParts + 1];
+  int parts = 1;
+  part_begin[0] = 0;
+  if (p.remote_floats > 0 && p.mode == kPlanGiven && wanted_parts > 1) {
+    const uint64_t per_part = (p.total_slots + wanted_parts - 1) / wanted_parts;
+    for (int i = 1; i < count && parts < wanted_parts; ++i)
+      if ((uint64_t)img.tabs[i].slot_base >= per_part * (uint64_t)parts) part_begin[parts++] = i;
+  }
+  part_begin[parts] = count;
+  auto slot_end = [&](int i) { return i < count ? img.tabs[i].slot_base : total_slots; };
+  auto act_end = [&](int i) { return i < count ? img.tabs[i].act_base : total_act; };
   SideStream* side = nullptr;
   if (p.remote_floats > 0) {
-    // Rows of remote shards: fetch each distinct row once, then gather from the local copies.  The
-    // fetch (NVLink-bound) runs on a side stream while this stream builds the plan.
+    // Rows of remote shards: fetch each distinct row once, then gather from the local copies.
     side = side_stream();
     if (side == nullptr) SC_FAIL(SC_CUDA_ERROR, "cannot create the side stream of the forward");
     SC_CUDA_OK(cudaEventRecord(side->fork, cs));
     SC_CUDA_OK(cudaStreamWaitEvent(side->stream, side->fork, 0));
     cudaStream_t fs = side->stream;
     PhaseScope phase("FetchRemoteRows", fs);
-    fwd_remote_heads_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, fs>>>(tabs, count, total_slots, s.heads);
-    SC_LAUNCH_OK("fwd_remote_heads_kernel");
-    uint32_t* total_jobs = s.heads_temp + scan_temp_elems((size_t)total_slots);
-    SC_CUDA_OK(exclusive_scan<uint32_t>(s.heads, s.heads, (size_t)total_slots, s.heads_temp, total_jobs, fs));
-    fwd_fetch_plan_kernel<<<(unsigned)ceil_div(total_slots, kBlock), kBlock, 0, fs>>>(tabs, count, total_slots, s.heads, s.run_ord,
-                                                                                     s.fetch_jobs);
-    SC_LAUNCH_OK("fwd_fetch_plan_kernel");
-    fwd_fetch_kernel<<<(unsigned)sm_count() * 8, kBlock, 0, fs>>>(s.fetch_jobs, total_jobs, total_slots);
-    SC_LAUNCH_OK("fwd_fetch_kernel");
-    SC_CUDA_OK(cudaEventRecord(side->join, fs));
+    for (int k = 0; k < parts; ++k) {
+      const int a = part_begin[k], n = part_begin[k + 1] - a;
+      const uint32_t first = slot_end(a), slots = slot_end(a + n) - first;
+      if (slots > 0) {
+        const unsigned blocks = (unsigned)ceil_div(slots, kBlock);
+        fwd_remote_heads_kernel<<<blocks, kBlock, 0, fs>>>(tabs + a, n, first, slots, s.heads);
+        SC_LAUNCH_OK("fwd_remote_heads_kernel");
+        uint32_t* total_jobs = s.heads_temp + scan_temp_elems((size_t)total_slots) + k;
+        SC_CUDA_OK(exclusive_scan<uint32_t>(s.heads + first, s.heads + first, (size_t)slots, s.heads_temp, total_jobs, fs));
+        fwd_fetch_plan_kernel<<<blocks, kBlock, 0, fs>>>(tabs + a, n, first, slots, s.heads, s.run_ord, s.fetch_jobs + first);
+        SC_LAUNCH_OK("fwd_fetch_plan_kernel");
+        fwd_fetch_kernel<<<(unsigned)sm_count() * 8, kBlock, 0, fs>>>(s.fetch_jobs + first, total_jobs, slots);
+        SC_LAUNCH_OK("fwd_fetch_kernel");
+      }
+      SC_CUDA_OK(cudaEventRecord(side->part[k], fs));
+    }
   }
   if (p.mode == kPlanSingle) {
     PhaseScope phase("ForwardPlan", cs);
@@ -2693,17 +2728,27 @@ extern "C" int32_t sc_sparse_dense_matmul_fwd_grouped(const sc_fwd_item_t* items
                                                                bit_width_u32(total_slots), 1);
     SC_LAUNCH_OK("fwd_bigrow_kernel");
   }
-  if (side != nullptr) SC_CUDA_OK(cudaStreamWaitEvent(cs, side->join, 0));  // the gather reads the fetched rows
   PhaseScope phase("GatherCombine", cs);
-  if (ring) return dispatch_fwd_ring(tabs, count, total_act, p.max_dim, cs);
-  if (p.single_valent) {
-#define SC_FWD_SINGLE_CALL(W, K, G) launch_fwd_single<W, K, G>(tabs, count, total_act, cs)
-    SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_SINGLE_CALL);
+  for (int k = 0; k < parts; ++k) {
+    const int a = part_begin[k], n = part_begin[k + 1] - a;
+    const uint32_t first = act_end(a), end = act_end(a + n);
+    if (side != nullptr) SC_CUDA_OK(cudaStreamWaitEvent(cs, side->part[k], 0));  // this part's remote rows have arrived
+    if (end == first) continue;
+    int rc = SC_OK;
+    if (ring) {
+      rc = dispatch_fwd_ring(tabs + a, n, first, end, p.max_dim, cs);
+    } else if (p.single_valent) {
+#define SC_FWD_SINGLE_CALL(W, K, G) launch_fwd_single<W, K, G>(tabs + a, n, first, end, cs)
+      rc = [&]() -> int { SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_SINGLE_CALL); }();
 #undef SC_FWD_SINGLE_CALL
-  }
-#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs, count, total_act, cs)
-  SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL);
+    } else {
+#define SC_FWD_CALL(W, K, G) launch_fwd<W, K, G>(tabs + a, n, first, end, cs)
+      rc = [&]() -> int { SC_SHAPE_SWITCH(p.w, p.k, p.g, SC_FWD_CALL); }();
 #undef SC_FWD_CALL
+    }
+    if (rc != SC_OK) return rc;
+  }
+  return SC_OK;
 }
 
 extern "C" size_t sc_sparse_dense_matmul_grad_grouped_workspace_bytes(const sc_grad_item_t* items, int32_t count) {
