@@ -1464,30 +1464,35 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
 }
 
 // ---- the same pipeline for rows of at most 64 floats: several rows per warp instruction
-// Step slots of 512 bytes in a warp's ring and steps in flight while one is consumed: 16 rows in flight.
-__host__ __device__ constexpr int group_ring_steps(int NG) { return NG >= 4 ? 8 : 16; }
-__host__ __device__ constexpr int group_ahead(int NG) { return NG >= 4 ? 4 : 8; }
-__host__ __device__ constexpr int group_list_rows(int NS) { return 32 * (2 + NS) + 4; }
-__host__ __device__ constexpr size_t group_pipe_warp_bytes(int NG, int NS) {
-  return (size_t)group_ring_steps(NG) * 512 + (size_t)group_list_rows(NS) * 16;
+constexpr int kGroupRingSteps = 8;  // step slots of 512 bytes in a warp's ring
+constexpr int kGroupAhead = 4;      // steps in flight while one is consumed
+constexpr uint32_t kRowToRun = 128; // a run that this chunk owns ends here: keep its sum for the apply phase (index in bits 8..12)
+// Per warp: ring | gradient-row list (address, descriptor, gain per entry) | table / slot row addresses of the
+// runs to apply | the sums of those runs.
+__host__ __device__ constexpr size_t group_pipe_warp_bytes(int NG, bool reduce_only) {
+  return (size_t)kGroupRingSteps * 512 + 32 * 16 + (reduce_only ? 0 : 32 * 3 * 8 + 32 * (32 / NG) * 16);
 }
 
-// Same contract and the same row descriptors as bwd_pipe_kernel, for rows that fill only a part
-// of a warp (dim <= 64).  The warp's 32 lanes form NG groups of 32 / NG lanes (4 groups for rows of
-// up to 32 floats, 2 up to 64).  Every run of the chunk belongs to the group in whose window of
-// 32 / NG entries it starts, so the runs - and with them the table rows to update - are dealt to
-// the groups in contiguous, roughly equal shares; each group gets its own part of the row list.
-// All groups then advance in lockstep: in step t every group streams and executes the t-th row
-// of its part, 16 bytes per lane, through a ring of 512-byte step slots (kGroupAhead steps in
-// flight).  One warp instruction therefore moves or sums NG rows, where bwd_pipe_kernel would
-// use a quarter or half of its lanes.  Sums still run in entry order inside a run.
+// Same contract as bwd_pipe_kernel, for rows that fill only a part of a warp (dim <= 64).  The warp's
+// 32 lanes form NG groups of 32 / NG lanes (4 groups for rows of up to 32 floats, 2 up to 64), and a
+// chunk is processed in two phases whose steps are uniform across the groups:
+//   reduce  every run of the chunk belongs to the group in whose window of 32 / NG entries it starts, so
+//           the runs are dealt to the groups in contiguous, roughly equal shares.  In step t every group
+//           streams the t-th gradient row of its share through a ring of 512-byte step slots (16 bytes
+//           per lane, kGroupAhead steps in flight) and adds it; where a run ends, its sum goes to shared
+//           memory (runs owned by the chunk), to the partial-sum scratch (runs that cross the chunk) or
+//           to the exchange buffer (reduce-only mode);
+//   apply   the runs to apply are dealt round-robin, NG per step triple: the groups stream the table row
+//           and the slot rows of their runs and all apply the optimizer in the same step.
+// One warp instruction therefore moves, sums or updates NG rows, and the long optimizer epilogue is
+// never executed for the sake of a single group.  Sums still run in entry order inside a run.
 template <int NG, int NS, bool REDUCE, bool EXTRA>
 __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableDesc* __restrict__ tabs, int count,
                                                                    uint32_t total_chunks, float* __restrict__ partial,
                                                                    uint8_t* __restrict__ chunk_flags, int pstride) {
   constexpr int Gc = 32 / NG;
-  constexpr int R = group_ring_steps(NG), A = group_ahead(NG);
-  constexpr int kListRows = group_list_rows(NS);
+  constexpr int R = kGroupRingSteps, A = kGroupAhead;
+  constexpr int kRowsPerApply = 1 + NS;
   static_assert(A + 1 + NS < R, "a step being applied must not be overwritten by the copies issued ahead");
   extern __shared__ __align__(128) unsigned char pipe_smem[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
@@ -1505,12 +1510,14 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   const RowCtx ctx = make_ctx(td);
   const int dim = ctx.dim;
   const int vec_per_row = dim >> 2;
-  unsigned char* mine = pipe_smem + (size_t)wib * group_pipe_warp_bytes(NG, NS);
+  unsigned char* mine = pipe_smem + (size_t)wib * group_pipe_warp_bytes(NG, REDUCE);
   const uint32_t ring_base = smem_addr(mine);
   unsigned char* list = mine + (size_t)R * 512;
   const float** rowaddr = reinterpret_cast<const float**>(list);
-  uint32_t* rowdesc = reinterpret_cast<uint32_t*>(list + kListRows * 8);
-  float* rowgain = reinterpret_cast<float*>(list + kListRows * 12);
+  uint32_t* rowdesc = reinterpret_cast<uint32_t*>(list + 32 * 8);
+  float* rowgain = reinterpret_cast<float*>(list + 32 * 12);
+  float** applyaddr = reinterpret_cast<float**>(list + 32 * 16);  // [run][table, slot 0, slot 1]
+  const uint32_t runs_base = smem_addr(list + 32 * 16 + 32 * 3 * 8);  // [run][Gc float4]
 
   const int e = e0 + lane;
   const uint32_t my_row = entry_row(td, e, n);
@@ -1550,14 +1557,14 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   const bool head_run = valid && ((heads >> run_start) & 1u);
   const bool is_end = valid && (lane == 31 || (((starts | ~valids) >> (lane + 1)) & 1u));
   const bool goes_on = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
-  const bool w_end = is_end && head_run && !goes_on;                // apply the optimizer here
+  const bool w_end = is_end && head_run && !goes_on;                // a run that this chunk owns ends here
   const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
   if (lane == 31)
     chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
-  constexpr int kExtra = REDUCE ? 0 : 1 + NS;
-  // Deal the runs to the groups and lay the groups' parts of the list out one after the other.
+  // Deal the runs to the groups and lay the groups' shares of the gradient rows out one after the other.
   const int grp = valid ? run_start / Gc : NG;
-  int my_part_base = 0, my_part_rows = 0;  // part of the group this lane CONSUMES for
+  const int my_group = lane / Gc, gl = lane % Gc;
+  int my_part_base = 0, my_part_rows = 0;  // share of the group this lane CONSUMES for
   int o = 0;                               // list position of this lane's entry
   int max_rows = 0;
   {
@@ -1565,93 +1572,119 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
 #pragma unroll
     for (int g = 0; g < NG; ++g) {
       const uint32_t gm = __ballot_sync(0xffffffffu, grp == g);
-      const int rows = __popc(gm) + kExtra * __popc(wendmask & gm);
-      if (grp == g) o = base + __popc(gm & lt) + kExtra * __popc(wendmask & gm & lt);
-      if (lane / Gc == g) { my_part_base = base; my_part_rows = rows; }
+      const int rows = __popc(gm);
+      if (grp == g) o = base + __popc(gm & lt);
+      if (my_group == g) { my_part_base = base; my_part_rows = rows; }
       max_rows = max(max_rows, rows);
       base += rows;
     }
   }
+  const int apply_index = __popc(wendmask & lt);  // of the run that ends at this lane
+  // Every address of the chunk is known now: ask L2 for the rows, so that the two phases below stream from L2
+  // instead of paying the DRAM latency once per ring step.
+  if (my_src != nullptr) prefetch_row(my_src, dim * 4);
   if (valid) {
     rowaddr[o] = my_src != nullptr ? my_src : any_grad;
     rowdesc[o] = kRowGrad | (((starts >> lane) & 1u) ? kRowZero : 0u) | (my_src == nullptr ? kRowIgnore : 0u) |
                  ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u) |
-                 ((REDUCE && w_end) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u);
+                 ((REDUCE && w_end) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u) |
+                 ((!REDUCE && w_end) ? (kRowToRun | ((uint32_t)apply_index << 8)) : 0u);
     rowgain[o] = my_gain;
     if (!REDUCE && w_end) {
       float *pw, *pa, *pb;
       row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
-      rowaddr[++o] = pw;
-      rowdesc[o] = NS == 0 ? kRowApply : 0u;
-      if (NS >= 1) { rowaddr[++o] = pa; rowdesc[o] = NS == 1 ? kRowApply : 0u; }
-      if (NS >= 2) { rowaddr[++o] = pb; rowdesc[o] = kRowApply; }
+      applyaddr[apply_index * 3 + 0] = pw;
+      applyaddr[apply_index * 3 + 1] = pa;
+      applyaddr[apply_index * 3 + 2] = pb;
+      prefetch_row(pw, dim * 4);
+      if (NS >= 1) prefetch_row(pa, dim * 4);
+      if (NS >= 2) prefetch_row(pb, dim * 4);
     }
   }
   __syncwarp();
 
-  const int gl = lane % Gc;
   const bool in_row = gl < vec_per_row;
   const uint32_t lane_off = (uint32_t)lane * 16u;
-  // Starts the copies of step t: the t-th row of every group's part.  Always one commit group.
-  auto issue = [&](int t) {
-    if (t < my_part_rows && in_row)
-      cp_async16(ring_base + (uint32_t)(t & (R - 1)) * 512u + lane_off,
-                 reinterpret_cast<const float4*>(rowaddr[my_part_base + t]) + gl);
-    cp_async_commit();
-  };
-  const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  auto consume = [&](int t) {
-    if (t >= my_part_rows) return;
-    const int r = my_part_base + t;
-    const uint32_t d = rowdesc[r];
-    const uint32_t slot_addr = ring_base + (uint32_t)(t & (R - 1)) * 512u + lane_off;
-    if (d & kRowGrad) {
+  const uint32_t run_off = (uint32_t)gl * 16u;
+  // ---- phase 1: the groups reduce their runs
+  {
+    auto issue = [&](int step) {
+      if (step < my_part_rows && in_row)
+        cp_async16(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off,
+                   reinterpret_cast<const float4*>(rowaddr[my_part_base + step]) + gl);
+      cp_async_commit();
+    };
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto consume = [&](int step) {
+      if (step >= my_part_rows) return;
+      const int r = my_part_base + step;
+      const uint32_t d = rowdesc[r];
       if (d & kRowZero) acc = make_float4(0.f, 0.f, 0.f, 0.f);
       if (!(d & kRowIgnore) && in_row) {
         const float gain = rowgain[r];
-        const float4 x = lds128(slot_addr);
+        const float4 x = lds128(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off);
         acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
         acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
       }
-      if (REDUCE && (d & kRowReduce)) {
-        if (in_row) reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((d >> 8) & 31u)) * dim)[gl] = acc;
+      if (!in_row) return;
+      if (!REDUCE && (d & kRowToRun)) {
+        const uint32_t dst = runs_base + ((d >> 8) & 31u) * (uint32_t)(Gc * 16) + run_off;
+        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
       }
-      if (d & kRowPartial) {
-        if (in_row)
-          reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * pstride)[gl] = acc;
-      }
-    } else if (!REDUCE && (d & kRowApply)) {
-      // Steps t - NS .. t of this group hold the table row and the slot rows.
-      if (in_row) {
-        float* pw = const_cast<float*>(rowaddr[r - NS]);
-        float* pa = NS >= 1 ? const_cast<float*>(rowaddr[r - NS + (NS >= 1 ? 1 : 0)]) : nullptr;
-        float* pb = NS >= 2 ? const_cast<float*>(rowaddr[r]) : nullptr;
-        float4 w = lds128(ring_base + (uint32_t)((t - NS) & (R - 1)) * 512u + lane_off);
-        float4 x0 = NS >= 1 ? lds128(ring_base + (uint32_t)((t - NS + 1) & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 x1 = NS >= 2 ? lds128(slot_addr) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float* wf = reinterpret_cast<float*>(&w);
-        float* af = reinterpret_cast<float*>(&x0);
-        float* bf = reinterpret_cast<float*>(&x1);
-        const float* gf = reinterpret_cast<const float*>(&acc);
+      if (REDUCE && (d & kRowReduce)) reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((d >> 8) & 31u)) * dim)[gl] = acc;
+      if (d & kRowPartial)
+        reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * pstride)[gl] = acc;
+    };
 #pragma unroll
-        for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast<NS, EXTRA>(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
-        reinterpret_cast<float4*>(pw)[gl] = w;
-        if (NS >= 1) reinterpret_cast<float4*>(pa)[gl] = x0;
-        if (NS >= 2) reinterpret_cast<float4*>(pb)[gl] = x1;
-      }
+    for (int a = 0; a < A; ++a) issue(a);
+    for (int step = 0; step < max_rows; ++step) {
+      issue(step + A);
+      cp_async_wait<A>();  // this lane's copies of `step` have landed
+      __syncwarp();        // ... and every other lane's
+      consume(step);
     }
-  };
-
-#pragma unroll
-  for (int a = 0; a < A; ++a) issue(a);
-  for (int step = 0; step < max_rows; ++step) {
-    issue(step + A);
-    cp_async_wait<A>();  // this lane's copies of `step` have landed
-    __syncwarp();        // ... and every other lane's
-    consume(step);
+    cp_async_wait<0>();
   }
-  cp_async_wait<0>();
+  if (REDUCE) return;
+  const int num_apply = __popc(wendmask);
+  if (num_apply == 0) return;
+  __syncwarp();  // the sums of all runs are in shared memory; the ring is free again
+  // ---- phase 2: NG runs per step triple; step kRowsPerApply * u + k streams array k of run u * NG + group
+  {
+    const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
+    const int steps = ((num_apply + NG - 1) / NG) * kRowsPerApply;
+    auto issue = [&](int step) {
+      const int a = (step / kRowsPerApply) * NG + my_group;
+      if (step < steps && a < num_apply && in_row)
+        cp_async16(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off,
+                   reinterpret_cast<const float4*>(applyaddr[a * 3 + step % kRowsPerApply]) + gl);
+      cp_async_commit();
+    };
+#pragma unroll
+    for (int a = 0; a < A; ++a) issue(a);
+    for (int step = 0; step < steps; ++step) {
+      issue(step + A);
+      cp_async_wait<A>();
+      __syncwarp();
+      if (step % kRowsPerApply != NS) continue;  // the run's last array has landed: apply
+      const int a = (step / kRowsPerApply) * NG + my_group;
+      if (a >= num_apply || !in_row) continue;
+      float4 w = lds128(ring_base + (uint32_t)((step - NS) & (R - 1)) * 512u + lane_off);
+      float4 x0 = NS >= 1 ? lds128(ring_base + (uint32_t)((step - NS + 1) & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
+      float4 x1 = NS >= 2 ? lds128(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 g = lds128(runs_base + (uint32_t)a * (uint32_t)(Gc * 16) + run_off);
+      float* wf = reinterpret_cast<float*>(&w);
+      float* af = reinterpret_cast<float*>(&x0);
+      float* bf = reinterpret_cast<float*>(&x1);
+      const float* gf = reinterpret_cast<const float*>(&g);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast<NS, EXTRA>(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
+      reinterpret_cast<float4*>(applyaddr[a * 3 + 0])[gl] = w;
+      if (NS >= 1) reinterpret_cast<float4*>(applyaddr[a * 3 + 1])[gl] = x0;
+      if (NS >= 2) reinterpret_cast<float4*>(applyaddr[a * 3 + 2])[gl] = x1;
+    }
+    cp_async_wait<0>();
+  }
 }
 
 // Second level of the partial sums, for rows hit by thousands of entries.  Warp per group of 32
@@ -2271,7 +2304,7 @@ int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, con
 
 template <int NG, int NS, bool REDUCE = false, bool EXTRA = false>
 int launch_group_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
-  const size_t smem = (size_t)kPipeWarps * group_pipe_warp_bytes(NG, NS);
+  const size_t smem = (size_t)kPipeWarps * group_pipe_warp_bytes(NG, REDUCE);
   if (int rc = configure_smem<bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>>(smem)) return rc;
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
   bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
