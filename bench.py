@@ -703,12 +703,12 @@ def config_block(name, world, rank, args, peak):
     wl = dict(wl, batch=131072 // world)
   global_batch = wl["batch"] * world
   run = Run(name, wl, world, rank, global_batch)
-  for _ in range(5):
+  for _ in range(10):
     run.step()
   ms, launches = run.timed_steps(10)
   roof = run.operator_rooflines(10, peak)
   out = {"workload": describe(name, wl, wl["batch"]), "global_batch": global_batch,
-         "scaling": "strong" if strong else "weak", "steps": 10, "warmup": 5, "ms_per_step": ms,
+         "scaling": "strong" if strong else "weak", "steps": 10, "warmup": 10, "ms_per_step": ms,
          "value": global_batch / (ms * 1e-3), "unit": "samples/s", "gpu_launches": launches,
          "forward": roof["forward"], "backward": roof["backward"], "nnz": roof["nnz"], "unique_rows": roof["unique_rows"],
          "table_bytes": int(run.table_bytes), "preprocess": run.preprocess_block(5, peak)}
