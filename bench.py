@@ -36,6 +36,11 @@ for _p in (ROOT, os.path.join(ROOT, "jax-tpu-embedding_b200")):
 
 L2_BYTES = 126 * 1024 * 1024
 NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+# DRAM traffic of the backward kernels per launch (dram__bytes_read.sum + dram__bytes_write.sum of ncu) divided by
+# the algorithmic bytes of the same launch, from captures of cases small enough for ncu's replay passes: c2 and c3
+# with scaled-down vocabularies (traffic and algorithmic bytes grow with the same quantities: lookups, distinct
+# rows, batch), c5 at full size.  c3: update kernel only (its fix-up pass was not captured).  None: no capture.
+TRAFFIC_RATIO = {"c2": 1.03, "c3": 0.90, "c5": 1.04, "c4": None, "c1": None}
 
 
 # --------------------------------------------------------------------------------- workloads
@@ -712,6 +717,8 @@ def config_block(name, world, rank, args, peak):
          "value": global_batch / (ms * 1e-3), "unit": "samples/s", "gpu_launches": launches,
          "forward": roof["forward"], "backward": roof["backward"], "nnz": roof["nnz"], "unique_rows": roof["unique_rows"],
          "table_bytes": int(run.table_bytes), "preprocess": run.preprocess_block(5, peak)}
+  ratio = TRAFFIC_RATIO.get(name)
+  out["backward"]["traffic"] = None if ratio is None else int(roof["backward"]["algorithmic_bytes"] * ratio)
   hbm_ms = (roof["forward"]["algorithmic_bytes"] + roof["backward"]["algorithmic_bytes"]) / (peak * 1e9) * 1e3
   out["hbm_bound_ms"] = hbm_ms
   if world > 1:
@@ -815,10 +822,8 @@ def main():
   reps = max(3, min(args.steps, 20))
   roof = run.operator_rooflines(reps, peak)
   bwd, fwd = roof["backward"], roof["forward"]
-  # DRAM traffic per launch of the backward kernels, from an ncu capture of a scaled-down c2 case: 1.03 x the
-  # algorithmic bytes; both grow with the same quantities, so the ratio is applied to this launch.  Other
-  # workloads have no capture: null.
-  traffic = int(bwd["algorithmic_bytes"] * 1.03) if args.workload == "c2" else None
+  ratio = TRAFFIC_RATIO.get(args.workload)
+  traffic = None if ratio is None else int(bwd["algorithmic_bytes"] * ratio)
   preprocess = run.preprocess_block(max(3, min(args.steps, 10)), peak)
   phases = run.phases(max(3, min(args.steps, 10)))
   parity = run.parity() if args.parity else None
