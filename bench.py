@@ -477,13 +477,22 @@ class Run:
     e1.record()
     torch.cuda.synchronize()
     ms = self.max_over_ranks(e0.elapsed_time(e1) / reps)
+    from jax_tpu_embedding.sparsecore import _native
+
+    _native.phase_timing(True)
+    for _ in range(reps):
+      run()
+    torch.cuda.synchronize()
+    stages = {k: v[0] / reps for k, v in _native.phase_report().items()}
+    _native.phase_timing(False)
     rows = sum(f.shape[0] if isinstance(f, np.ndarray) else len(f.row_splits) - 1 for f in self.feats)
     written = sum(table_stats(self.pre, name, self.world, self.rank)[0] for name in self.stacked)
     weighted = self.wl["weights"]
     nbytes = self.nnz_in * (4 + (4 if weighted else 0)) + rows * 4 + written * 12 + len(self.stacked) * 8 * 4
     return {"ms": ms, "ids_per_s": self.nnz_in * self.world / (ms * 1e-3), "algorithmic_bytes": int(nbytes),
-            "achieved": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak,
-            "includes": "all kernels of one call and its read of the statistics block (one synchronisation)"}
+            "achieved": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak, "stages_ms": stages,
+            "includes": "all kernels of one call and its read of the statistics block (one synchronisation); "
+                        "stages_ms: device time of the call's stages (CUDA events)"}
 
   def phases(self, reps):
     """Stage times per step (ms) from the library's CUDA events plus the barriers of the sharded step."""
