@@ -665,33 +665,56 @@ class Run:
       torch.cuda.set_device(device)
       return prepare_batch()
 
-    def lookup_update_step(batch):
+    # The step's result is read back every step, but the host does not stall on it: the checksum of step i is
+    # copied to pinned memory behind the step's kernels and read by the host during step i + 1 (what a training
+    # loop does with its loss), so the GPU always has the next kernels queued.
+    results = [torch.zeros(1, pin_memory=True) for _ in range(2)]
+    landed = [None, None]
+    checksums = []
+
+    def collect(k):
+      if landed[k] is not None:
+        landed[k].synchronize()
+        checksums.append(float(results[k][0]))
+        landed[k] = None
+
+    def lookup_update_step(batch, index):
       p2, done = batch
       nxt = pool.submit(prepare_in_worker)
       main_stream.wait_event(done)
       acts = embedding.tpu_sparse_dense_matmul(p2, self.variables, specs, global_device_count=world, num_sc_per_device=1)
-      # The step's result read back by the host: a checksum over the first 1024 values of every feature's
-      # activations; the activations themselves stay on the device for the dense part of a model.
+      # A checksum over the first 1024 values of every feature's activations; the activations themselves stay on
+      # the device for the dense part of a model.
       checksum = torch.cat([a[:rows_1024] for a in acts]).sum()
+      k = index % 2
+      collect(k)  # the read-back of two steps ago has long landed
+      results[k].copy_(checksum.reshape(1), non_blocking=True)
+      landed[k] = torch.cuda.Event()
+      landed[k].record()
       embedding.tpu_sparse_dense_matmul_grad(self.grads, p2, self.variables, specs, global_device_count=world,
                                              num_sc_per_device=1, step=0)
-      return float(checksum.item()), nxt.result()
+      collect(1 - k)  # the previous step's result, while this step's kernels run
+      return nxt.result()
 
     batch = prepare_batch()
-    for _ in range(2):
-      _, batch = lookup_update_step(batch)
+    for i in range(2):
+      batch = lookup_update_step(batch, i)
+    collect(0), collect(1)
     self.barrier()
     t0 = time.perf_counter()
-    for _ in range(steps):
-      _, batch = lookup_update_step(batch)
+    for i in range(steps):
+      batch = lookup_update_step(batch, i)
+    collect(0), collect(1)  # every step's result has reached the host before the clock stops
     self.barrier()
     pool.shutdown()
+    assert len(checksums) == steps + 2 and all(np.isfinite(checksums))
     ms = self.max_over_ranks((time.perf_counter() - t0) / steps * 1e3)
     return {"value": self.wl["batch"] * world / (ms * 1e-3), "unit": "samples/s", "ms_per_step": ms,
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": 4 + 4 * sum(2 * 1 + 1 + 3 for _ in self.stacked),
             "host": "two Python threads: one issues copy + preprocessing of the next batch, one lookup, read-back and update",
-            "read_back": "a 4-byte checksum of 1024 activations per feature; the activations stay on the device and the "
-                         "preprocessing statistics are copied to pinned memory without a wait (sync_stats=False)",
+            "read_back": "a 4-byte checksum of 1024 activations per feature, every step, copied to pinned memory behind the "
+                         "step's kernels and read by the host during the next step; the activations stay on the device and "
+                         "the preprocessing statistics are copied to pinned memory without a wait (sync_stats=False)",
             "pipeline": "copy + preprocessing of batch i+1 on a second stream while batch i is looked up and updated"}
 
   def release(self):

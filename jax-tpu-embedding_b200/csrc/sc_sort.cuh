@@ -144,16 +144,50 @@ static __global__ void __launch_bounds__(kSortThreads) radix_hist_kernel(const u
   hist[(size_t)threadIdx.x * tiles + blockIdx.x] = bins[threadIdx.x];
 }
 
+// hist is [digit][tile].  Block d turns row d into its exclusive prefix over the tiles and stores the row's total
+// in totals[d]: together with an exclusive scan of the 256 totals (done by every scatter block for itself) that is
+// the position of each (digit, tile) run in the output, in two launches per pass instead of a device-wide scan.
+static __global__ void __launch_bounds__(kScanThreads) radix_rowscan_kernel(uint32_t* __restrict__ hist, uint32_t tiles,
+                                                                            uint32_t* __restrict__ totals) {
+  __shared__ uint32_t s_carry;
+  uint32_t* row = hist + (size_t)blockIdx.x * tiles;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (uint32_t base = 0; base < tiles; base += kScanTile) {
+    const uint32_t first = base + threadIdx.x * kScanItems;
+    uint32_t v[kScanItems];
+    uint32_t sum = 0;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) {
+      v[i] = first + i < tiles ? row[first + i] : 0u;
+      sum += v[i];
+    }
+    uint32_t total;
+    uint32_t prefix = block_exclusive_scan<uint32_t>(sum, &total) + s_carry;
+#pragma unroll
+    for (int i = 0; i < kScanItems; ++i) {
+      if (first + i < tiles) row[first + i] = prefix;
+      prefix += v[i];
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) totals[blockIdx.x] = s_carry;
+}
+
 // Stable scatter of one tile.  Warp w owns the contiguous span [w*512, (w+1)*512) of
 // the tile and visits it in 16 rounds of 32 consecutive keys, so ranks follow input
 // order.  vals_in == nullptr means "payload = input index".
 static __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
                                                                      uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
-                                                                     const uint32_t* __restrict__ offsets, size_t n, int shift,
+                                                                     const uint32_t* __restrict__ offsets,
+                                                                     const uint32_t* __restrict__ totals, size_t n, int shift,
                                                                      uint32_t digit_mask, uint32_t tiles) {
   constexpr int kWarps = kSortThreads / 32;
   __shared__ uint32_t warp_cnt[kWarps][kRadix];
   __shared__ uint32_t digit_start[kRadix];
+  __shared__ uint32_t digit_base[kRadix];  // keys of all tiles with a smaller digit
   __shared__ uint32_t s_keys[kSortTile];
   __shared__ uint32_t s_vals[kSortTile];
 
@@ -193,6 +227,7 @@ static __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(cons
     uint32_t total;
     uint32_t start = block_exclusive_scan<uint32_t>(run, &total);
     digit_start[d] = start;
+    digit_base[d] = block_exclusive_scan<uint32_t>(totals[d], &total);
   }
   __syncthreads();
 #pragma unroll
@@ -209,7 +244,7 @@ static __global__ void __launch_bounds__(kSortThreads) radix_scatter_kernel(cons
   for (uint32_t j = threadIdx.x; j < tile_count; j += kSortThreads) {
     const uint32_t k = s_keys[j];
     const uint32_t d = (k >> shift) & digit_mask;
-    const size_t dst = (size_t)offsets[(size_t)d * tiles + blockIdx.x] + (j - digit_start[d]);
+    const size_t dst = (size_t)digit_base[d] + offsets[(size_t)d * tiles + blockIdx.x] + (j - digit_start[d]);
     keys_out[dst] = k;
     vals_out[dst] = s_vals[j];
   }
@@ -223,7 +258,7 @@ struct SortBuffers {
 };
 
 inline size_t sort_tiles(size_t n) { return (size_t)ceil_div((int64_t)(n ? n : 1), kSortTile); }
-inline size_t sort_hist_elems(size_t n) { return (size_t)kRadix * sort_tiles(n); }
+inline size_t sort_hist_elems(size_t n) { return (size_t)kRadix * sort_tiles(n) + kRadix; }  // + the digit totals
 
 // Sorts (keys[0], vals[0]) ascending by the low `bits` bits of the key, stably.
 // vals[0] may be nullptr on entry only through `iota_payload` (payload = position).
@@ -245,11 +280,14 @@ inline cudaError_t radix_sort_pairs(SortBuffers& b, size_t n, int bits, bool iot
     count_launch(2);  // histogram and scatter of this pass
     cudaError_t err = cudaGetLastError();
     if (err != cudaSuccess) return err;
-    err = exclusive_scan<uint32_t>(b.hist, b.hist, (size_t)kRadix * tiles, b.scan_temp, nullptr, stream);
+    uint32_t* totals = b.hist + (size_t)kRadix * tiles;
+    radix_rowscan_kernel<<<kRadix, kScanThreads, 0, stream>>>(b.hist, tiles, totals);
+    count_launch();
+    err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     const uint32_t* vin = (p == 0 && iota_payload) ? nullptr : b.vals[cur];
-    radix_scatter_kernel<<<tiles, kSortThreads, 0, stream>>>(b.keys[cur], vin, b.keys[cur ^ 1], b.vals[cur ^ 1], b.hist, n, shift,
-                                                             mask, tiles);
+    radix_scatter_kernel<<<tiles, kSortThreads, 0, stream>>>(b.keys[cur], vin, b.keys[cur ^ 1], b.vals[cur ^ 1], b.hist, totals, n,
+                                                             shift, mask, tiles);
     err = cudaGetLastError();
     if (err != cudaSuccess) return err;
     cur ^= 1;

@@ -191,10 +191,14 @@ class ForwardGroupCall:
       nbytes = lib.sc_sparse_dense_matmul_fwd_grouped_workspace_bytes(items, len(idxs))
       if nbytes == 0:
         _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), None, 0, None))
-      self.groups.append((items, idxs, nbytes))
+      # The activation pointers of the group's descriptors as one strided numpy view (filled per run).
+      act_field = np.ndarray((len(idxs),), dtype=np.uint64, buffer=items, offset=_native.FwdItem.activations.offset,
+                             strides=(ctypes.sizeof(_native.FwdItem),))
+      self.groups.append((items, idxs, nbytes, act_field))
     self.shapes = [tuple(r.act.shape) for r in requests]
     self.sizes = [int(np.prod(shape)) for shape in self.shapes]
     self.total_floats = sum(self.sizes)
+    self.byte_offsets = np.concatenate([[0], np.cumsum(self.sizes)[:-1]]).astype(np.uint64) * np.uint64(4)
     self.first = True
     self.sharded = any(r.geo.l != r.geo.c for r in requests)
     self.keep = [(r.ptrs,) for r in requests]
@@ -211,16 +215,16 @@ class ForwardGroupCall:
       # One allocation for all activations of the call.
       flat = torch.empty(self.total_floats, dtype=torch.float32, device="cuda")
       outs = [t.view(shape) for t, shape in zip(flat.split(self.sizes), self.shapes)]
-      for items, idxs, _ in self.groups:
-        for j, i in enumerate(idxs):
-          items[j].activations = outs[i].data_ptr()
+      addresses = self.byte_offsets + np.uint64(flat.data_ptr())
+      for _, idxs, _, act_field in self.groups:
+        act_field[:] = addresses[idxs]
     stream = _native.current_stream_ptr()
     if self.sharded:
       # Every peer must have finished updating its shard before remote rows are read.
       from jax_tpu_embedding.sparsecore import distributed  # pylint: disable=g-import-not-at-top
 
       distributed.barrier_before_lookup()
-    for items, idxs, nbytes in self.groups:
+    for items, idxs, nbytes, _ in self.groups:
       ws = _native.workspace(nbytes, "lookup")
       _native.check(lib.sc_sparse_dense_matmul_fwd_grouped(items, len(idxs), ws.data_ptr(), ws.numel(), stream))
     return outs

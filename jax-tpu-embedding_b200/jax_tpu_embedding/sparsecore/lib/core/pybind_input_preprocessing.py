@@ -522,6 +522,36 @@ class _DensePlan:
     self.int_total = pos
     self.float_offsets = [4 * sum(self.coos[:i]) for i in range(n)]
     self.float_total = sum(self.coos)
+    # One split of the int32 buffer yields every output view: pieces in address order, alignment gaps included.
+    pieces = sorted([(off // 4, size, ("csr", i)) for i, (off, size) in enumerate(zip(self.int_offsets, self.int_sizes))] +
+                    [(off // 4, size, ("plan", i)) for i, (off, size) in enumerate(zip(self.plan_offsets, self.plan_sizes))])
+    self.split_sizes, self.csr_piece, self.plan_piece = [], [0] * len(self.int_sizes), [0] * len(self.plan_sizes)
+    cursor = 0
+    for off, size, (kind, i) in pieces:
+      if off > cursor:
+        self.split_sizes.append(off - cursor)
+      (self.csr_piece if kind == "csr" else self.plan_piece)[i] = len(self.split_sizes)
+      self.split_sizes.append(size)
+      cursor = off + size
+    if cursor < self.int_total:
+      self.split_sizes.append(self.int_total - cursor)
+    # The pointer fields of the launch descriptors as strided numpy views: a call fills them with a few
+    # vector operations instead of one attribute assignment per field and stack.
+    stride = ctypes.sizeof(_native.PreprocessItem)
+
+    def field(name):
+      return np.ndarray((n,), dtype=np.uint64, buffer=self.items, offset=getattr(_native.PreprocessItem, name).offset,
+                        strides=(stride,))
+
+    self.f_ids, self.f_weights = field("ids"), field("weights")
+    self.f_out = [field(k) for k in ("row_pointers", "embedding_ids", "sample_ids", "plan_slots", "plan_bags")]
+    self.o_out = [np.asarray(self.int_offsets[0::3], np.uint64), np.asarray(self.int_offsets[1::3], np.uint64),
+                  np.asarray(self.int_offsets[2::3], np.uint64), np.asarray(self.plan_offsets[0::2], np.uint64),
+                  np.asarray(self.plan_offsets[1::2], np.uint64)]
+    self.f_gains, self.o_gains = field("gains"), np.asarray(self.float_offsets, np.uint64)
+    self.f_stats, self.o_stats = field("stats"), np.arange(n, dtype=np.uint64) * np.uint64(self.stats_size * 4)
+    self.single_member = all(len(m) == 1 for m in self.members)
+    self.first_member = [m[0] for m in self.members]
     self.groups = None  # launch groups and workspace sizes, sized on the first run (needs real addresses)
     self.deferred = [None] * 4  # statistics of the last calls made with sync_stats=False (ring)
     self.deferred_next = 0
@@ -558,31 +588,33 @@ class _DensePlan:
     stats_dev = torch.empty((n, self.stats_size), dtype=torch.int32, device="cuda")
     ibase, fbase, sbase = ints.data_ptr(), floats.data_ptr(), stats_dev.data_ptr()
     keep = []
-    for si in range(n):
-      it = self.items[si]
-      idxs = self.members[si]
-      if len(idxs) == 1:
-        it.ids = features[idxs[0]].data_ptr()
-        if self.weighted:
-          it.weights = feature_weights[idxs[0]].data_ptr()
-      else:
-        cat = torch.cat([features[i].reshape(-1) for i in idxs])
-        keep.append(cat)
-        it.ids = cat.data_ptr()
-        if self.weighted:
-          wcat = torch.cat([feature_weights[i].reshape(-1) for i in idxs])
-          keep.append(wcat)
-          it.weights = wcat.data_ptr()
-      it.row_pointers = ibase + self.int_offsets[3 * si]
-      it.embedding_ids = ibase + self.int_offsets[3 * si + 1]
-      it.sample_ids = ibase + self.int_offsets[3 * si + 2]
-      it.gains = fbase + self.float_offsets[si]
-      it.stats = sbase + si * self.stats_size * 4
-      if device_output:
-        it.plan_slots = ibase + self.plan_offsets[2 * si]
-        it.plan_bags = ibase + self.plan_offsets[2 * si + 1]
-      else:
-        it.plan_slots = it.plan_bags = None
+    if self.single_member:
+      self.f_ids[:] = [features[i].data_ptr() for i in self.first_member]
+      if self.weighted:
+        self.f_weights[:] = [feature_weights[i].data_ptr() for i in self.first_member]
+    else:
+      for si in range(n):
+        it = self.items[si]
+        idxs = self.members[si]
+        if len(idxs) == 1:
+          it.ids = features[idxs[0]].data_ptr()
+          if self.weighted:
+            it.weights = feature_weights[idxs[0]].data_ptr()
+        else:
+          cat = torch.cat([features[i].reshape(-1) for i in idxs])
+          keep.append(cat)
+          it.ids = cat.data_ptr()
+          if self.weighted:
+            wcat = torch.cat([feature_weights[i].reshape(-1) for i in idxs])
+            keep.append(wcat)
+            it.weights = wcat.data_ptr()
+    for view, offsets in zip(self.f_out[:3] if not device_output else self.f_out, self.o_out):
+      view[:] = offsets + np.uint64(ibase)
+    if not device_output:
+      self.f_out[3][:] = 0
+      self.f_out[4][:] = 0
+    self.f_gains[:] = self.o_gains + np.uint64(fbase)
+    self.f_stats[:] = self.o_stats + np.uint64(sbase)
     stream = _native.current_stream_ptr()
     if self.groups is None:
       self._size_groups()
@@ -624,30 +656,28 @@ class _DensePlan:
       stats.required_buffer_sizes = LazyStatsDict(deferred=deferred, field=2)
       stats.dropped_id_count = LazyStatsDict(deferred=deferred, field=3)
     del keep
-    int_views = ints[:sum(self.int_sizes)].split(self.int_sizes)
+    pieces = ints.split(self.split_sizes)
     float_views = floats.split(self.coos)
-    out_rp, out_ids, out_sids, out_gains = BufferDict(), BufferDict(), BufferDict(), BufferDict()
-    for si, name in enumerate(self.names):
-      arrays = (int_views[3 * si], int_views[3 * si + 1], int_views[3 * si + 2], float_views[si])
-      if has_leading_dimension:
-        arrays = tuple(t.view(1, -1) for t in arrays)
-      if not device_output:
-        arrays = tuple(t.cpu().numpy() for t in arrays)
-      out_rp[name], out_ids[name], out_sids[name], out_gains[name] = arrays
-      if host is not None:
+    columns = [[pieces[self.csr_piece[3 * si + k]] for si in range(n)] for k in range(3)] + [list(float_views)]
+    if has_leading_dimension:
+      columns = [[t.view(1, -1) for t in col] for col in columns]
+    if not device_output:
+      columns = [[t.cpu().numpy() for t in col] for col in columns]
+    # dict.__init__ fills the dicts without the per-item bookkeeping of BufferDict.__setitem__.
+    out_rp, out_ids, out_sids, out_gains = (BufferDict(zip(self.names, col)) for col in columns)
+    if host is not None:
+      for si, name in enumerate(self.names):
         stats.max_ids_per_partition[name] = max_ids[si]
         stats.max_unique_ids_per_partition[name] = max_unique[si]
         stats.required_buffer_sizes[name] = required[si]
         stats.dropped_id_count[name] = int(dropped[si])
     if device_output:
       # The arrays keep the two buffers alive, so the addresses identify the contents' location.
-      token = (ints.data_ptr(), floats.data_ptr(), id(self), bool(has_leading_dimension))
+      token = (ibase, fbase, id(self), bool(has_leading_dimension))
       for i, d in enumerate((out_rp, out_ids, out_sids, out_gains)):
         d.token = token + (i,)
-      out_rp.forward_plans = {
-          name: (ints[self.plan_offsets[2 * si] // 4:self.plan_offsets[2 * si] // 4 + self.plan_sizes[2 * si]],
-                 ints[self.plan_offsets[2 * si + 1] // 4:self.plan_offsets[2 * si + 1] // 4 + self.plan_sizes[2 * si + 1]])
-          for si, name in enumerate(self.names)}
+      out_rp.forward_plans = {name: (pieces[self.plan_piece[2 * si]], pieces[self.plan_piece[2 * si + 1]])
+                              for si, name in enumerate(self.names)}
     return out_rp, out_ids, out_sids, out_gains, 1, stats
 
 
