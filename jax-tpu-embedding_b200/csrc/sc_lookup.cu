@@ -488,12 +488,18 @@ struct RowMeta {
 // the next G (with an L2 prefetch of their rows) while these are summed - and the table rows of U
 // entries are loaded before the first of them is added, in bag order.  Every activation row is
 // written exactly once; the sum runs in ascending slot order.
+// Rows of up to 64 floats (K <= 2): 4 blocks per SM and U = 4 / 2 rows in registers; measured against 3 blocks and
+// U = 8 / 4 on the multi-hot benchmark configurations: 0.118 ms instead of 0.181 ms (dim 64, bags of ~20) and 0.94 ms
+// instead of 1.11 ms (dim 32, bags of ~8.5).  Longer rows keep 3 blocks (4 were 12 % slower at dim 128).
+#ifndef SC_GATHER_ROWS_SHORT
+#define SC_GATHER_ROWS_SHORT 4
+#endif
 template <int W, int K, int G>
-__global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : 3) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first_act,
+__global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : K <= 2 ? 4 : 3) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first_act,
     uint32_t total_act) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
-  constexpr int U = K >= 4 ? 2 : K == 2 ? 4 : 8;  // rows in registers per group: 8 vectors per lane
+  constexpr int U = K >= 4 ? 2 : SC_GATHER_ROWS_SHORT / K;  // table rows held in registers per group
   __shared__ RowMeta s_meta[kWarpsPerBlock][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t r0 = first_act + (blockIdx.x * kWarpsPerBlock + wib) * 32u;  // rows [first_act, total_act) of `tabs`

@@ -14,7 +14,8 @@ import threading
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsc_b200.so")
+# SC_B200_LIBRARY selects another build of the library (kernel tuning experiments).
+LIB_PATH = os.environ.get("SC_B200_LIBRARY") or os.path.join(_HERE, "libsc_b200.so")
 
 SC_OK = 0
 SC_INVALID_ARGUMENT = 1
