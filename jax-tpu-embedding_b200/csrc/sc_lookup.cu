@@ -1215,7 +1215,8 @@ __host__ __device__ constexpr int pipe_ring_rows(int K, int NS) {
   const int need = (kPipeAhead + 1) * pipe_batch_rows(K) + 1 + NS;
   return need <= 4 ? 4 : need <= 8 ? 8 : 16;
 }
-__host__ __device__ constexpr int pipe_list_rows(int K, int NS) { return 32 * (2 + NS) + pipe_batch_rows(K); }
+// Rows of a warp's list: 32 entries, up to 31 entries taken over from the next chunk, 1 + NS rows per run end.
+__host__ __device__ constexpr int pipe_list_rows(int K, int NS) { return 32 * (3 + NS) + pipe_batch_rows(K); }
 // Per-warp shared memory besides the ring: row addresses (8 bytes), descriptors and gains (4 + 4).
 __host__ __device__ constexpr int pipe_list_bytes(int K, int NS) { return pipe_list_rows(K, NS) * 16; }
 
@@ -1260,6 +1261,67 @@ __device__ __forceinline__ float apply_opt_fast(const OptParams& o, bool clipped
 }
 
 
+// Position q of entry e of a table's ordered entry list (e < entry_count) in the entry space of the table.
+__device__ __forceinline__ int entry_slot(const TableDesc& td, int e) {
+  return td.indirect == 1 ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
+}
+// Gradient row and gain of the entry at position q: `src` stays nullptr when the entry's sample id is outside the
+// batch; `any_grad` is a readable address of the same memory.
+__device__ __forceinline__ void entry_source(const TableDesc& td, int q, int dim, const float*& src, float& gain,
+                                             const float*& any_grad) {
+  const CsrView& v = td.v;
+  if (td.pull != nullptr) {
+    const int s = q / td.pull_cap;
+    const PullSrc& ps = td.pull[s];
+    const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
+    const int sid = ps.sids[slot];
+    gain = ps.gains[slot];
+    any_grad = ps.grad;
+    if (sid >= 0 && sid < td.pull_rows) src = ps.grad + (int64_t)sid * dim;
+  } else {
+    const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
+    const int sid = v.sids[q];
+    gain = v.gains[q];
+    if (sid >= 0 && sid < v.bsc) src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
+  }
+}
+
+// The rows around a chunk [e0, e0 + 32), loaded together with the chunk's own rows so that no later decision waits
+// for memory again.
+struct ChunkRows {
+  uint32_t mine;    // row of entry e0 + lane (kNoRow past the list)
+  uint32_t ahead;   // row of entry e0 + 32 + lane
+  uint32_t before;  // row of entry e0 - 1
+  uint32_t back;    // row of entry e0 - 33
+};
+__device__ __forceinline__ ChunkRows load_chunk_rows(const TableDesc& td, int e0, int n, int lane) {
+  ChunkRows r;
+  r.mine = entry_row(td, e0 + lane, n);
+  r.ahead = entry_row(td, e0 + 32 + lane, n);
+  const uint32_t behind = lane < 2 ? entry_row(td, e0 - 1 - 32 * lane, n) : kNoRow;
+  r.before = __shfl_sync(0xffffffffu, behind, 0);
+  r.back = __shfl_sync(0xffffffffu, behind, 1);
+  return r;
+}
+
+// Which runs that cross a border of the chunk the chunk's warp handles alone.  A run whose head lies in chunk c
+// and which ends inside chunk c + 1 without filling it belongs to c entirely: c also reads the run's `ext` entries
+// of c + 1, and c + 1 skips its first `skip` entries.  Every other crossing run goes through the chunks' partial
+// sums.  Both chunks evaluate the same conditions on the same rows, so they agree.
+struct ChunkBorders {
+  int skip;  // leading entries of this chunk that the previous chunk handles
+  int ext;   // entries of the next chunk that this chunk handles (they continue its last run)
+};
+__device__ __forceinline__ ChunkBorders chunk_borders(const ChunkRows& r, bool last_run_head_continues) {
+  ChunkBorders b{0, 0};
+  const uint32_t lead = __ballot_sync(0xffffffffu, r.mine != kNoRow && r.mine == r.before);
+  if (lead != 0 && lead != 0xffffffffu && r.back != r.before) b.skip = __popc(lead);
+  const uint32_t last_row = __shfl_sync(0xffffffffu, r.mine, 31);
+  const uint32_t same = __ballot_sync(0xffffffffu, r.ahead == last_row);
+  if (last_run_head_continues && same != 0xffffffffu) b.ext = __ffs(~same) - 1;
+  return b;
+}
+
 // Same contract as bwd_main_kernel, for rows of `dim` floats with dim % 4 == 0 and 16-byte aligned
 // tables, slot variables and gradients.  A warp owns 32 consecutive entries.  Lane j describes
 // entry j and appends its rows to a per-warp list in shared memory, in entry order: the
@@ -1285,7 +1347,6 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   if (gchunk >= total_chunks) return;
   const int t = warp_find_table(count, gchunk, lane, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
-  const CsrView& v = td.v;
   const int n = entry_count(td);
   const int e0 = (int)(gchunk - td.chunk_base) * 32;
   if (e0 >= n) {
@@ -1304,31 +1365,12 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   float* rowgain = reinterpret_cast<float*>(list + kListRows * 12);
 
   const int e = e0 + lane;
-  const uint32_t my_row = entry_row(td, e, n);
+  const ChunkRows cr = load_chunk_rows(td, e0, n, lane);
+  const uint32_t my_row = cr.mine;
   uint32_t prev_row = __shfl_up_sync(0xffffffffu, my_row, 1);
-  if (lane == 0) prev_row = entry_row(td, e0 - 1, n);
-  const uint32_t next_row = entry_row(td, e0 + 32, n);  // row after the chunk
+  if (lane == 0) prev_row = cr.before;
+  const uint32_t next_row = __shfl_sync(0xffffffffu, cr.ahead, 0);  // row after the chunk
   const bool valid = my_row != kNoRow;
-  const float* my_src = nullptr;
-  float my_gain = 0.f;
-  const float* any_grad = td.grad;  // a readable address for entries without a gradient row
-  if (valid) {
-    const int q = td.indirect == 1 ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
-    if (td.pull != nullptr) {
-      const int s = q / td.pull_cap;
-      const PullSrc& src = td.pull[s];
-      const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
-      const int sid = src.sids[slot];
-      my_gain = src.gains[slot];
-      any_grad = src.grad;
-      if (sid >= 0 && sid < td.pull_rows) my_src = src.grad + (int64_t)sid * dim;
-    } else {
-      const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
-      const int sid = v.sids[q];
-      my_gain = v.gains[q];
-      if (sid >= 0 && sid < v.bsc) my_src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
-    }
-  }
   const uint32_t lt = (1u << lane) - 1u;
   const uint32_t heads = __ballot_sync(0xffffffffu, valid && my_row != prev_row);
   const uint32_t valids = __ballot_sync(0xffffffffu, valid);
@@ -1341,20 +1383,37 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   const int run_start = 31 - __clz(starts & (lt | (1u << lane)));
   const bool head_run = valid && ((heads >> run_start) & 1u);
   const bool is_end = valid && (lane == 31 || (((starts | ~valids) >> (lane + 1)) & 1u));
-  const bool goes_on = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
-  const bool w_end = is_end && head_run && !goes_on;                // apply the optimizer here
+  const bool crosses = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
+  const ChunkBorders border = chunk_borders(cr, __shfl_sync(0xffffffffu, crosses && head_run, 31));
+  const bool goes_on = crosses && border.ext == 0;    // ... and is summed through the partial sums
+  const bool w_end = is_end && head_run && !goes_on;  // a run that this chunk owns ends here: apply the optimizer
+  const bool listed = valid && lane >= border.skip;   // the first `skip` entries are the previous chunk's
   const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
+  const uint32_t listedmask = __ballot_sync(0xffffffffu, listed);
   if (lane == 31)
     chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
+  // Sources of this lane's entry and of the entry it describes among those taken over from the next chunk (x_*):
+  // the two chains of loads run side by side.
+  const float *my_src = nullptr, *x_src = nullptr;
+  float my_gain = 0.f, x_gain = 0.f;
+  const float* any_grad = td.grad;  // a readable address for entries without a gradient row
+  {
+    const int q = listed ? entry_slot(td, e) : -1;
+    const int xq = lane < border.ext ? entry_slot(td, e + 32) : -1;
+    if (q >= 0) entry_source(td, q, dim, my_src, my_gain, any_grad);
+    if (xq >= 0) entry_source(td, xq, dim, x_src, x_gain, any_grad);
+  }
   constexpr int kExtra = REDUCE ? 0 : 1 + NS;  // table and slot rows of an entry that applies the optimizer
-  const int total = __popc(valids) + kExtra * __popc(wendmask);  // rows to stream
-  if (valid) {
-    int o = __popc(valids & lt) + kExtra * __popc(wendmask & lt);
+  const int total = __popc(listedmask) + border.ext + kExtra * __popc(wendmask);  // rows to stream
+  if (listed) {
+    int o = __popc(listedmask & lt) + kExtra * __popc(wendmask & lt);
+    const bool more = lane == 31 && border.ext > 0;  // the run goes on with the entries taken from the next chunk
     rowaddr[o] = my_src != nullptr ? my_src : any_grad;
     rowdesc[o] = kRowGrad | (((starts >> lane) & 1u) ? kRowZero : 0u) | (my_src == nullptr ? kRowIgnore : 0u) |
                  ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u) |
-                 ((REDUCE && w_end) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u);
+                 ((REDUCE && w_end && !more) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u);
     rowgain[o] = my_gain;
+    if (more) o += border.ext;
     if (!REDUCE && w_end) {
       float *pw, *pa, *pb;
       row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
@@ -1363,6 +1422,15 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
       if (NS >= 1) { rowaddr[++o] = pa; rowdesc[o] = NS == 1 ? kRowApply : 0u; }
       if (NS >= 2) { rowaddr[++o] = pb; rowdesc[o] = kRowApply; }
     }
+  }
+  const int last_run_start = __shfl_sync(0xffffffffu, run_start, 31);
+  if (lane < border.ext) {
+    // Entry lane of the next chunk: it follows entry 31 in the list (which is listed: its run has its head here).
+    const int o = __popc(listedmask) + kExtra * __popc(wendmask & 0x7fffffffu) + lane;
+    rowaddr[o] = x_src != nullptr ? x_src : any_grad;
+    rowdesc[o] = kRowGrad | (x_src == nullptr ? kRowIgnore : 0u) |
+                 ((REDUCE && lane == border.ext - 1) ? (kRowReduce | ((uint32_t)last_run_start << 8)) : 0u);
+    rowgain[o] = x_gain;
   }
   if (lane < B) rowdesc[total + lane] = 0;  // the tail of the last batch does nothing
   __syncwarp();
@@ -1472,33 +1540,40 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
 // ---- the same pipeline for rows of at most 64 floats: several rows per warp instruction
 constexpr int kGroupRingSteps = 8;  // step slots of 512 bytes in a warp's ring
 constexpr int kGroupAhead = 4;      // steps in flight while one is consumed
-constexpr uint32_t kRowToRun = 128; // a run that this chunk owns ends here: keep its sum for the apply phase (index in bits 8..12)
-// Per warp: ring | gradient-row list (address, descriptor, gain per entry) | table / slot row addresses of the
-// runs to apply | the sums of those runs.
+constexpr uint32_t kSegZero = 1;    // first entry of a segment: clear the sum
+constexpr uint32_t kSegIgnore = 2;  // the entry has no gradient row
+constexpr uint32_t kSegStore = 4;   // last entry of a segment: keep the sum (segment index in bits 8..12)
+// Per warp: ring | per entry: gradient row address, descriptor, gain | per run end: first segment, segment count,
+// run start | table / slot row addresses of the runs to apply | the segment sums.
 __host__ __device__ constexpr size_t group_pipe_warp_bytes(int NG, bool reduce_only) {
-  return (size_t)kGroupRingSteps * 512 + 32 * 16 + (reduce_only ? 0 : 32 * 3 * 8 + 32 * (32 / NG) * 16);
+  return (size_t)kGroupRingSteps * 512 + 32 * 16 + 34 * 4 + 8 + (reduce_only ? 0 : 32 * 3 * 8) + (32 + NG) * (32 / NG) * 16;
 }
 
 // Same contract as bwd_pipe_kernel, for rows that fill only a part of a warp (dim <= 64).  The warp's
 // 32 lanes form NG groups of 32 / NG lanes (4 groups for rows of up to 32 floats, 2 up to 64), and a
-// chunk is processed in two phases whose steps are uniform across the groups:
-//   reduce  every run of the chunk belongs to the group in whose window of 32 / NG entries it starts, so
-//           the runs are dealt to the groups in contiguous, roughly equal shares.  In step t every group
-//           streams the t-th gradient row of its share through a ring of 512-byte step slots (16 bytes
-//           per lane, kGroupAhead steps in flight) and adds it; where a run ends, its sum goes to shared
-//           memory (runs owned by the chunk), to the partial-sum scratch (runs that cross the chunk) or
-//           to the exchange buffer (reduce-only mode);
-//   apply   the runs to apply are dealt round-robin, NG per step triple: the groups stream the table row
-//           and the slot rows of their runs and all apply the optimizer in the same step.
-// One warp instruction therefore moves, sums or updates NG rows, and the long optimizer epilogue is
-// never executed for the sake of a single group.  Sums still run in entry order inside a run.
+// chunk is processed in phases whose steps are uniform across the groups:
+//   reduce   group g owns the WINDOW of entries [g * 32 / NG, (g + 1) * 32 / NG) of the chunk, whatever the
+//            runs are, so every group has the same number of steps.  In step t it streams the gradient row
+//            of its t-th entry through a ring of 512-byte step slots (16 bytes per lane, kGroupAhead steps in
+//            flight) and adds it; a SEGMENT ends where a run ends or the window ends, and its sum goes to
+//            shared memory;
+//   combine  the sum of a run is the sum of its at most NG segments, added in window order;
+//   apply    the runs that this chunk owns are dealt round-robin, NG per step triple: the groups stream the
+//            table row and the slot rows of their runs and all apply the optimizer in the same step.  Runs
+//            that cross the chunk store their sum as the chunk's partial sum; in reduce-only mode the
+//            sums go to the exchange buffer.
+// One warp instruction therefore moves, sums or updates NG rows, a hot row that fills the chunk is
+// spread over all groups, and the long optimizer epilogue is never executed for the sake of a single
+// group.  Inside a segment the sum runs in entry order; segments are added in window order.
 template <int NG, int NS, bool REDUCE, bool EXTRA>
 __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableDesc* __restrict__ tabs, int count,
                                                                    uint32_t total_chunks, float* __restrict__ partial,
                                                                    uint8_t* __restrict__ chunk_flags, int pstride) {
-  constexpr int Gc = 32 / NG;
+  static_assert(NG >= 2, "the two runs that may cross a chunk are stored by groups 0 and 1");
+  constexpr int Gc = 32 / NG;  // lanes of a group = entries of a window
   constexpr int R = kGroupRingSteps, A = kGroupAhead;
   constexpr int kRowsPerApply = 1 + NS;
+  // A lane may issue step s + A while another still reads steps s - 1 - NS .. s - 1 of the previous iteration.
   static_assert(A + 1 + NS < R, "a step being applied must not be overwritten by the copies issued ahead");
   extern __shared__ __align__(128) unsigned char pipe_smem[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
@@ -1506,7 +1581,6 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   if (gchunk >= total_chunks) return;
   const int t = warp_find_table(count, gchunk, lane, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
-  const CsrView& v = td.v;
   const int n = entry_count(td);
   const int e0 = (int)(gchunk - td.chunk_base) * 32;
   if (e0 >= n) {
@@ -1518,39 +1592,21 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   const int vec_per_row = dim >> 2;
   unsigned char* mine = pipe_smem + (size_t)wib * group_pipe_warp_bytes(NG, REDUCE);
   const uint32_t ring_base = smem_addr(mine);
-  unsigned char* list = mine + (size_t)R * 512;
-  const float** rowaddr = reinterpret_cast<const float**>(list);
-  uint32_t* rowdesc = reinterpret_cast<uint32_t*>(list + 32 * 8);
-  float* rowgain = reinterpret_cast<float*>(list + 32 * 12);
-  float** applyaddr = reinterpret_cast<float**>(list + 32 * 16);  // [run][table, slot 0, slot 1]
-  const uint32_t runs_base = smem_addr(list + 32 * 16 + 32 * 3 * 8);  // [run][Gc float4]
+  unsigned char* aux = mine + (size_t)R * 512;
+  const float** ent_addr = reinterpret_cast<const float**>(aux);           // [32]
+  uint32_t* ent_desc = reinterpret_cast<uint32_t*>(aux + 32 * 8);          // [32]
+  float* ent_gain = reinterpret_cast<float*>(aux + 32 * 12);               // [32]
+  uint32_t* item_desc = reinterpret_cast<uint32_t*>(aux + 32 * 16);        // [32] runs to apply, [2] runs that cross
+  float** applyaddr = reinterpret_cast<float**>(aux + 32 * 16 + 34 * 4 + 8);  // [run][table, slot 0, slot 1]
+  const uint32_t segs_base = smem_addr(aux + 32 * 16 + 34 * 4 + 8 + (REDUCE ? 0 : 32 * 3 * 8));  // [segment][Gc float4]
 
   const int e = e0 + lane;
-  const uint32_t my_row = entry_row(td, e, n);
+  const ChunkRows cr = load_chunk_rows(td, e0, n, lane);
+  const uint32_t my_row = cr.mine;
   uint32_t prev_row = __shfl_up_sync(0xffffffffu, my_row, 1);
-  if (lane == 0) prev_row = entry_row(td, e0 - 1, n);
-  const uint32_t next_row = entry_row(td, e0 + 32, n);  // row after the chunk
+  if (lane == 0) prev_row = cr.before;
+  const uint32_t next_row = __shfl_sync(0xffffffffu, cr.ahead, 0);  // row after the chunk
   const bool valid = my_row != kNoRow;
-  const float* my_src = nullptr;
-  float my_gain = 0.f;
-  const float* any_grad = td.grad;  // a readable address for entries without a gradient row
-  if (valid) {
-    const int q = td.indirect == 1 ? (int)(td.slots[td.range[0] + (uint32_t)e] - td.ent_base) : e;
-    if (td.pull != nullptr) {
-      const int s = q / td.pull_cap;
-      const PullSrc& src = td.pull[s];
-      const int slot = td.pull_begin[s] + (q - s * td.pull_cap);
-      const int sid = src.sids[slot];
-      my_gain = src.gains[slot];
-      any_grad = src.grad;
-      if (sid >= 0 && sid < td.pull_rows) my_src = src.grad + (int64_t)sid * dim;
-    } else {
-      const int s = v.S == 1 ? 0 : q / v.coo_per_sc;
-      const int sid = v.sids[q];
-      my_gain = v.gains[q];
-      if (sid >= 0 && sid < v.bsc) my_src = td.grad + (int64_t)(s * v.bsc + sid) * dim;
-    }
-  }
   const uint32_t lt = (1u << lane) - 1u;
   const uint32_t heads = __ballot_sync(0xffffffffu, valid && my_row != prev_row);
   const uint32_t valids = __ballot_sync(0xffffffffu, valid);
@@ -1559,105 +1615,184 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
     return;
   }
   const uint32_t starts = heads | (valids & 1u);
+  // The run of lane j starts at the highest start bit at or below j.
   const int run_start = 31 - __clz(starts & (lt | (1u << lane)));
   const bool head_run = valid && ((heads >> run_start) & 1u);
   const bool is_end = valid && (lane == 31 || (((starts | ~valids) >> (lane + 1)) & 1u));
-  const bool goes_on = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
-  const bool w_end = is_end && head_run && !goes_on;                // a run that this chunk owns ends here
+  const bool crosses = lane == 31 && valid && next_row == my_row;  // the last run continues in the next chunk
+  const ChunkBorders border = chunk_borders(cr, __shfl_sync(0xffffffffu, crosses && head_run, 31));
+  const bool goes_on = crosses && border.ext == 0;    // ... and is summed through the partial sums
+  const bool w_end = is_end && head_run && !goes_on;  // a run that this chunk owns ends here: apply the optimizer
+  const bool listed = valid && lane >= border.skip;   // the first `skip` entries are the previous chunk's
   const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
+  const uint32_t listedmask = __ballot_sync(0xffffffffu, listed);
   if (lane == 31)
     chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
-  // Deal the runs to the groups and lay the groups' shares of the gradient rows out one after the other.
-  const int grp = valid ? run_start / Gc : NG;
-  const int my_group = lane / Gc, gl = lane % Gc;
-  int my_part_base = 0, my_part_rows = 0;  // share of the group this lane CONSUMES for
-  int o = 0;                               // list position of this lane's entry
-  int max_rows = 0;
+  // Sources of this lane's entry and of the entry it describes among those taken over from the next chunk (x_*):
+  // the two chains of loads run side by side.
+  const float *my_src = nullptr, *x_src = nullptr;
+  float my_gain = 0.f, x_gain = 0.f;
+  const float* any_grad = td.grad;  // a readable address for entries without a gradient row
   {
-    int base = 0;
-#pragma unroll
-    for (int g = 0; g < NG; ++g) {
-      const uint32_t gm = __ballot_sync(0xffffffffu, grp == g);
-      const int rows = __popc(gm);
-      if (grp == g) o = base + __popc(gm & lt);
-      if (my_group == g) { my_part_base = base; my_part_rows = rows; }
-      max_rows = max(max_rows, rows);
-      base += rows;
-    }
+    const int q = listed ? entry_slot(td, e) : -1;
+    const int xq = lane < border.ext ? entry_slot(td, e + 32) : -1;
+    if (q >= 0) entry_source(td, q, dim, my_src, my_gain, any_grad);
+    if (xq >= 0) entry_source(td, xq, dim, x_src, x_gain, any_grad);
   }
-  const int apply_index = __popc(wendmask & lt);  // of the run that ends at this lane
-  // Every address of the chunk is known now: ask L2 for the rows, so that the two phases below stream from L2
-  // instead of paying the DRAM latency once per ring step.  Only for this GPU's own memory: in pull mode the
-  // gradient rows live in the peers' exchange buffers, and a prefetch of a peer address is not a hint but a
-  // slow remote access (measured: 142 ms instead of 1.6 ms for the update of 4 x 7 M entries over 4 GPUs).
+  const uint32_t crossmask = __ballot_sync(0xffffffffu, listed && is_end && !w_end);  // at most 2: first and last run
+  if (x_src != nullptr && td.pull == nullptr) prefetch_row(x_src, dim * 4);
+  // Segments: a new one starts with every run and with every window.
+  const bool seg_first = listed && (((starts >> lane) & 1u) || lane % Gc == 0);
+  const bool seg_last = listed && (is_end || lane % Gc == Gc - 1);
+  const uint32_t seglast_mask = __ballot_sync(0xffffffffu, seg_last);
+  const int seg_id = __popc(seglast_mask & lt);  // of the segment this entry belongs to
+  const int first_seg = __popc(seglast_mask & ((1u << run_start) - 1u));  // of the run this entry belongs to
+  const int my_group = lane / Gc, gl = lane % Gc;
+  const bool in_row = gl < vec_per_row;
+  const uint32_t lane_off = (uint32_t)lane * 16u;
+  const uint32_t seg_off = (uint32_t)gl * 16u;
+  // Every address of the chunk is known now: ask L2 for the rows of this GPU's own memory (a prefetch of a peer
+  // address - the gradient rows in pull mode - is not a hint but a slow remote access).
   if (my_src != nullptr && td.pull == nullptr) prefetch_row(my_src, dim * 4);
-  if (valid) {
-    rowaddr[o] = my_src != nullptr ? my_src : any_grad;
-    rowdesc[o] = kRowGrad | (((starts >> lane) & 1u) ? kRowZero : 0u) | (my_src == nullptr ? kRowIgnore : 0u) |
-                 ((is_end && !w_end) ? kRowPartial : 0u) | (head_run ? kRowHead : 0u) |
-                 ((REDUCE && w_end) ? (kRowReduce | ((uint32_t)run_start << 8)) : 0u) |
-                 ((!REDUCE && w_end) ? (kRowToRun | ((uint32_t)apply_index << 8)) : 0u);
-    rowgain[o] = my_gain;
-    if (!REDUCE && w_end) {
-      float *pw, *pa, *pb;
-      row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
-      applyaddr[apply_index * 3 + 0] = pw;
-      applyaddr[apply_index * 3 + 1] = pa;
-      applyaddr[apply_index * 3 + 2] = pb;
-      prefetch_row(pw, dim * 4);
-      if (NS >= 1) prefetch_row(pa, dim * 4);
-      if (NS >= 2) prefetch_row(pb, dim * 4);
+  if (listed) {
+    ent_addr[lane] = my_src != nullptr ? my_src : any_grad;
+    ent_desc[lane] = (seg_first ? kSegZero : 0u) | (my_src == nullptr ? kSegIgnore : 0u) | (seg_last ? kSegStore : 0u) |
+                     ((uint32_t)seg_id << 8);
+    ent_gain[lane] = my_gain;
+    if (is_end) {
+      const uint32_t item = (uint32_t)first_seg | ((uint32_t)(seg_id - first_seg + 1) << 8) | ((uint32_t)run_start << 16) |
+                            (head_run ? 1u << 24 : 0u) | ((lane == 31 && border.ext > 0) ? 1u << 25 : 0u);
+      if (w_end) {
+        const int a = __popc(wendmask & lt);
+        item_desc[a] = item;
+        if (!REDUCE) {
+          float *pw, *pa, *pb;
+          row_pointers_of(ctx, (int64_t)my_row, &pw, &pa, &pb);
+          applyaddr[a * 3 + 0] = pw;
+          applyaddr[a * 3 + 1] = pa;
+          applyaddr[a * 3 + 2] = pb;
+          prefetch_row(pw, dim * 4);
+          if (NS >= 1) prefetch_row(pa, dim * 4);
+          if (NS >= 2) prefetch_row(pb, dim * 4);
+        }
+      } else {
+        item_desc[32 + __popc(crossmask & lt)] = item;
+      }
     }
   }
   __syncwarp();
 
-  const bool in_row = gl < vec_per_row;
-  const uint32_t lane_off = (uint32_t)lane * 16u;
-  const uint32_t run_off = (uint32_t)gl * 16u;
-  // ---- phase 1: the groups reduce their runs
+  // ---- reduce: group g sums the entries of window g, one per step
   {
+    constexpr uint32_t kWindowMask = Gc == 32 ? 0xffffffffu : ((1u << Gc) - 1u);
+    const uint32_t window = (listedmask >> (my_group * Gc)) & kWindowMask;  // entries of this group's window
+    int rows = 0;  // steps until every window is done
+#pragma unroll
+    for (int g = 0; g < NG; ++g) rows = max(rows, 32 - __clz((listedmask >> (g * Gc)) & kWindowMask));
+    const int first = my_group * Gc;
+    // ... followed by the entries taken over from the next chunk: a contiguous share of `per` entries per group,
+    // summed into segment 32 + group.  Their addresses and gains come from the lanes that describe them.
+    constexpr int A1 = R - 2;  // steps in flight (only the step of the previous iteration may still be read)
+    const int per = (border.ext + NG - 1) / NG;
+    const int steps = rows + per;
+    const uint32_t x_has = __ballot_sync(0xffffffffu, x_src != nullptr);
     auto issue = [&](int step) {
-      if (step < my_part_rows && in_row)
-        cp_async16(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off,
-                   reinterpret_cast<const float4*>(rowaddr[my_part_base + step]) + gl);
+      const float* src = nullptr;
+      if (step < rows) {
+        if ((window >> step) & 1u) src = ent_addr[first + step];
+      } else if (step < steps) {  // warp-uniform
+        const int j = my_group * per + (step - rows);
+        const float* p = reinterpret_cast<const float*>(__shfl_sync(0xffffffffu, (unsigned long long)x_src, j & 31));
+        if (j < border.ext) src = p;
+      }
+      if (src != nullptr && in_row)
+        cp_async16(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off, reinterpret_cast<const float4*>(src) + gl);
       cp_async_commit();
     };
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    auto consume = [&](int step) {
-      if (step >= my_part_rows) return;
-      const int r = my_part_base + step;
-      const uint32_t d = rowdesc[r];
-      if (d & kRowZero) acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (!(d & kRowIgnore) && in_row) {
-        const float gain = rowgain[r];
-        const float4 x = lds128(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off);
-        acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
-        acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
-      }
-      if (!in_row) return;
-      if (!REDUCE && (d & kRowToRun)) {
-        const uint32_t dst = runs_base + ((d >> 8) & 31u) * (uint32_t)(Gc * 16) + run_off;
-        asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
-      }
-      if (REDUCE && (d & kRowReduce)) reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((d >> 8) & 31u)) * dim)[gl] = acc;
-      if (d & kRowPartial)
-        reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((d & kRowHead) ? 1 : 0)) * pstride)[gl] = acc;
-    };
 #pragma unroll
-    for (int a = 0; a < A; ++a) issue(a);
-    for (int step = 0; step < max_rows; ++step) {
-      issue(step + A);
-      cp_async_wait<A>();  // this lane's copies of `step` have landed
-      __syncwarp();        // ... and every other lane's
-      consume(step);
+    for (int a = 0; a < A1; ++a) issue(a);
+    for (int step = 0; step < steps; ++step) {
+      issue(step + A1);
+      cp_async_wait<A1>();  // this lane's copies of `step` have landed
+      __syncwarp();         // ... and every other lane's
+      const uint32_t slot = ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off;
+      if (step < rows) {
+        if (!((window >> step) & 1u)) continue;
+        const uint32_t d = ent_desc[first + step];
+        if (d & kSegZero) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!in_row) continue;
+        if (!(d & kSegIgnore)) {
+          const float gain = ent_gain[first + step];
+          const float4 x = lds128(slot);
+          acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
+          acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
+        }
+        if (d & kSegStore) {
+          const uint32_t dst = segs_base + ((d >> 8) & 31u) * (uint32_t)(Gc * 16) + seg_off;
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+        }
+      } else {
+        const int j = my_group * per + (step - rows);
+        const float gain = __shfl_sync(0xffffffffu, x_gain, j & 31);
+        if (step == rows) acc = make_float4(0.f, 0.f, 0.f, 0.f);  // every window has stored its last segment
+        if (j < border.ext && ((x_has >> j) & 1u) && in_row) {
+          const float4 x = lds128(slot);
+          acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
+          acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
+        }
+      }
     }
     cp_async_wait<0>();
+    if (per > 0 && in_row) {
+      const uint32_t dst = segs_base + (uint32_t)(32 + my_group) * (uint32_t)(Gc * 16) + seg_off;
+      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
+    }
   }
-  if (REDUCE) return;
+  __syncwarp();  // all segment sums are in shared memory; the ring is free again
+  // Sum of the run described by `item`: its segments in window order (this lane's vector), then the groups' shares
+  // of the entries taken over from the next chunk.
+  auto run_sum = [&](uint32_t item) {
+    const uint32_t seg0 = item & 31u, nseg = (item >> 8) & 63u;
+    float4 g = lds128(segs_base + seg0 * (uint32_t)(Gc * 16) + seg_off);
+#pragma unroll
+    for (uint32_t k = 1; k < (uint32_t)NG; ++k) {
+      if (k < nseg) {
+        const float4 x = lds128(segs_base + (seg0 + k) * (uint32_t)(Gc * 16) + seg_off);
+        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+      }
+    }
+    if (item & (1u << 25)) {
+#pragma unroll
+      for (uint32_t k = 0; k < (uint32_t)NG; ++k) {
+        const float4 x = lds128(segs_base + (32u + k) * (uint32_t)(Gc * 16) + seg_off);
+        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+      }
+    }
+    return g;
+  };
+  // ---- runs that cross the chunk (at most two): their sums are the chunk's partial sums
+  {
+    const int ncross = __popc(crossmask);
+    if (my_group < ncross && in_row) {
+      const uint32_t item = item_desc[32 + my_group];
+      const float4 g = run_sum(item);
+      reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((item >> 24) & 1u)) * pstride)[gl] = g;
+    }
+  }
   const int num_apply = __popc(wendmask);
   if (num_apply == 0) return;
-  __syncwarp();  // the sums of all runs are in shared memory; the ring is free again
-  // ---- phase 2: NG runs per step triple; step kRowsPerApply * u + k streams array k of run u * NG + group
+  if (REDUCE) {
+    // ---- reduce-only: the sums of the owned runs go to the exchange buffer, NG runs at a time
+    for (int a = my_group; a < num_apply; a += NG) {
+      if (!in_row) continue;
+      const uint32_t item = item_desc[a];
+      const float4 g = run_sum(item);
+      reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((item >> 16) & 31u)) * dim)[gl] = g;
+    }
+    return;
+  }
+  // ---- apply: NG runs per step triple; step kRowsPerApply * u + k streams array k of run u * NG + group
   {
     const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
     const int steps = ((num_apply + NG - 1) / NG) * kRowsPerApply;
@@ -1680,7 +1815,7 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
       float4 w = lds128(ring_base + (uint32_t)((step - NS) & (R - 1)) * 512u + lane_off);
       float4 x0 = NS >= 1 ? lds128(ring_base + (uint32_t)((step - NS + 1) & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
       float4 x1 = NS >= 2 ? lds128(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 g = lds128(runs_base + (uint32_t)a * (uint32_t)(Gc * 16) + run_off);
+      const float4 g = run_sum(item_desc[a]);
       float* wf = reinterpret_cast<float*>(&w);
       float* af = reinterpret_cast<float*>(&x0);
       float* bf = reinterpret_cast<float*>(&x1);
@@ -1746,21 +1881,16 @@ __global__ void __launch_bounds__(kBlock) bwd_group_kernel(const TableDesc* __re
   }
 }
 
-// Warp per chunk that is flagged kChunkHeadContinues: adds the partial sums of the run that
+// For a chunk that is flagged kChunkHeadContinues: adds the partial sums of the run that
 // starts in this chunk and goes on through the following ones -- chunk by chunk up to the next
 // group boundary, then whole flagged groups, then chunk by chunk to the run's end -- and
-// applies the optimizer once.
+// applies the optimizer once.  Executed by a whole warp.
 template <int W, int K, bool EXTRA>
-__global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
-                                                           const float* __restrict__ partial,
-                                                           const uint8_t* __restrict__ chunk_flags,
-                                                           const float* __restrict__ group_partial,
-                                                           const uint8_t* __restrict__ group_flags, int pstride) {
+__device__ __forceinline__ void fixup_chunk(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
+                                            const float* __restrict__ partial, const uint8_t* __restrict__ chunk_flags,
+                                            const float* __restrict__ group_partial, const uint8_t* __restrict__ group_flags,
+                                            int pstride, uint32_t gchunk, int lane) {
   using VT = typename Vec<W>::T;
-  const int lane = threadIdx.x & 31;
-  const uint32_t gchunk = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (gchunk >= total_chunks) return;
-  if (!(chunk_flags[gchunk] & kChunkHeadContinues)) return;
   const int t = warp_find_table(count, gchunk, lane, [&](int i) { return tabs[i].chunk_base; });
   const TableDesc& td = tabs[t];
   // The flag says that entry 31 of the chunk exists and holds a valid row.
@@ -1863,6 +1993,28 @@ __global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const
     store_row<W, K, EXTRA>(ctx, (int64_t)row, lane, acc, w, x0, x1);
   }
 }
+
+// Flagged chunks are few once short crossing runs are handled by the chunk that holds their head: a warp looks at
+// kFixupSpan consecutive flags and fixes up the flagged chunks one after the other.
+constexpr int kFixupSpan = 8;
+template <int W, int K, bool EXTRA>
+__global__ void __launch_bounds__(kBlock, K <= 2 ? 4 : 1) bwd_fixup_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t total_chunks,
+                                                           const float* __restrict__ partial,
+                                                           const uint8_t* __restrict__ chunk_flags,
+                                                           const float* __restrict__ group_partial,
+                                                           const uint8_t* __restrict__ group_flags, int pstride) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t c0 = (blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5)) * (uint32_t)kFixupSpan;
+  if (c0 >= total_chunks) return;
+  const uint32_t c = c0 + lane;
+  uint32_t todo = __ballot_sync(0xffffffffu, lane < kFixupSpan && c < total_chunks && (chunk_flags[c] & kChunkHeadContinues));
+  while (todo != 0) {
+    const uint32_t i = (uint32_t)__ffs(todo) - 1u;
+    todo &= todo - 1u;
+    fixup_chunk<W, K, EXTRA>(tabs, count, total_chunks, partial, chunk_flags, group_partial, group_flags, pstride, c0 + i, lane);
+  }
+}
+
 
 // Entry index space of all indirect tables -> sort key (row_base + global row; `invalid` for
 // indices that hold no entry).  Virtual-device tables: entry index = slot of the concatenated
@@ -2272,7 +2424,7 @@ int launch_fixup(const TableDesc* tabs, int count, uint32_t total_chunks, const 
   bwd_group_kernel<W, K32><<<(unsigned)ceil_div(groups, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, total_chunks, u.partial,
                                                                                         u.flags, u.group_partial, u.group_flags, u.pstride);
   SC_LAUNCH_OK("bwd_group_kernel");
-  const unsigned blocks = (unsigned)ceil_div(total_chunks, kWarpsPerBlock);
+  const unsigned blocks = (unsigned)ceil_div(ceil_div(total_chunks, kFixupSpan), kWarpsPerBlock);
   if (extra)
     bwd_fixup_kernel<W, K32, true><<<blocks, kBlock, 0, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.group_partial,
                                                              u.group_flags, u.pstride);
