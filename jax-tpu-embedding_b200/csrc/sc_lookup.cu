@@ -496,19 +496,20 @@ struct RowMeta {
 #endif
 template <int W, int K, int G>
 __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : K <= 2 ? 4 : 3) fwd_gather_kernel(const TableDesc* __restrict__ tabs, int count, uint32_t first_act,
-    uint32_t total_act) {
+    uint32_t total_act, int rows_per_warp) {
   using VT = typename Vec<W>::T;
   constexpr int NG = 32 / G;
   constexpr int U = K >= 4 ? 2 : SC_GATHER_ROWS_SHORT / K;  // table rows held in registers per group
   __shared__ RowMeta s_meta[kWarpsPerBlock][32];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const uint32_t r0 = first_act + (blockIdx.x * kWarpsPerBlock + wib) * 32u;  // rows [first_act, total_act) of `tabs`
+  // Rows [first_act, total_act) of `tabs`, rows_per_warp (a multiple of 32 / G, at most 32) to a warp.
+  const uint32_t r0 = first_act + (blockIdx.x * kWarpsPerBlock + wib) * (uint32_t)rows_per_warp;
   if (r0 >= total_act) return;
   {
     RowMeta m;
     m.src = nullptr; m.begin = m.end = 0; m.table = 0; m.gain = 0.f;
     const uint32_t my_r = r0 + lane;
-    if (my_r < total_act) {
+    if (lane < rows_per_warp && my_r < total_act) {
       m.table = find_table(count, my_r, [&](int i) { return tabs[i].act_base; });
       const TableDesc& td = tabs[m.table];
       const uint2 bag = reinterpret_cast<const uint2*>(td.bags)[my_r - td.act_base];
@@ -524,7 +525,7 @@ __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : K <= 2 ? 4 : 3) fwd_gathe
   __syncwarp();
   const int group = lane / G, gl = lane % G;
   const unsigned gmask = G == 32 ? 0xffffffffu : (((1u << G) - 1u) << (group * G));
-  const int rows_here = (int)min(32u, total_act - r0);
+  const int rows_here = (int)min((uint32_t)rows_per_warp, total_act - r0);
   int cached_t = -1, dim = 0, vec_per_row = 0;
   float* act = nullptr;
   uint32_t act_base = 0;
@@ -1537,44 +1538,41 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
   cp_async_wait<0>();
 }
 
-// ---- the same pipeline for rows of at most 64 floats: several rows per warp instruction
-constexpr int kGroupRingSteps = 8;  // step slots of 512 bytes in a warp's ring
-constexpr int kGroupAhead = 4;      // steps in flight while one is consumed
-constexpr uint32_t kSegZero = 1;    // first entry of a segment: clear the sum
-constexpr uint32_t kSegIgnore = 2;  // the entry has no gradient row
-constexpr uint32_t kSegStore = 4;   // last entry of a segment: keep the sum (segment index in bits 8..12)
-// Per warp: ring | per entry: gradient row address, descriptor, gain | per run end: first segment, segment count,
-// run start | table / slot row addresses of the runs to apply | the segment sums.
-__host__ __device__ constexpr size_t group_pipe_warp_bytes(int NG, bool reduce_only) {
-  return (size_t)kGroupRingSteps * 512 + 32 * 16 + 34 * 4 + 8 + (reduce_only ? 0 : 32 * 3 * 8) + (32 + NG) * (32 / NG) * 16;
+// ---- rows of at most 128 floats: lane groups, several rows per warp instruction, rows through registers
+constexpr int kGroupWindow = 8;  // entries of a window = gradient rows a lane holds in registers at a time
+// Per warp: per entry the gradient row address and the gain | per run end a descriptor | table / slot row addresses
+// of the runs to apply | segment sums: one round's segments, the carry, the groups' shares of taken-over entries.
+__host__ __device__ constexpr size_t lane_groups_warp_bytes(int NG, int ROUNDS, bool reduce_only) {
+  return 32 * 12 + 34 * 4 + 8 + (reduce_only ? 0 : 32 * 3 * 8) + (size_t)(32 / ROUNDS + 1 + NG) * (32 / NG) * 16;
 }
 
-// Same contract as bwd_pipe_kernel, for rows that fill only a part of a warp (dim <= 64).  The warp's
-// 32 lanes form NG groups of 32 / NG lanes (4 groups for rows of up to 32 floats, 2 up to 64), and a
-// chunk is processed in phases whose steps are uniform across the groups:
-//   reduce   group g owns the WINDOW of entries [g * 32 / NG, (g + 1) * 32 / NG) of the chunk, whatever the
-//            runs are, so every group has the same number of steps.  In step t it streams the gradient row
-//            of its t-th entry through a ring of 512-byte step slots (16 bytes per lane, kGroupAhead steps in
-//            flight) and adds it; a SEGMENT ends where a run ends or the window ends, and its sum goes to
-//            shared memory;
-//   combine  the sum of a run is the sum of its at most NG segments, added in window order;
-//   apply    the runs that this chunk owns are dealt round-robin, NG per step triple: the groups stream the
-//            table row and the slot rows of their runs and all apply the optimizer in the same step.  Runs
-//            that cross the chunk store their sum as the chunk's partial sum; in reduce-only mode the
-//            sums go to the exchange buffer.
-// One warp instruction therefore moves, sums or updates NG rows, a hot row that fills the chunk is
-// spread over all groups, and the long optimizer epilogue is never executed for the sake of a single
-// group.  Inside a segment the sum runs in entry order; segments are added in window order.
-template <int NG, int NS, bool REDUCE, bool EXTRA>
-__global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableDesc* __restrict__ tabs, int count,
-                                                                   uint32_t total_chunks, float* __restrict__ partial,
-                                                                   uint8_t* __restrict__ chunk_flags, int pstride) {
-  static_assert(NG >= 2, "the two runs that may cross a chunk are stored by groups 0 and 1");
-  constexpr int Gc = 32 / NG;  // lanes of a group = entries of a window
-  constexpr int R = kGroupRingSteps, A = kGroupAhead;
-  constexpr int kRowsPerApply = 1 + NS;
-  // A lane may issue step s + A while another still reads steps s - 1 - NS .. s - 1 of the previous iteration.
-  static_assert(A + 1 + NS < R, "a step being applied must not be overwritten by the copies issued ahead");
+__device__ __forceinline__ float4 ld_row16(const float4* p) { return *p; }
+__device__ __forceinline__ uint32_t lanes_below(int j) { return j >= 32 ? 0xffffffffu : (1u << j) - 1u; }
+
+// Same contract as bwd_pipe_kernel, for rows of at most 128 / NG floats.  The warp's 32 lanes form NG groups of
+// 32 / NG lanes (one float4 per lane and row), so one warp instruction moves, sums or updates NG rows.  A chunk is
+// processed in ROUNDS rounds of 32 / ROUNDS entries; a round has phases whose steps are uniform across the groups:
+//   reduce   group g owns the WINDOW of kGroupWindow entries [g * 8, g * 8 + 8) of the round, whatever the runs
+//            are: it loads the window's gradient rows into registers and adds them up; a SEGMENT ends where a run
+//            ends or the window ends, and its sum goes to shared memory.  (The entries taken over from the next
+//            chunk are split evenly among the groups in the last round.)
+//   combine  the sum of a run is the carry (the run's segments of earlier rounds), its at most NG segments of the
+//            round in window order, and the groups' shares of the taken-over entries;
+//   apply    the runs that the chunk owns and that end in the round are dealt round-robin to the groups, which load
+//            the table row and the slot rows, apply the optimizer and store.  Runs that cross the chunk store their
+//            sum as the chunk's partial sum; in reduce-only mode the sums go to the exchange buffer.
+// A hot row that fills the chunk is spread over all groups, nothing waits in a ring, and a warp needs about 6 KiB of
+// shared memory and at most 64 registers per thread, so that half of the SM's warp slots are filled and hide the
+// latency of a chunk's dependent metadata loads.  Inside a segment the sum runs in entry order.
+template <int NG, int ROUNDS, int NS, bool REDUCE, bool EXTRA>
+__global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const TableDesc* __restrict__ tabs, int count,
+                                                                       uint32_t total_chunks, float* __restrict__ partial,
+                                                                       uint8_t* __restrict__ chunk_flags, int pstride) {
+  constexpr int Gc = 32 / NG;     // lanes of a group
+  constexpr int S = 32 / ROUNDS;  // entries of a round
+  constexpr int Wd = S / NG;      // entries of a window
+  static_assert(Wd == kGroupWindow, "a window is one batch of register loads");
+  constexpr int kCarry = S, kTaken = S + 1;  // segment slots after the round's own
   extern __shared__ __align__(128) unsigned char pipe_smem[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t gchunk = blockIdx.x * kPipeWarps + wib;
@@ -1590,15 +1588,12 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   const RowCtx ctx = make_ctx(td);
   const int dim = ctx.dim;
   const int vec_per_row = dim >> 2;
-  unsigned char* mine = pipe_smem + (size_t)wib * group_pipe_warp_bytes(NG, REDUCE);
-  const uint32_t ring_base = smem_addr(mine);
-  unsigned char* aux = mine + (size_t)R * 512;
-  const float** ent_addr = reinterpret_cast<const float**>(aux);           // [32]
-  uint32_t* ent_desc = reinterpret_cast<uint32_t*>(aux + 32 * 8);          // [32]
-  float* ent_gain = reinterpret_cast<float*>(aux + 32 * 12);               // [32]
-  uint32_t* item_desc = reinterpret_cast<uint32_t*>(aux + 32 * 16);        // [32] runs to apply, [2] runs that cross
-  float** applyaddr = reinterpret_cast<float**>(aux + 32 * 16 + 34 * 4 + 8);  // [run][table, slot 0, slot 1]
-  const uint32_t segs_base = smem_addr(aux + 32 * 16 + 34 * 4 + 8 + (REDUCE ? 0 : 32 * 3 * 8));  // [segment][Gc float4]
+  unsigned char* aux = pipe_smem + (size_t)wib * lane_groups_warp_bytes(NG, ROUNDS, REDUCE);
+  const float** ent_addr = reinterpret_cast<const float**>(aux);              // [32]
+  float* ent_gain = reinterpret_cast<float*>(aux + 32 * 8);                   // [32]
+  uint32_t* item_desc = reinterpret_cast<uint32_t*>(aux + 32 * 12);           // [32] runs to apply, [2] runs that cross
+  float** applyaddr = reinterpret_cast<float**>(aux + 32 * 12 + 34 * 4 + 8);  // [run][table, slot 0, slot 1]
+  const uint32_t segs_base = smem_addr(aux + 32 * 12 + 34 * 4 + 8 + (REDUCE ? 0 : 32 * 3 * 8));  // [slot][Gc float4]
 
   const int e = e0 + lane;
   const ChunkRows cr = load_chunk_rows(td, e0, n, lane);
@@ -1626,6 +1621,8 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   const bool listed = valid && lane >= border.skip;   // the first `skip` entries are the previous chunk's
   const uint32_t wendmask = __ballot_sync(0xffffffffu, w_end);
   const uint32_t listedmask = __ballot_sync(0xffffffffu, listed);
+  const uint32_t endmask = __ballot_sync(0xffffffffu, listed && is_end);
+  const uint32_t crossmask = endmask & ~wendmask;  // runs that cross the chunk, at most 2: the first and the last
   if (lane == 31)
     chunk_flags[gchunk] = goes_on ? (head_run ? kChunkHeadContinues : (run_start == 0 ? kChunkAllContinues : 0)) : 0;
   // Sources of this lane's entry and of the entry it describes among those taken over from the next chunk (x_*):
@@ -1639,29 +1636,27 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
     if (q >= 0) entry_source(td, q, dim, my_src, my_gain, any_grad);
     if (xq >= 0) entry_source(td, xq, dim, x_src, x_gain, any_grad);
   }
-  const uint32_t crossmask = __ballot_sync(0xffffffffu, listed && is_end && !w_end);  // at most 2: first and last run
-  if (x_src != nullptr && td.pull == nullptr) prefetch_row(x_src, dim * 4);
-  // Segments: a new one starts with every run and with every window.
-  const bool seg_first = listed && (((starts >> lane) & 1u) || lane % Gc == 0);
-  const bool seg_last = listed && (is_end || lane % Gc == Gc - 1);
-  const uint32_t seglast_mask = __ballot_sync(0xffffffffu, seg_last);
-  const int seg_id = __popc(seglast_mask & lt);  // of the segment this entry belongs to
-  const int first_seg = __popc(seglast_mask & ((1u << run_start) - 1u));  // of the run this entry belongs to
-  const int my_group = lane / Gc, gl = lane % Gc;
-  const bool in_row = gl < vec_per_row;
-  const uint32_t lane_off = (uint32_t)lane * 16u;
-  const uint32_t seg_off = (uint32_t)gl * 16u;
   // Every address of the chunk is known now: ask L2 for the rows of this GPU's own memory (a prefetch of a peer
   // address - the gradient rows in pull mode - is not a hint but a slow remote access).
-  if (my_src != nullptr && td.pull == nullptr) prefetch_row(my_src, dim * 4);
+  if (td.pull == nullptr) {
+    if (my_src != nullptr) prefetch_row(my_src, dim * 4);
+    if (x_src != nullptr) prefetch_row(x_src, dim * 4);
+  }
+  // Segments: a new one starts with every run and with every window.
+  const uint32_t segfirst_mask = __ballot_sync(0xffffffffu, listed && (((starts >> lane) & 1u) || lane % Wd == 0));
+  const uint32_t seglast_mask = __ballot_sync(0xffffffffu, listed && (is_end || lane % Wd == Wd - 1));
+  const uint32_t src_mask = __ballot_sync(0xffffffffu, listed && my_src != nullptr);
+  const int my_group = lane / Gc, gl = lane % Gc;
+  const bool in_row = gl < vec_per_row;
+  const uint32_t seg_off = (uint32_t)gl * 16u;
   if (listed) {
     ent_addr[lane] = my_src != nullptr ? my_src : any_grad;
-    ent_desc[lane] = (seg_first ? kSegZero : 0u) | (my_src == nullptr ? kSegIgnore : 0u) | (seg_last ? kSegStore : 0u) |
-                     ((uint32_t)seg_id << 8);
     ent_gain[lane] = my_gain;
     if (is_end) {
-      const uint32_t item = (uint32_t)first_seg | ((uint32_t)(seg_id - first_seg + 1) << 8) | ((uint32_t)run_start << 16) |
-                            (head_run ? 1u << 24 : 0u) | ((lane == 31 && border.ext > 0) ? 1u << 25 : 0u);
+      // First and last segment of the run (numbered over the chunk), its first entry, and what to do with the sum.
+      const uint32_t item = (uint32_t)__popc(seglast_mask & ((1u << run_start) - 1u)) | ((uint32_t)__popc(seglast_mask & lt) << 8) |
+                            ((uint32_t)run_start << 16) | (head_run ? 1u << 24 : 0u) |
+                            ((lane == 31 && border.ext > 0) ? 1u << 25 : 0u) | ((uint32_t)lane << 26);
       if (w_end) {
         const int a = __popc(wendmask & lt);
         item_desc[a] = item;
@@ -1682,151 +1677,155 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_group_pipe_kernel(const TableD
   }
   __syncwarp();
 
-  // ---- reduce: group g sums the entries of window g, one per step
-  {
-    constexpr uint32_t kWindowMask = Gc == 32 ? 0xffffffffu : ((1u << Gc) - 1u);
-    const uint32_t window = (listedmask >> (my_group * Gc)) & kWindowMask;  // entries of this group's window
-    int rows = 0;  // steps until every window is done
-#pragma unroll
-    for (int g = 0; g < NG; ++g) rows = max(rows, 32 - __clz((listedmask >> (g * Gc)) & kWindowMask));
-    const int first = my_group * Gc;
-    // ... followed by the entries taken over from the next chunk: a contiguous share of `per` entries per group,
-    // summed into segment 32 + group.  Their addresses and gains come from the lanes that describe them.
-    constexpr int A1 = R - 2;  // steps in flight (only the step of the previous iteration may still be read)
-    const int per = (border.ext + NG - 1) / NG;
-    const int steps = rows + per;
-    const uint32_t x_has = __ballot_sync(0xffffffffu, x_src != nullptr);
-    auto issue = [&](int step) {
-      const float* src = nullptr;
-      if (step < rows) {
-        if ((window >> step) & 1u) src = ent_addr[first + step];
-      } else if (step < steps) {  // warp-uniform
-        const int j = my_group * per + (step - rows);
-        const float* p = reinterpret_cast<const float*>(__shfl_sync(0xffffffffu, (unsigned long long)x_src, j & 31));
-        if (j < border.ext) src = p;
-      }
-      if (src != nullptr && in_row)
-        cp_async16(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off, reinterpret_cast<const float4*>(src) + gl);
-      cp_async_commit();
-    };
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int a = 0; a < A1; ++a) issue(a);
-    for (int step = 0; step < steps; ++step) {
-      issue(step + A1);
-      cp_async_wait<A1>();  // this lane's copies of `step` have landed
-      __syncwarp();         // ... and every other lane's
-      const uint32_t slot = ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off;
-      if (step < rows) {
-        if (!((window >> step) & 1u)) continue;
-        const uint32_t d = ent_desc[first + step];
-        if (d & kSegZero) acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (!in_row) continue;
-        if (!(d & kSegIgnore)) {
-          const float gain = ent_gain[first + step];
-          const float4 x = lds128(slot);
-          acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
-          acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
-        }
-        if (d & kSegStore) {
-          const uint32_t dst = segs_base + ((d >> 8) & 31u) * (uint32_t)(Gc * 16) + seg_off;
-          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
-        }
-      } else {
-        const int j = my_group * per + (step - rows);
-        const float gain = __shfl_sync(0xffffffffu, x_gain, j & 31);
-        if (step == rows) acc = make_float4(0.f, 0.f, 0.f, 0.f);  // every window has stored its last segment
-        if (j < border.ext && ((x_has >> j) & 1u) && in_row) {
-          const float4 x = lds128(slot);
-          acc.x = fast_axpy(acc.x, gain, x.x); acc.y = fast_axpy(acc.y, gain, x.y);
-          acc.z = fast_axpy(acc.z, gain, x.z); acc.w = fast_axpy(acc.w, gain, x.w);
-        }
-      }
-    }
-    cp_async_wait<0>();
-    if (per > 0 && in_row) {
-      const uint32_t dst = segs_base + (uint32_t)(32 + my_group) * (uint32_t)(Gc * 16) + seg_off;
-      asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
-    }
-  }
-  __syncwarp();  // all segment sums are in shared memory; the ring is free again
-  // Sum of the run described by `item`: its segments in window order (this lane's vector), then the groups' shares
-  // of the entries taken over from the next chunk.
-  auto run_sum = [&](uint32_t item) {
-    const uint32_t seg0 = item & 31u, nseg = (item >> 8) & 63u;
-    float4 g = lds128(segs_base + seg0 * (uint32_t)(Gc * 16) + seg_off);
-#pragma unroll
-    for (uint32_t k = 1; k < (uint32_t)NG; ++k) {
-      if (k < nseg) {
-        const float4 x = lds128(segs_base + (seg0 + k) * (uint32_t)(Gc * 16) + seg_off);
-        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
-      }
-    }
-    if (item & (1u << 25)) {
-#pragma unroll
-      for (uint32_t k = 0; k < (uint32_t)NG; ++k) {
-        const float4 x = lds128(segs_base + (32u + k) * (uint32_t)(Gc * 16) + seg_off);
-        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
-      }
-    }
-    return g;
+  auto store_slot = [&](int slot, const float4& acc) {
+    const uint32_t dst = segs_base + (uint32_t)slot * (uint32_t)(Gc * 16) + seg_off;
+    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(acc.x), "f"(acc.y), "f"(acc.z), "f"(acc.w) : "memory");
   };
-  // ---- runs that cross the chunk (at most two): their sums are the chunk's partial sums
-  {
-    const int ncross = __popc(crossmask);
-    if (my_group < ncross && in_row) {
-      const uint32_t item = item_desc[32 + my_group];
-      const float4 g = run_sum(item);
-      reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((item >> 24) & 1u)) * pstride)[gl] = g;
+  auto load_slot = [&](int slot) { return lds128(segs_base + (uint32_t)slot * (uint32_t)(Gc * 16) + seg_off); };
+  const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
+  const int ncross = __popc(crossmask);
+
+#pragma unroll
+  for (int h = 0; h < ROUNDS; ++h) {
+    const int lane0 = h * S;                                         // first entry of the round
+    const int segbase = __popc(seglast_mask & lanes_below(lane0));   // segments of earlier rounds
+    if (h > 0 && (listedmask >> lane0) == 0) break;                  // no entries left
+    // ---- reduce: this lane's vector of the window's gradient rows, summed segment by segment
+    {
+      const int first = lane0 + my_group * Wd;
+      float4 x[Wd];
+#pragma unroll
+      for (int u = 0; u < Wd; ++u) {
+        x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (((src_mask >> (first + u)) & 1u) && in_row) x[u] = ld_row16(reinterpret_cast<const float4*>(ent_addr[first + u]) + gl);
+      }
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < Wd; ++u) {
+        const int j = first + u;
+        if (!((listedmask >> j) & 1u)) continue;
+        if ((segfirst_mask >> j) & 1u) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((src_mask >> j) & 1u) {  // (the gain of an entry without a gradient row may be anything)
+          const float gain = ent_gain[j];
+          acc.x = fast_axpy(acc.x, gain, x[u].x); acc.y = fast_axpy(acc.y, gain, x[u].y);
+          acc.z = fast_axpy(acc.z, gain, x[u].z); acc.w = fast_axpy(acc.w, gain, x[u].w);
+        }
+        if (((seglast_mask >> j) & 1u) && in_row) store_slot(__popc(seglast_mask & lanes_below(j)) - segbase, acc);
+      }
     }
-  }
-  const int num_apply = __popc(wendmask);
-  if (num_apply == 0) return;
-  if (REDUCE) {
-    // ---- reduce-only: the sums of the owned runs go to the exchange buffer, NG runs at a time
-    for (int a = my_group; a < num_apply; a += NG) {
-      if (!in_row) continue;
-      const uint32_t item = item_desc[a];
-      const float4 g = run_sum(item);
-      reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((item >> 16) & 31u)) * dim)[gl] = g;
+    // ---- the entries taken over from the next chunk (they continue the chunk's last run): a contiguous share per group
+    if (h == ROUNDS - 1 && border.ext > 0) {
+      const int per = (border.ext + NG - 1) / NG;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int i = 0; i < per; i += 2) {
+        float4 x[2];
+        float gain[2];
+        bool on[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int j = my_group * per + i + u;
+          const float* src = reinterpret_cast<const float*>(__shfl_sync(0xffffffffu, (unsigned long long)x_src, j & 31));
+          gain[u] = __shfl_sync(0xffffffffu, x_gain, j & 31);
+          on[u] = i + u < per && j < border.ext && src != nullptr && in_row;
+          x[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (on[u]) x[u] = ld_row16(reinterpret_cast<const float4*>(src) + gl);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!on[u]) continue;
+          acc.x = fast_axpy(acc.x, gain[u], x[u].x); acc.y = fast_axpy(acc.y, gain[u], x[u].y);
+          acc.z = fast_axpy(acc.z, gain[u], x[u].z); acc.w = fast_axpy(acc.w, gain[u], x[u].w);
+        }
+      }
+      if (in_row) store_slot(kTaken + my_group, acc);
     }
-    return;
-  }
-  // ---- apply: NG runs per step triple; step kRowsPerApply * u + k streams array k of run u * NG + group
-  {
-    const bool clipped = !isnan(ctx.o.lo) || !isnan(ctx.o.hi);
-    const int steps = ((num_apply + NG - 1) / NG) * kRowsPerApply;
-    auto issue = [&](int step) {
-      const int a = (step / kRowsPerApply) * NG + my_group;
-      if (step < steps && a < num_apply && in_row)
-        cp_async16(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off,
-                   reinterpret_cast<const float4*>(applyaddr[a * 3 + step % kRowsPerApply]) + gl);
-      cp_async_commit();
+    __syncwarp();  // the round's segment sums are in shared memory
+    // Sum of a run whose segments up to `last` lie in this round or earlier ones (this lane's vector).
+    auto run_sum = [&](int first, int last, bool taken) {
+      float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (ROUNDS > 1 && first < segbase) {
+        g = load_slot(kCarry);
+        first = segbase;
+      }
+#pragma unroll
+      for (int k = 0; k < NG; ++k) {
+        if (first + k <= last) {
+          const float4 x = load_slot(first + k - segbase);
+          g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+        }
+      }
+      if (taken) {
+#pragma unroll
+        for (int k = 0; k < NG; ++k) {
+          const float4 x = load_slot(kTaken + k);
+          g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+        }
+      }
+      return g;
     };
-#pragma unroll
-    for (int a = 0; a < A; ++a) issue(a);
-    for (int step = 0; step < steps; ++step) {
-      issue(step + A);
-      cp_async_wait<A>();
-      __syncwarp();
-      if (step % kRowsPerApply != NS) continue;  // the run's last array has landed: apply
-      const int a = (step / kRowsPerApply) * NG + my_group;
-      if (a >= num_apply || !in_row) continue;
-      float4 w = lds128(ring_base + (uint32_t)((step - NS) & (R - 1)) * 512u + lane_off);
-      float4 x0 = NS >= 1 ? lds128(ring_base + (uint32_t)((step - NS + 1) & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
-      float4 x1 = NS >= 2 ? lds128(ring_base + (uint32_t)(step & (R - 1)) * 512u + lane_off) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 g = run_sum(item_desc[a]);
-      float* wf = reinterpret_cast<float*>(&w);
-      float* af = reinterpret_cast<float*>(&x0);
-      float* bf = reinterpret_cast<float*>(&x1);
-      const float* gf = reinterpret_cast<const float*>(&g);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast<NS, EXTRA>(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
-      reinterpret_cast<float4*>(applyaddr[a * 3 + 0])[gl] = w;
-      if (NS >= 1) reinterpret_cast<float4*>(applyaddr[a * 3 + 1])[gl] = x0;
-      if (NS >= 2) reinterpret_cast<float4*>(applyaddr[a * 3 + 2])[gl] = x1;
+    auto item_sum = [&](uint32_t item) { return run_sum((int)(item & 31u), (int)((item >> 8) & 31u), (item >> 25) & 1u); };
+    // ---- runs that cross the chunk and end in this round: their sums are the chunk's partial sums
+    for (int k = 0; k < ncross; ++k) {
+      const uint32_t item = item_desc[32 + k];
+      const int end_lane = (int)(item >> 26);
+      if (end_lane >= lane0 && end_lane < lane0 + S && my_group == k % NG && in_row)
+        reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((item >> 24) & 1u)) * pstride)[gl] = item_sum(item);
     }
-    cp_async_wait<0>();
+    // ---- the owned runs that end in this round
+    const int a_begin = __popc(wendmask & lanes_below(lane0)), a_end = __popc(wendmask & lanes_below(lane0 + S));
+    if (REDUCE) {
+      // reduce-only: the sums go to the exchange buffer
+      for (int a = a_begin + my_group; a < a_end; a += NG) {
+        if (!in_row) break;
+        const uint32_t item = item_desc[a];
+        reinterpret_cast<float4*>(td.red + (int64_t)(e0 + (int)((item >> 16) & 31u)) * dim)[gl] = item_sum(item);
+      }
+    } else {
+      // dealt round-robin to the groups, two runs in registers at a time
+      for (int a0 = a_begin + my_group; a0 < a_end; a0 += 2 * NG) {
+        if (!in_row) break;
+        float4 w[2], x0[2], x1[2];
+        bool on[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int a = a0 + u * NG;
+          on[u] = a < a_end;
+          w[u] = x0[u] = x1[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (on[u]) {
+            w[u] = reinterpret_cast<const float4*>(applyaddr[a * 3 + 0])[gl];
+            if (NS >= 1) x0[u] = reinterpret_cast<const float4*>(applyaddr[a * 3 + 1])[gl];
+            if (NS >= 2) x1[u] = reinterpret_cast<const float4*>(applyaddr[a * 3 + 2])[gl];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int a = a0 + u * NG;
+          if (!on[u]) continue;
+          const float4 g = item_sum(item_desc[a]);
+          float* wf = reinterpret_cast<float*>(&w[u]);
+          float* af = reinterpret_cast<float*>(&x0[u]);
+          float* bf = reinterpret_cast<float*>(&x1[u]);
+          const float* gf = reinterpret_cast<const float*>(&g);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) wf[i] = apply_opt_fast<NS, EXTRA>(ctx.o, clipped, wf[i], gf[i], af[i], bf[i]);
+          reinterpret_cast<float4*>(applyaddr[a * 3 + 0])[gl] = w[u];
+          if (NS >= 1) reinterpret_cast<float4*>(applyaddr[a * 3 + 1])[gl] = x0[u];
+          if (NS >= 2) reinterpret_cast<float4*>(applyaddr[a * 3 + 2])[gl] = x1[u];
+        }
+      }
+    }
+    if (h + 1 < ROUNDS) {
+      // ---- a run that goes on in the next round: its sum so far becomes the carry
+      __syncwarp();  // every group has read the old carry and the round's segments
+      const int jl = lane0 + S - 1;
+      if (((listedmask >> jl) & 1u) && !((endmask >> jl) & 1u)) {  // warp-uniform
+        const int rs = __shfl_sync(0xffffffffu, run_start, jl);
+        const float4 g = run_sum(__popc(seglast_mask & lanes_below(rs)), __popc(seglast_mask & lanes_below(jl)), false);
+        __syncwarp();
+        if (my_group == 0 && in_row) store_slot(kCarry, g);
+      }
+      __syncwarp();  // the next round overwrites the segment slots
+    }
   }
 }
 
@@ -2400,10 +2399,26 @@ int launch_fwd_single(const TableDesc* tabs, int count, uint32_t first_act, uint
   return SC_OK;
 }
 
+// Activation rows per warp of the multi-hot gather.  A warp works through its rows 32 / G at a time and every step
+// waits for dependent loads, so a launch too small to fill the SMs is split into more and shorter warps: the largest
+// of 32, 16, 8, ... 32 / G rows that gives every SM at least 16 warps.  Launches that fill the GPU keep 32 rows (the
+// first entries of 32 bags are then resolved side by side): on 8 tables x 16384 bags of ~20 ids, dim 64, 32 and 16
+// rows per warp took 0.114 ms, 8 rows 0.121 ms, 4 rows 0.136 ms; on 16384 bags of one 1e8-row table, dim 128, 4 rows
+// per warp took 0.052 ms instead of 0.097 ms.  SC_FWD_ROWS_PER_WARP overrides the choice.
+inline int gather_rows_per_warp(uint32_t rows, int groups) {
+  static const int forced = [] { const char* e = getenv("SC_FWD_ROWS_PER_WARP"); return e ? atoi(e) : 0; }();
+  if (forced >= groups && forced <= 32 && forced % groups == 0) return forced;
+  const uint64_t want = (uint64_t)sm_count() * 16;  // warps
+  int r = 32;
+  while (r > groups && ceil_div(rows, r) < (int64_t)want) r /= 2;
+  return r;
+}
+
 template <int W, int K, int G>
 int launch_fwd(const TableDesc* tabs, int count, uint32_t first_act, uint32_t end_act, cudaStream_t st) {
-  const unsigned warps = (unsigned)ceil_div(end_act - first_act, 32);
-  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, first_act, end_act);
+  const int rows_per_warp = gather_rows_per_warp(end_act - first_act, 32 / G);
+  const unsigned warps = (unsigned)ceil_div(end_act - first_act, rows_per_warp);
+  fwd_gather_kernel<W, K, G><<<(unsigned)ceil_div(warps, kWarpsPerBlock), kBlock, 0, st>>>(tabs, count, first_act, end_act, rows_per_warp);
   SC_LAUNCH_OK("fwd_gather_kernel");
   return SC_OK;
 }
@@ -2462,43 +2477,51 @@ int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, con
   return launch_fixup<4, K32>(tabs, count, total_chunks, u, extra, st);
 }
 
-template <int NG, int NS, bool REDUCE = false, bool EXTRA = false>
-int launch_group_pipe_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
-  const size_t smem = (size_t)kPipeWarps * group_pipe_warp_bytes(NG, REDUCE);
-  if (int rc = configure_smem<bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA>>(smem)) return rc;
+template <int NG, int ROUNDS, int NS, bool REDUCE = false, bool EXTRA = false>
+int launch_lane_groups_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
+  const size_t smem = (size_t)kPipeWarps * lane_groups_warp_bytes(NG, ROUNDS, REDUCE);
+  if (int rc = configure_smem<bwd_lane_groups_kernel<NG, ROUNDS, NS, REDUCE, EXTRA>>(smem)) return rc;
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
-  bwd_group_pipe_kernel<NG, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
-  SC_LAUNCH_OK("bwd_group_pipe_kernel");
+  bwd_lane_groups_kernel<NG, ROUNDS, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
+  SC_LAUNCH_OK("bwd_lane_groups_kernel");
   return SC_OK;
 }
 
-// Rows of at most 64 floats: NG rows per warp instruction.
+// Rows of at most 128 / NG floats: NG rows per warp instruction.
 template <int NG>
-int launch_bwd_group_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
-                          bool extra, cudaStream_t st) {
+int launch_bwd_lane_groups(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
+                           bool extra, cudaStream_t st) {
+  constexpr int ROUNDS = 4 / NG;
   int rc;
-  if (num_slots == kReduceOnly) rc = launch_group_pipe_ns<NG, 0, true>(tabs, count, total_chunks, u, st);
-  else if (num_slots == 0) rc = launch_group_pipe_ns<NG, 0>(tabs, count, total_chunks, u, st);
-  else if (num_slots == 1) rc = launch_group_pipe_ns<NG, 1>(tabs, count, total_chunks, u, st);
-  else if (!extra) rc = launch_group_pipe_ns<NG, 2>(tabs, count, total_chunks, u, st);
-  else rc = launch_group_pipe_ns<NG, 2, false, true>(tabs, count, total_chunks, u, st);
+  if (num_slots == kReduceOnly) rc = launch_lane_groups_ns<NG, ROUNDS, 0, true>(tabs, count, total_chunks, u, st);
+  else if (num_slots == 0) rc = launch_lane_groups_ns<NG, ROUNDS, 0>(tabs, count, total_chunks, u, st);
+  else if (num_slots == 1) rc = launch_lane_groups_ns<NG, ROUNDS, 1>(tabs, count, total_chunks, u, st);
+  else if (!extra) rc = launch_lane_groups_ns<NG, ROUNDS, 2>(tabs, count, total_chunks, u, st);
+  else rc = launch_lane_groups_ns<NG, ROUNDS, 2, false, true>(tabs, count, total_chunks, u, st);
   if (rc != SC_OK) return rc;
   return launch_fixup<4, 1>(tabs, count, total_chunks, u, extra, st);
 }
 
-// SC_BWD_GROUPS=off keeps short rows on the one-row-per-instruction kernel.
-inline bool group_pipe_enabled() {
-  static const bool on = [] { const char* e = getenv("SC_BWD_GROUPS"); return !(e && strcmp(e, "off") == 0); }();
-  return on;
+// SC_BWD_GROUPS=off keeps short rows on the cp.async pipeline; SC_BWD_GROUPS=<dim> sends rows of up to <dim> floats
+// (at most 128) to the lane-group kernel instead of the default 64.
+inline int lane_groups_max_dim() {
+  static const int v = [] {
+    const char* e = getenv("SC_BWD_GROUPS");
+    if (e == nullptr) return 64;
+    if (strcmp(e, "off") == 0) return 0;
+    const int d = atoi(e);
+    return d < 0 ? 0 : d > 128 ? 128 : d;
+  }();
+  return v;
 }
 
 inline int dispatch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u,
                              int num_slots, bool extra, int max_dim, cudaStream_t st) {
-  static const int forced_groups = [] { const char* e = getenv("SC_BWD_GROUPS"); return e ? atoi(e) : 0; }();
-  if (group_pipe_enabled() && (max_dim <= 32 || (forced_groups == 4 && max_dim <= 32)))
-    return launch_bwd_group_pipe<4>(tabs, count, total_chunks, u, num_slots, extra, st);
-  if (group_pipe_enabled() && forced_groups == 2 && max_dim <= 64)
-    return launch_bwd_group_pipe<2>(tabs, count, total_chunks, u, num_slots, extra, st);
+  if (max_dim <= lane_groups_max_dim()) {
+    if (max_dim <= 32) return launch_bwd_lane_groups<4>(tabs, count, total_chunks, u, num_slots, extra, st);
+    if (max_dim <= 64) return launch_bwd_lane_groups<2>(tabs, count, total_chunks, u, num_slots, extra, st);
+    return launch_bwd_lane_groups<1>(tabs, count, total_chunks, u, num_slots, extra, st);
+  }
   const int vecs = (max_dim / 4 + 31) / 32;
   if (vecs <= 1) return launch_bwd_pipe<1>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
   if (vecs <= 2) return launch_bwd_pipe<2>(tabs, count, total_chunks, u, num_slots, extra, max_dim, st);
