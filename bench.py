@@ -36,11 +36,11 @@ for _p in (ROOT, os.path.join(ROOT, "jax-tpu-embedding_b200")):
 
 L2_BYTES = 126 * 1024 * 1024
 NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
-# DRAM traffic of the backward kernels per launch (dram__bytes_read.sum + dram__bytes_write.sum of ncu) divided by
-# the algorithmic bytes of the same launch, from captures of cases small enough for ncu's replay passes: c2 and c3
-# with scaled-down vocabularies (traffic and algorithmic bytes grow with the same quantities: lookups, distinct
-# rows, batch), c5 at full size.  c3: update kernel only (its fix-up pass was not captured).  None: no capture.
-TRAFFIC_RATIO = {"c2": 1.03, "c3": 0.90, "c5": 1.04, "c4": None, "c1": None}
+# DRAM traffic of the backward kernels per launch (dram__bytes_read.sum + dram__bytes_write.sum of ncu, update +
+# group + fix-up kernels) divided by the algorithmic bytes of the same launch, from captures of cases small enough for
+# ncu's replay passes (vocabularies scaled to 0.05 for c2 and c3, 0.25 for c5; traffic and algorithmic bytes grow with
+# the same quantities: lookups, distinct rows, batch).  None: no capture (c4 holds 102 GB on the device).
+TRAFFIC_RATIO = {"c2": 1.02, "c3": 0.94, "c5": 0.99, "c4": None, "c1": None}
 
 
 # --------------------------------------------------------------------------------- workloads
@@ -887,7 +887,9 @@ def main():
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
         "lookups_per_s": nnz_in * world / (ms * 1e-3),
-        "roofline": {"bound": "hbm", "kernel": "bwd_pipe_kernel + bwd_group_kernel + bwd_fixup_kernel (fused backward, all tables)",
+        "roofline": {"bound": "hbm",
+                     "kernel": ("bwd_lane_groups_kernel" if max(t["dim"] for t in wl["tables"]) <= 64 else "bwd_pipe_kernel") +
+                               " + bwd_group_kernel + bwd_fixup_kernel (fused backward, all tables)",
                      "achieved": bwd["achieved"], "peak": peak, "unit": "GB/s", "frac": bwd["frac"], "peak_kind": peak_kind,
                      "traffic": traffic, "algorithmic_bytes": bwd["algorithmic_bytes"], "ms": bwd["ms"], "forward": fwd},
         "preprocess": preprocess, "phases_ms": phases, "parity": parity,

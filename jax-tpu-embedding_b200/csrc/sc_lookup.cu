@@ -1948,7 +1948,7 @@ __device__ __forceinline__ void fixup_chunk(const TableDesc* __restrict__ tabs, 
       acc[k] = c < vec_per_row ? src[c] : Vec<W>::zero();
     }
   }
-  constexpr int U = K <= 2 ? 4 : 2;  // partial rows in flight
+  constexpr int U = K == 1 ? 8 : K == 2 ? 4 : 2;  // partial rows in flight
   uint32_t i = 0;
   for (; i + U <= total; i += U) {
     VT p[U][K];

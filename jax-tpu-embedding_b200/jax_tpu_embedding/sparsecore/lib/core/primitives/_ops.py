@@ -198,6 +198,9 @@ class ForwardGroupCall:
     self.shapes = [tuple(r.act.shape) for r in requests]
     self.sizes = [int(np.prod(shape)) for shape in self.shapes]
     self.total_floats = sum(self.sizes)
+    dims = {shape[-1] for shape in self.shapes if len(shape) == 2}
+    self.common_dim = dims.pop() if len(dims) == 1 and all(len(shape) == 2 for shape in self.shapes) else 0
+    self.rows = [shape[0] for shape in self.shapes]
     self.byte_offsets = np.concatenate([[0], np.cumsum(self.sizes)[:-1]]).astype(np.uint64) * np.uint64(4)
     self.first = True
     self.sharded = any(r.geo.l != r.geo.c for r in requests)
@@ -213,8 +216,13 @@ class ForwardGroupCall:
       self.requests = None
     else:
       # One allocation for all activations of the call.
-      flat = torch.empty(self.total_floats, dtype=torch.float32, device="cuda")
-      outs = [t.view(shape) for t, shape in zip(flat.split(self.sizes), self.shapes)]
+      if self.common_dim:
+        # All activations are [rows, dim] with one dim: the pieces of a 2-D buffer need no reshaping.
+        flat = torch.empty((self.total_floats // self.common_dim, self.common_dim), dtype=torch.float32, device="cuda")
+        outs = list(torch.split_with_sizes(flat, self.rows))
+      else:
+        flat = torch.empty(self.total_floats, dtype=torch.float32, device="cuda")
+        outs = [t.view(shape) for t, shape in zip(torch.split_with_sizes(flat, self.sizes), self.shapes)]
       addresses = self.byte_offsets + np.uint64(flat.data_ptr())
       for _, idxs, _, act_field in self.groups:
         act_field[:] = addresses[idxs]

@@ -24,6 +24,7 @@ from __future__ import annotations
 import ctypes
 import dataclasses
 import enum
+import operator
 from typing import Any, Sequence
 
 import numpy as np
@@ -535,6 +536,14 @@ class _DensePlan:
       cursor = off + size
     if cursor < self.int_total:
       self.split_sizes.append(self.int_total - cursor)
+    # Pickers of the pieces of one output column (row pointers, ids, sample ids) and of the plan arrays, in stack order.
+    def picker(indices):
+      indices = list(indices)
+      return operator.itemgetter(*indices) if len(indices) > 1 else (lambda seq, i=indices[0]: (seq[i],))
+    n_stacks = len(self.int_sizes) // 3
+    self.pick_columns = [picker(self.csr_piece[3 * si + k] for si in range(n_stacks)) for k in range(3)]
+    self.pick_plan_slots = picker(self.plan_piece[2 * si] for si in range(n_stacks))
+    self.pick_plan_bags = picker(self.plan_piece[2 * si + 1] for si in range(n_stacks))
     # The pointer fields of the launch descriptors as strided numpy views: a call fills them with a few
     # vector operations instead of one attribute assignment per field and stack.
     stride = ctypes.sizeof(_native.PreprocessItem)
@@ -656,9 +665,9 @@ class _DensePlan:
       stats.required_buffer_sizes = LazyStatsDict(deferred=deferred, field=2)
       stats.dropped_id_count = LazyStatsDict(deferred=deferred, field=3)
     del keep
-    pieces = ints.split(self.split_sizes)
-    float_views = floats.split(self.coos)
-    columns = [[pieces[self.csr_piece[3 * si + k]] for si in range(n)] for k in range(3)] + [list(float_views)]
+    pieces = torch.split_with_sizes(ints, self.split_sizes)
+    float_views = torch.split_with_sizes(floats, self.coos)
+    columns = [list(pick(pieces)) for pick in self.pick_columns] + [list(float_views)]
     if has_leading_dimension:
       columns = [[t.view(1, -1) for t in col] for col in columns]
     if not device_output:
@@ -676,8 +685,7 @@ class _DensePlan:
       token = (ibase, fbase, id(self), bool(has_leading_dimension))
       for i, d in enumerate((out_rp, out_ids, out_sids, out_gains)):
         d.token = token + (i,)
-      out_rp.forward_plans = {name: (pieces[self.plan_piece[2 * si]], pieces[self.plan_piece[2 * si + 1]])
-                              for si, name in enumerate(self.names)}
+      out_rp.forward_plans = dict(zip(self.names, zip(self.pick_plan_slots(pieces), self.pick_plan_bags(pieces))))
     return out_rp, out_ids, out_sids, out_gains, 1, stats
 
 

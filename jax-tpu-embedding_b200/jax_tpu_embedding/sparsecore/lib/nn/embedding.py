@@ -21,6 +21,7 @@ from __future__ import annotations
 import collections
 import dataclasses
 from typing import Any, Mapping, NamedTuple, Sequence
+import sys
 import warnings
 
 import numpy as np
@@ -39,8 +40,23 @@ get_default_limits = table_stacking.get_default_limits
 RaggedInput = pybind_input_preprocessing.RaggedInput
 
 
+_LEAF_TYPES: tuple = ()
+
+
+def _leaf_types() -> tuple:
+  """The classes whose instances are leaves of a feature tree (torch.Tensor joins once torch is loaded)."""
+  global _LEAF_TYPES
+  if len(_LEAF_TYPES) < 5:
+    types = (embedding_spec.FeatureSpec, embedding_spec.TableSpec, RaggedInput, np.ndarray)
+    torch = sys.modules.get("torch")
+    if torch is not None:
+      types += (torch.Tensor,)
+    _LEAF_TYPES = types
+  return _LEAF_TYPES
+
+
 def _is_feature_leaf(x) -> bool:
-  return isinstance(x, (embedding_spec.FeatureSpec, embedding_spec.TableSpec, RaggedInput)) or _is_array(x)
+  return isinstance(x, _leaf_types()) or _is_array(x)
 
 
 def _is_array(x) -> bool:
@@ -51,8 +67,9 @@ def _flat_leaves(tree) -> bool:
   """True for the common case: a plain list or tuple whose elements are all leaves."""
   if type(tree) is not list and type(tree) is not tuple:
     return False
+  types = _leaf_types()
   for x in tree:
-    if not _is_feature_leaf(x):
+    if not isinstance(x, types) and not _is_array(x):
       return False
   return True
 
@@ -471,13 +488,23 @@ class _SpecInfo:
           and f.output_shape[0] == self.stacked[name].total_sample_count)
     self.all_trivial = all(self.trivial.values())
     self.hypers: dict = {}  # step -> {stack: optimizer hyper-parameters as floats}
+    self.flat_stack_names = [f.table_spec.stacked_table_spec.stack_name for f in self.flat]
+    self.first_stacked = self.flat[0].table_spec._stacked_table_spec if self.flat else None  # pylint: disable=protected-access
     self.keep = feature_specs  # keeps the ids in the cache key alive
 
 
 _SPEC_INFO: dict = {}
+_LAST_SPEC_INFO: list = [None, None]  # the tree object of the previous call and its facts
 
 
 def _spec_info(feature_specs) -> _SpecInfo:
+  # The same tree object as in the previous call (a training loop): no walk over the tree.  A tree that was
+  # changed in place, or whose tables were stacked again, is noticed by its length and its first stacked spec.
+  last_tree, last = _LAST_SPEC_INFO
+  if (last_tree is feature_specs and type(feature_specs) in (list, tuple) and len(feature_specs) == len(last.flat)
+      and last.flat and feature_specs[0] is last.flat[0]
+      and last.flat[0].table_spec._stacked_table_spec is last.first_stacked):  # pylint: disable=protected-access
+    return last
   flat = _leaves(feature_specs)
   key = tuple((id(f), id(f.table_spec._stacked_table_spec), id(f._id_transformation)) for f in flat)  # pylint: disable=protected-access
   info = _SPEC_INFO.get(key)
@@ -485,6 +512,7 @@ def _spec_info(feature_specs) -> _SpecInfo:
     if len(_SPEC_INFO) > 64:
       _SPEC_INFO.clear()
     info = _SPEC_INFO[key] = _SpecInfo(feature_specs)
+  _LAST_SPEC_INFO[0], _LAST_SPEC_INFO[1] = feature_specs, info
   return info
 
 
@@ -528,13 +556,25 @@ def _tensor_key(tensors):
   return key if len(key) == len(tensors) else None
 
 
+def _address_key(tensors):
+  """Addresses of torch tensors, or None if any element is something else.  For operands that live as long as the
+  cached descriptors are useful (tables and slot variables): whatever else there is to check about them was checked
+  when the descriptors were built, and a host tensor or a new allocation has another address."""
+  try:
+    return tuple([x.data_ptr() for x in tensors])
+  except AttributeError:
+    return None
+
+
 def clear_caches() -> None:
   """Forgets the cached launch descriptors and spec facts (they hold addresses of tables and buffers).
 
-  Call it after freeing or replacing embedding variables whose addresses may be reused by new ones.
+  Call it after freeing or replacing embedding variables whose addresses may be reused by new ones, and after
+  changing a feature-spec tree in place.
   """
   _CALL_CACHE.clear()
   _SPEC_INFO.clear()
+  _LAST_SPEC_INFO[0] = _LAST_SPEC_INFO[1] = None
   pybind_input_preprocessing.clear_caches()
 
 
@@ -567,7 +607,7 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
 
   key = None
   csr_key = _csr_key(rps, eids, sids, gains, stacked_table_specs)
-  table_key = _tensor_key([embedding_variables[n].table for n in stacked_table_specs])
+  table_key = _address_key([embedding_variables[n].table for n in stacked_table_specs])
   if csr_key is not None and table_key is not None:
     key = ("fwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, csr_key, table_key)
   cached = _CALL_CACHE.get(key) if key is not None else None
@@ -594,15 +634,18 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
           forward_plan=plans.get(name) if plans else None,
       ))
     cached = (_ops.ForwardGroupCall(requests), local)
-    if key is not None:
+    # (The key holds bare addresses of the tables: only descriptors built from device tensors may be replayed.)
+    if key is not None and all(_is_cuda_tensor(embedding_variables[n].table) for n in stacked_table_specs):
       _cache_put(key, cached)
   call, local = cached
   # One grouped launch sequence for all stacked tables (the reference issues one call per table).
   activations = dict(zip(stacked_table_specs.keys(), call.run()))
   if perform_unstacking:
     if info.all_trivial and local == 1:
-      return _tree.unflatten(feature_specs, [activations[f.table_spec.stacked_table_spec.stack_name]
-                                             for f in info.flat], is_leaf=_is_feature_leaf)
+      leaves = [activations[name] for name in info.flat_stack_names]
+      if type(feature_specs) is list and len(feature_specs) == len(leaves) and _flat_leaves(feature_specs):
+        return leaves
+      return _tree.unflatten(feature_specs, leaves, is_leaf=_is_feature_leaf)
     activations = unstack_embedding_activations(
         activations, feature_specs, global_device_count, num_sc_per_device,
         use_activation_unstack_primitive=use_activation_unstack_primitive, local_device_count=local)
@@ -679,7 +722,7 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
     _assert_same_structure(feature_specs, activation_gradients, "feature_specs", "activation_gradients")
     grad_leaves = _leaves(activation_gradients)
     if info.all_trivial and local == 1 and all(_is_cuda_tensor(g) and g.dim() == 2 for g in grad_leaves):
-      gradients = {f.table_spec.stacked_table_spec.stack_name: g for f, g in zip(info.flat, grad_leaves)}
+      gradients = dict(zip(info.flat_stack_names, grad_leaves))
     else:
       gradients = stack_embedding_gradients(activation_gradients, feature_specs, num_sc_per_device,
                                             global_device_count, use_gradient_stacking_primitive,
@@ -703,8 +746,11 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
       tuple(embedding_var_limits[n]) for n in stacked_table_specs)
   key = None
   csr_key = _csr_key(rps, eids, sids, gains, stacked_table_specs)
-  tensor_key = _tensor_key([x for n in stacked_table_specs
-                            for x in (embedding_variables[n].table, *embedding_variables[n].slot, gradients[n])])
+  names = tuple(stacked_table_specs)
+  variable_key = _address_key([x for n in names for x in (embedding_variables[n].table, *embedding_variables[n].slot)])
+  tensor_key = None if variable_key is None else _tensor_key([gradients[n] for n in names])
+  if tensor_key is not None:
+    tensor_key = (variable_key, tensor_key)
   if csr_key is not None and tensor_key is not None:
     key = ("bwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, label, limits,
            tuple(hypers.values()), csr_key, tensor_key)
@@ -729,10 +775,15 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
           num_sc_per_device=num_sc_per_device, global_device_count=global_device_count, local_device_count=local,
           **extra))
     call = _ops.GradGroupCall(requests)
-    if key is not None:
+    # (The key holds bare addresses of tables and slot variables: only descriptors built from device tensors may be
+    # replayed.)
+    if key is not None and all(_is_cuda_tensor(x) for n in names
+                               for x in (embedding_variables[n].table, *embedding_variables[n].slot)):
       _cache_put(key, call)
   first_results = call.run()
   # Tables and slot variables were updated in place; hand the same tensors back.
+  if first_results is None:  # replayed descriptors: every operand is a device tensor that was updated in place
+    return {name: embedding_variables[name] for name in names}
   updated = {}
   for index, name in enumerate(stacked_table_specs):
     variables = embedding_variables[name]
