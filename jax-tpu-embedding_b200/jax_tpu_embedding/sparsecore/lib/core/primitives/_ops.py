@@ -163,6 +163,36 @@ class ForwardRequest:
       self.local_shard = distributed.rank() * self.geo.s_eff
 
 
+class _CsrFields:
+  """The CSR (and forward plan) pointer fields of a descriptor array as strided numpy views, with their offsets from
+  the two buffers of the preprocessing output the descriptors were built from: moving the descriptors to another
+  output of the same layout is a handful of vector additions."""
+
+  def __init__(self, items, item_type, count: int, bases, with_plan: bool):
+    size = ctypes.sizeof(item_type)
+    field = lambda offset: np.ndarray((count,), dtype=np.uint64, buffer=items, offset=offset, strides=(size,))
+    c = item_type.csr.offset
+    self.int_fields = [field(c + _native.Csr.row_pointers.offset), field(c + _native.Csr.embedding_ids.offset),
+                       field(c + _native.Csr.sample_ids.offset)]
+    if with_plan:
+      self.int_fields += [field(item_type.plan_slots.offset), field(item_type.plan_bags.offset)]
+    self.float_fields = [field(c + _native.Csr.gains.offset)]
+    self.bases = (int(bases[0]), int(bases[1]))
+    # A null pointer (a descriptor without a plan) stays null.
+    self.int_rel = [(f != 0, f - np.uint64(self.bases[0])) for f in self.int_fields]
+    self.float_rel = [(f != 0, f - np.uint64(self.bases[1])) for f in self.float_fields]
+
+  def rebase(self, bases) -> None:
+    ibase, fbase = int(bases[0]), int(bases[1])
+    if (ibase, fbase) == self.bases:
+      return
+    for f, (used, rel) in zip(self.int_fields, self.int_rel):
+      np.copyto(f, rel + np.uint64(ibase), where=used)
+    for f, (used, rel) in zip(self.float_fields, self.float_rel):
+      np.copyto(f, rel + np.uint64(fbase), where=used)
+    self.bases = (ibase, fbase)
+
+
 class ForwardGroupCall:
   """Validated requests turned into ready-to-launch descriptor arrays (one per shape class).
 
@@ -170,10 +200,11 @@ class ForwardGroupCall:
   again; outputs are allocated per run.
   """
 
-  def __init__(self, requests):
+  def __init__(self, requests, bases=None):
     lib = _native.lib()
     self.requests = requests
     self.groups = []
+    self.csr_fields = []
     by_class: dict = {}
     for i, r in enumerate(requests):
       by_class.setdefault(shape_class(r.geo.dim), []).append(i)
@@ -195,6 +226,8 @@ class ForwardGroupCall:
       act_field = np.ndarray((len(idxs),), dtype=np.uint64, buffer=items, offset=_native.FwdItem.activations.offset,
                              strides=(ctypes.sizeof(_native.FwdItem),))
       self.groups.append((items, idxs, nbytes, act_field))
+      if bases is not None:
+        self.csr_fields.append(_CsrFields(items, _native.FwdItem, len(idxs), bases, with_plan=True))
     self.shapes = [tuple(r.act.shape) for r in requests]
     self.sizes = [int(np.prod(shape)) for shape in self.shapes]
     self.total_floats = sum(self.sizes)
@@ -206,6 +239,11 @@ class ForwardGroupCall:
     self.sharded = any(r.geo.l != r.geo.c for r in requests)
     self.keep = [(r.ptrs,) for r in requests]
     # Requests keep tensors alive; a replayable call must not, so drop them after the first run.
+
+  def rebase(self, bases) -> None:
+    """Points the descriptors at another preprocessing output of the same layout (its two buffer addresses)."""
+    for fields in self.csr_fields:
+      fields.rebase(bases)
 
   def run(self):
     torch = _native.torch_mod()
@@ -300,10 +338,11 @@ class GradRequest:
 class GradGroupCall:
   """Ready-to-launch descriptors of a grouped backward call (addresses and sizes only)."""
 
-  def __init__(self, requests):
+  def __init__(self, requests, bases=None):
     lib = _native.lib()
     self.requests = requests
     self.groups = []
+    self.csr_fields = []
     by_class: dict = {}
     for i, r in enumerate(requests):
       by_class.setdefault((shape_class(r.geo.dim), r.opt.optimizer), []).append(i)
@@ -333,10 +372,17 @@ class GradGroupCall:
           _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), None, 0, None))
         nbytes = max(nbytes, stage_bytes)
       self.groups.append((items, idxs, nbytes))
+      if bases is not None:
+        self.csr_fields.append(_CsrFields(items, _native.GradItem, len(idxs), bases, with_plan=False))
     self.keep = [(r.t_ptrs, r.s_ptrs, r.pull) for r in requests]
     self.sharded = any(r.pull is not None for r in requests)
     self._results = [r.results() for r in requests]
     self.first = True
+
+  def rebase(self, bases) -> None:
+    """Points the descriptors at another preprocessing output of the same layout (its two buffer addresses)."""
+    for fields in self.csr_fields:
+      fields.rebase(bases)
 
   def run(self):
     lib = _native.lib()

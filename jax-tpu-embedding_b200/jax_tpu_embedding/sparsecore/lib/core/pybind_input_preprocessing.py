@@ -322,22 +322,36 @@ class _DeferredStats:
 
   def __init__(self, pinned, event, names, limits, p, s):
     self.pinned, self.event, self.names, self.limits, self.p, self.s = pinned, event, names, limits, p, s
+    self.host = None  # the block once it has arrived
     self.fields = None
     self.error = None
 
-  def resolve(self):
-    if self.fields is None and self.error is None:
+  def check(self):
+    """Waits for the copy and raises the error of the call, if any (cheap: one vector test of the status column).
+    The per-table dicts are built only when somebody reads them."""
+    if self.host is None:
       self.event.synchronize()
-      host = self.pinned.numpy().copy()
+      self.host = self.pinned.numpy().copy()
       self.pinned = None
       p, s = self.p, self.s
       try:
-        status = host[:, 2 * p + s + 1]
+        status = self.host[:, 2 * p + s + 1]
         if status.any():
           si = int(np.flatnonzero(status)[0])
-          _raise_for_status(host[si], p, s, self.names[si], *self.limits[si])
+          _raise_for_status(self.host[si], p, s, self.names[si], *self.limits[si])
       except ValueError as e:
         self.error = e
+    if self.error is not None:
+      raise self.error
+
+  @property
+  def checked(self) -> bool:
+    return self.host is not None
+
+  def resolve(self):
+    self.check()
+    if self.fields is None:
+      host, p, s = self.host, self.p, self.s
       fields = ({}, {}, {}, {})
       for si, name in enumerate(self.names):
         fields[0][name] = host[si, :p].copy()
@@ -345,8 +359,6 @@ class _DeferredStats:
         fields[2][name] = host[si, 2 * p:2 * p + s].copy()
         fields[3][name] = int(host[si, 2 * p + s])
       self.fields = fields
-    if self.error is not None:
-      raise self.error
     return self.fields
 
 
@@ -416,8 +428,10 @@ class LazyStatsDict(dict):
 class BufferDict(dict):
   """dict of output arrays that remembers which device buffers all its values are views of.
 
-  `token` identifies (buffer addresses, layout); callers that cache launch descriptors use it
-  instead of looking at every array.  Any change of the dict drops the token.
+  `token` = (address of the int32 buffer, address of the float32 buffer, layout ..., index of the dict): callers
+  that cache launch descriptors use it instead of looking at every array - the layout part keys the cache, the
+  two addresses are all that differs between the outputs of two calls with one layout.  Any change of the dict drops
+  the token.
   """
 
   token = None
@@ -590,8 +604,8 @@ class _DensePlan:
     if not sync_stats:
       # The statistics of the previous deferred call have long arrived: a violated limit surfaces here.
       previous = self.deferred[(self.deferred_next - 1) % len(self.deferred)]
-      if previous is not None and previous.fields is None and previous.error is None and previous.event.query():
-        previous.resolve()
+      if previous is not None and not previous.checked and previous.event.query():
+        previous.check()
     ints = torch.empty(self.int_total, dtype=torch.int32, device="cuda")
     floats = torch.empty(self.float_total, dtype=torch.float32, device="cuda")
     stats_dev = torch.empty((n, self.stats_size), dtype=torch.int32, device="cuda")
@@ -648,9 +662,9 @@ class _DensePlan:
       # it (and raise for a violated limit) when they are first read.
       slot = self.deferred_next % len(self.deferred)
       old = self.deferred[slot]
-      if old is not None and old.fields is None and old.error is None:
+      if old is not None and not old.checked:
         try:
-          old.resolve()  # its pinned buffer is about to be recycled
+          old.check()  # its pinned buffer is about to be recycled
         except ValueError:
           pass
       pinned = torch.empty((n, self.stats_size), dtype=torch.int32, pin_memory=True)
@@ -682,7 +696,7 @@ class _DensePlan:
         stats.dropped_id_count[name] = int(dropped[si])
     if device_output:
       # The arrays keep the two buffers alive, so the addresses identify the contents' location.
-      token = (ibase, fbase, id(self), bool(has_leading_dimension))
+      token = (ibase, fbase, self, bool(has_leading_dimension))  # (addresses of the two buffers, layout ...)
       for i, d in enumerate((out_rp, out_ids, out_sids, out_gains)):
         d.token = token + (i,)
       out_rp.forward_plans = dict(zip(self.names, zip(self.pick_plan_slots(pieces), self.pick_plan_bags(pieces))))

@@ -521,21 +521,28 @@ def _is_cuda_tensor(x) -> bool:
 
 
 _CALL_CACHE: dict = {}
+# Replays and rebuilds of launch descriptors since import (a training loop should show replays only).
+CALL_CACHE_STATS = {"replayed": 0, "built": 0}
 
 
 def _csr_key(rps, eids, sids, gains, names):
-  """Identity of the four CSR array dicts for the launch-descriptor cache, or None.
+  """(key, bases): identity of the four CSR array dicts for the launch-descriptor cache (None: not cacheable).
 
-  Dicts that come from this package's preprocessing carry a token naming the device buffers they
-  are views of; otherwise every array is described by (address, shape, dtype).
+  Dicts that come from this package's preprocessing carry a token naming the two device buffers they are views of
+  and their layout.  The key then holds the layout only and `bases` the two addresses: cached descriptors are
+  replayed for every output of that layout, their CSR pointers moved to the new buffers (`rebase`).  Otherwise every
+  array is described by (address, shape, dtype) and `bases` is None.
   """
   tokens = tuple(getattr(d, "token", None) for d in (rps, eids, sids, gains))
   if all(t is not None for t in tokens) and len(rps) == len(names):
-    return tokens
+    bases = tokens[0][:2]
+    if all(t[:2] == bases for t in tokens):
+      return tuple(t[2:] for t in tokens), bases
+    return tokens, None
   arrays = [d[n] for n in names for d in (rps, eids, sids, gains)]
   if not all(_is_cuda_tensor(x) for x in arrays):
-    return None
-  return tuple((x.data_ptr(), tuple(x.shape), x.dtype) for x in arrays)
+    return None, None
+  return tuple((x.data_ptr(), tuple(x.shape), x.dtype) for x in arrays), None
 
 
 def _forward_plans(rps, eids, sids, gains):
@@ -606,11 +613,12 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
   strategy = int(sharding_strategy_to_enum(sharding_strategy))
 
   key = None
-  csr_key = _csr_key(rps, eids, sids, gains, stacked_table_specs)
+  csr_key, bases = _csr_key(rps, eids, sids, gains, stacked_table_specs)
   table_key = _address_key([embedding_variables[n].table for n in stacked_table_specs])
   if csr_key is not None and table_key is not None:
     key = ("fwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, csr_key, table_key)
   cached = _CALL_CACHE.get(key) if key is not None else None
+  CALL_CACHE_STATS["built" if cached is None else "replayed"] += 1
   if cached is None:
     requests, local = [], 1
     # Sample-major plans that this package's preprocessing emitted together with these buffers.
@@ -633,11 +641,13 @@ def tpu_sparse_dense_matmul(preprocessed_inputs, embedding_variables, feature_sp
           max_ids_per_sample=info.max_ids_per_sample[name],
           forward_plan=plans.get(name) if plans else None,
       ))
-    cached = (_ops.ForwardGroupCall(requests), local)
+    cached = (_ops.ForwardGroupCall(requests, bases), local)
     # (The key holds bare addresses of the tables: only descriptors built from device tensors may be replayed.)
     if key is not None and all(_is_cuda_tensor(embedding_variables[n].table) for n in stacked_table_specs):
       _cache_put(key, cached)
   call, local = cached
+  if bases is not None:
+    call.rebase(bases)
   # One grouped launch sequence for all stacked tables (the reference issues one call per table).
   activations = dict(zip(stacked_table_specs.keys(), call.run()))
   if perform_unstacking:
@@ -745,7 +755,7 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
   limits = None if embedding_var_limits is None else tuple(
       tuple(embedding_var_limits[n]) for n in stacked_table_specs)
   key = None
-  csr_key = _csr_key(rps, eids, sids, gains, stacked_table_specs)
+  csr_key, bases = _csr_key(rps, eids, sids, gains, stacked_table_specs)
   names = tuple(stacked_table_specs)
   variable_key = _address_key([x for n in names for x in (embedding_variables[n].table, *embedding_variables[n].slot)])
   tensor_key = None if variable_key is None else _tensor_key([gradients[n] for n in names])
@@ -755,6 +765,7 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
     key = ("bwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, label, limits,
            tuple(hypers.values()), csr_key, tensor_key)
   call = _CALL_CACHE.get(key) if key is not None else None
+  CALL_CACHE_STATS["built" if call is None else "replayed"] += 1
   if call is None:
     requests = []
     for name, stacked in stacked_table_specs.items():
@@ -774,12 +785,14 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
           computation_name=symbol, sharding_strategy=strategy, enable_minibatching=enable_minibatching,
           num_sc_per_device=num_sc_per_device, global_device_count=global_device_count, local_device_count=local,
           **extra))
-    call = _ops.GradGroupCall(requests)
+    call = _ops.GradGroupCall(requests, bases)
     # (The key holds bare addresses of tables and slot variables: only descriptors built from device tensors may be
     # replayed.)
     if key is not None and all(_is_cuda_tensor(x) for n in names
                                for x in (embedding_variables[n].table, *embedding_variables[n].slot)):
       _cache_put(key, call)
+  if bases is not None:
+    call.rebase(bases)
   first_results = call.run()
   # Tables and slot variables were updated in place; hand the same tensors back.
   if first_results is None:  # replayed descriptors: every operand is a device tensor that was updated in place
