@@ -343,6 +343,7 @@ class GradGroupCall:
     self.requests = requests
     self.groups = []
     self.csr_fields = []
+    self.grad_fields = []
     by_class: dict = {}
     for i, r in enumerate(requests):
       by_class.setdefault((shape_class(r.geo.dim), r.opt.optimizer), []).append(i)
@@ -372,6 +373,10 @@ class GradGroupCall:
           _native.check(lib.sc_sparse_dense_matmul_grad_stage(items, len(idxs), None, 0, None))
         nbytes = max(nbytes, stage_bytes)
       self.groups.append((items, idxs, nbytes))
+      # The gradient pointers of the group's descriptors as one strided numpy view (see set_gradients).
+      self.grad_fields.append(np.ndarray((len(idxs),), dtype=np.uint64, buffer=items,
+                                         offset=_native.GradItem.activation_grad.offset,
+                                         strides=(ctypes.sizeof(_native.GradItem),)))
       if bases is not None:
         self.csr_fields.append(_CsrFields(items, _native.GradItem, len(idxs), bases, with_plan=False))
     self.keep = [(r.t_ptrs, r.s_ptrs, r.pull) for r in requests]
@@ -383,6 +388,13 @@ class GradGroupCall:
     """Points the descriptors at another preprocessing output of the same layout (its two buffer addresses)."""
     for fields in self.csr_fields:
       fields.rebase(bases)
+
+  def set_gradients(self, addresses) -> None:
+    """Points the descriptors at the activation gradients of this call (device addresses in request order; the
+    tensors have the shapes and dtype of those the descriptors were built from)."""
+    addresses = np.asarray(addresses, dtype=np.uint64)
+    for (_, idxs, _), field in zip(self.groups, self.grad_fields):
+      field[:] = addresses[idxs]
 
   def run(self):
     lib = _native.lib()

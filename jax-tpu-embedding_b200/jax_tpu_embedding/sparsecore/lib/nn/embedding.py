@@ -758,9 +758,14 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
   csr_key, bases = _csr_key(rps, eids, sids, gains, stacked_table_specs)
   names = tuple(stacked_table_specs)
   variable_key = _address_key([x for n in names for x in (embedding_variables[n].table, *embedding_variables[n].slot)])
-  tensor_key = None if variable_key is None else _tensor_key([gradients[n] for n in names])
-  if tensor_key is not None:
-    tensor_key = (variable_key, tensor_key)
+  # Gradients arrive at other addresses every step (they are outputs of the dense model's backward pass): the key
+  # holds their shapes and dtype, the descriptors get the addresses of this call (`set_gradients`).
+  grad_list = [gradients[n] for n in names]
+  tensor_key = None
+  if variable_key is not None and all(_is_cuda_tensor(g) for g in grad_list):
+    f32 = _native.torch_mod().float32  # (any other dtype is converted into a copy when the descriptors are built)
+    if all(g.dtype == f32 for g in grad_list):
+      tensor_key = (variable_key, tuple([g.shape for g in grad_list]))
   if csr_key is not None and tensor_key is not None:
     key = ("bwd", id(info), global_device_count, num_sc_per_device, strategy, enable_minibatching, label, limits,
            tuple(hypers.values()), csr_key, tensor_key)
@@ -793,6 +798,8 @@ def tpu_sparse_dense_matmul_grad(activation_gradients, preprocessed_inputs, embe
       _cache_put(key, call)
   if bases is not None:
     call.rebase(bases)
+  if key is not None:
+    call.set_gradients([g.data_ptr() for g in grad_list])
   first_results = call.run()
   # Tables and slot variables were updated in place; hand the same tensors back.
   if first_results is None:  # replayed descriptors: every operand is a device tensor that was updated in place
