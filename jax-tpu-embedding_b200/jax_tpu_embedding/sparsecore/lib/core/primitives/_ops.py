@@ -381,6 +381,12 @@ class GradGroupCall:
         self.csr_fields.append(_CsrFields(items, _native.GradItem, len(idxs), bases, with_plan=False))
     self.keep = [(r.t_ptrs, r.s_ptrs, r.pull) for r in requests]
     self.sharded = any(r.pull is not None for r in requests)
+    # Two row-sharded requests of one call must not stage into the same peer buffers (equal `exchange_key` and
+    # geometry): the second staging would overwrite the first before the update reads it.
+    staged = [id(r.pull) for r in requests if r.pull is not None]
+    if len(set(staged)) != len(staged):
+      raise ValueError("two requests of one grouped update share their exchange buffers: give each stacked table "
+                       "its own computation_name / exchange_key")
     self._results = [r.results() for r in requests]
     self.first = True
 
