@@ -501,6 +501,7 @@ __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : K <= 2 ? 4 : 3) fwd_gathe
   constexpr int NG = 32 / G;
   constexpr int U = K >= 4 ? 2 : SC_GATHER_ROWS_SHORT / K;  // table rows held in registers per group
   __shared__ RowMeta s_meta[kWarpsPerBlock][32];
+  __shared__ uint8_t s_order[kWarpsPerBlock][32];  // rows of the warp by descending bag length
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   // Rows [first_act, total_act) of `tabs`, rows_per_warp (a multiple of 32 / G, at most 32) to a warp.
   const uint32_t r0 = first_act + (blockIdx.x * kWarpsPerBlock + wib) * (uint32_t)rows_per_warp;
@@ -521,6 +522,20 @@ __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : K <= 2 ? 4 : 3) fwd_gathe
       }
     }
     s_meta[wib][lane] = m;
+    if (NG > 1) {
+      // The groups of a warp walk their bags side by side and share the warp's instruction stream, so rows of
+      // different lengths make them diverge.  Rows are therefore taken in order of descending bag length: the NG rows
+      // of a turn have neighbouring lengths.  (Every row is summed by one group in bag order whatever the turn is,
+      // so the result does not depend on this order.)
+      const uint32_t len = m.end - m.begin;
+      int rank = 0;
+#pragma unroll 8
+      for (int i = 0; i < 32; ++i) {
+        const uint32_t other = __shfl_sync(0xffffffffu, len, i);
+        rank += (other > len || (other == len && i < lane)) ? 1 : 0;
+      }
+      s_order[wib][rank] = (uint8_t)lane;
+    }
   }
   __syncwarp();
   const int group = lane / G, gl = lane % G;
@@ -529,7 +544,9 @@ __global__ void __launch_bounds__(kBlock, K >= 8 ? 1 : K <= 2 ? 4 : 3) fwd_gathe
   int cached_t = -1, dim = 0, vec_per_row = 0;
   float* act = nullptr;
   uint32_t act_base = 0;
-  for (int j = group; j < rows_here; j += NG) {
+  for (int turn = group; turn < 32; turn += NG) {
+    const int j = NG > 1 ? (int)s_order[wib][turn] : turn;
+    if (j >= rows_here) break;  // lanes past the warp's rows have empty bags and sort after every row of the warp
     const RowMeta m = s_meta[wib][j];
     if (m.table != cached_t) {
       const TableDesc& td = tabs[m.table];
