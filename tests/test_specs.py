@@ -236,3 +236,24 @@ def test_eval_shape_and_spec_lookups():
   dup = [_feature("same", tables[0], 16), _feature("same", tables[1], 16)]
   with pytest.raises(ValueError, match="already defined"):
     embedding.get_table_specs(dup)
+
+
+def test_spec_facts_are_remembered_per_tree_and_follow_restacking():
+  """The per-tree facts are memoised by the identity of the tree; stacking the tables again must not reuse them."""
+  tables = [_table("a", 100, 8), _table("b", 30, 8)]
+  feats = [_feature(f"f{i}", t, 16) for i, t in enumerate(tables)]
+  embedding.prepare_feature_specs_for_training(feats, global_device_count=1, num_sc_per_device=1)
+  first = embedding._spec_info(feats)  # pylint: disable=protected-access
+  assert embedding._spec_info(feats) is first  # pylint: disable=protected-access
+  assert set(first.stacked) == {"a", "b"} and first.flat_stack_names == ["a", "b"]
+  # The same list object, other stacked specs: the memo must notice.
+  ts.stack_tables(feats, ["a", "b"], global_device_count=1, num_sc_per_device=1, stack_name="ab")
+  second = embedding._spec_info(feats)  # pylint: disable=protected-access
+  assert second is not first and set(second.stacked) == {"ab"}
+  # A longer list that starts with the same features is another tree.
+  extra = _feature("g", _table("c", 50, 8), 16)
+  embedding.prepare_feature_specs_for_training([extra], global_device_count=1, num_sc_per_device=1)
+  third = embedding._spec_info(feats + [extra])  # pylint: disable=protected-access
+  assert set(third.stacked) == {"ab", "c"}
+  embedding.clear_caches()
+  assert embedding._spec_info(feats) is not second  # pylint: disable=protected-access
