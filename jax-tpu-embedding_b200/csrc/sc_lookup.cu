@@ -1558,9 +1558,9 @@ __global__ void __launch_bounds__(kPipeBlock) bwd_pipe_kernel(const TableDesc* _
 // ---- rows of at most 128 floats: lane groups, several rows per warp instruction, rows through registers
 constexpr int kGroupWindow = 8;  // entries of a window = gradient rows a lane holds in registers at a time
 // Per warp: per entry the gradient row address and the gain | per run end a descriptor | table / slot row addresses
-// of the runs to apply | segment sums: one round's segments, the carry, the groups' shares of taken-over entries.
-__host__ __device__ constexpr size_t lane_groups_warp_bytes(int NG, int ROUNDS, bool reduce_only) {
-  return 32 * 12 + 34 * 4 + 8 + (reduce_only ? 0 : 32 * 3 * 8) + (size_t)(32 / ROUNDS + 1 + NG) * (32 / NG) * 16;
+// of the runs to apply | segment sums: one pass's segments, the carry, the groups' shares of taken-over entries.
+__host__ __device__ constexpr size_t lane_groups_warp_bytes(int NG, int PASSES, bool reduce_only) {
+  return 32 * 12 + 34 * 4 + 8 + (reduce_only ? 0 : 32 * 3 * 8) + (size_t)(32 / PASSES + 1 + NG) * (32 / NG) * 16;
 }
 
 __device__ __forceinline__ float4 ld_row16(const float4* p) { return *p; }
@@ -1568,28 +1568,28 @@ __device__ __forceinline__ uint32_t lanes_below(int j) { return j >= 32 ? 0xffff
 
 // Same contract as bwd_pipe_kernel, for rows of at most 128 / NG floats.  The warp's 32 lanes form NG groups of
 // 32 / NG lanes (one float4 per lane and row), so one warp instruction moves, sums or updates NG rows.  A chunk is
-// processed in ROUNDS rounds of 32 / ROUNDS entries; a round has phases whose steps are uniform across the groups:
-//   reduce   group g owns the WINDOW of kGroupWindow entries [g * 8, g * 8 + 8) of the round, whatever the runs
+// processed in PASSES passes of 32 / PASSES entries; a pass has phases whose steps are uniform across the groups:
+//   reduce   group g owns the WINDOW of kGroupWindow entries [g * 8, g * 8 + 8) of the pass, whatever the runs
 //            are: it loads the window's gradient rows into registers and adds them up; a SEGMENT ends where a run
 //            ends or the window ends, and its sum goes to shared memory.  (The entries taken over from the next
-//            chunk are split evenly among the groups in the last round.)
-//   combine  the sum of a run is the carry (the run's segments of earlier rounds), its at most NG segments of the
-//            round in window order, and the groups' shares of the taken-over entries;
-//   apply    the runs that the chunk owns and that end in the round are dealt round-robin to the groups, which load
+//            chunk are split evenly among the groups in the last pass.)
+//   combine  the sum of a run is the carry (the run's segments of earlier passes), its at most NG segments of the
+//            pass in window order, and the groups' shares of the taken-over entries;
+//   apply    the runs that the chunk owns and that end in the pass are dealt round-robin to the groups, which load
 //            the table row and the slot rows, apply the optimizer and store.  Runs that cross the chunk store their
 //            sum as the chunk's partial sum; in reduce-only mode the sums go to the exchange buffer.
 // A hot row that fills the chunk is spread over all groups, nothing waits in a ring, and a warp needs about 6 KiB of
 // shared memory and at most 64 registers per thread, so that half of the SM's warp slots are filled and hide the
 // latency of a chunk's dependent metadata loads.  Inside a segment the sum runs in entry order.
-template <int NG, int ROUNDS, int NS, bool REDUCE, bool EXTRA>
+template <int NG, int PASSES, int NS, bool REDUCE, bool EXTRA>
 __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const TableDesc* __restrict__ tabs, int count,
                                                                        uint32_t total_chunks, float* __restrict__ partial,
                                                                        uint8_t* __restrict__ chunk_flags, int pstride) {
   constexpr int Gc = 32 / NG;     // lanes of a group
-  constexpr int S = 32 / ROUNDS;  // entries of a round
+  constexpr int S = 32 / PASSES;  // entries of a pass
   constexpr int Wd = S / NG;      // entries of a window
   static_assert(Wd == kGroupWindow, "a window is one batch of register loads");
-  constexpr int kCarry = S, kTaken = S + 1;  // segment slots after the round's own
+  constexpr int kCarry = S, kTaken = S + 1;  // segment slots after the pass's own
   extern __shared__ __align__(128) unsigned char pipe_smem[];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
   const uint32_t gchunk = blockIdx.x * kPipeWarps + wib;
@@ -1605,7 +1605,7 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
   const RowCtx ctx = make_ctx(td);
   const int dim = ctx.dim;
   const int vec_per_row = dim >> 2;
-  unsigned char* aux = pipe_smem + (size_t)wib * lane_groups_warp_bytes(NG, ROUNDS, REDUCE);
+  unsigned char* aux = pipe_smem + (size_t)wib * lane_groups_warp_bytes(NG, PASSES, REDUCE);
   const float** ent_addr = reinterpret_cast<const float**>(aux);              // [32]
   float* ent_gain = reinterpret_cast<float*>(aux + 32 * 8);                   // [32]
   uint32_t* item_desc = reinterpret_cast<uint32_t*>(aux + 32 * 12);           // [32] runs to apply, [2] runs that cross
@@ -1703,9 +1703,9 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
   const int ncross = __popc(crossmask);
 
 #pragma unroll
-  for (int h = 0; h < ROUNDS; ++h) {
-    const int lane0 = h * S;                                         // first entry of the round
-    const int segbase = __popc(seglast_mask & lanes_below(lane0));   // segments of earlier rounds
+  for (int h = 0; h < PASSES; ++h) {
+    const int lane0 = h * S;                                         // first entry of the pass
+    const int segbase = __popc(seglast_mask & lanes_below(lane0));   // segments of earlier passes
     if (h > 0 && (listedmask >> lane0) == 0) break;                  // no entries left
     // ---- reduce: this lane's vector of the window's gradient rows, summed segment by segment
     {
@@ -1731,7 +1731,7 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
       }
     }
     // ---- the entries taken over from the next chunk (they continue the chunk's last run): a contiguous share per group
-    if (h == ROUNDS - 1 && border.ext > 0) {
+    if (h == PASSES - 1 && border.ext > 0) {
       const int per = (border.ext + NG - 1) / NG;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
       for (int i = 0; i < per; i += 2) {
@@ -1756,11 +1756,11 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
       }
       if (in_row) store_slot(kTaken + my_group, acc);
     }
-    __syncwarp();  // the round's segment sums are in shared memory
-    // Sum of a run whose segments up to `last` lie in this round or earlier ones (this lane's vector).
+    __syncwarp();  // the pass's segment sums are in shared memory
+    // Sum of a run whose segments up to `last` lie in this pass or earlier ones (this lane's vector).
     auto run_sum = [&](int first, int last, bool taken) {
       float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (ROUNDS > 1 && first < segbase) {
+      if (PASSES > 1 && first < segbase) {
         g = load_slot(kCarry);
         first = segbase;
       }
@@ -1781,14 +1781,14 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
       return g;
     };
     auto item_sum = [&](uint32_t item) { return run_sum((int)(item & 31u), (int)((item >> 8) & 31u), (item >> 25) & 1u); };
-    // ---- runs that cross the chunk and end in this round: their sums are the chunk's partial sums
+    // ---- runs that cross the chunk and end in this pass: their sums are the chunk's partial sums
     for (int k = 0; k < ncross; ++k) {
       const uint32_t item = item_desc[32 + k];
       const int end_lane = (int)(item >> 26);
       if (end_lane >= lane0 && end_lane < lane0 + S && my_group == k % NG && in_row)
         reinterpret_cast<float4*>(partial + ((int64_t)2 * gchunk + ((item >> 24) & 1u)) * pstride)[gl] = item_sum(item);
     }
-    // ---- the owned runs that end in this round
+    // ---- the owned runs that end in this pass
     const int a_begin = __popc(wendmask & lanes_below(lane0)), a_end = __popc(wendmask & lanes_below(lane0 + S));
     if (REDUCE) {
       // reduce-only: the sums go to the exchange buffer
@@ -1831,9 +1831,9 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
         }
       }
     }
-    if (h + 1 < ROUNDS) {
-      // ---- a run that goes on in the next round: its sum so far becomes the carry
-      __syncwarp();  // every group has read the old carry and the round's segments
+    if (h + 1 < PASSES) {
+      // ---- a run that goes on in the next pass: its sum so far becomes the carry
+      __syncwarp();  // every group has read the old carry and the pass's segments
       const int jl = lane0 + S - 1;
       if (((listedmask >> jl) & 1u) && !((endmask >> jl) & 1u)) {  // warp-uniform
         const int rs = __shfl_sync(0xffffffffu, run_start, jl);
@@ -1841,7 +1841,7 @@ __global__ void __launch_bounds__(kPipeBlock, 8) bwd_lane_groups_kernel(const Ta
         __syncwarp();
         if (my_group == 0 && in_row) store_slot(kCarry, g);
       }
-      __syncwarp();  // the next round overwrites the segment slots
+      __syncwarp();  // the next pass overwrites the segment slots
     }
   }
 }
@@ -2494,12 +2494,12 @@ int launch_bwd_pipe(const TableDesc* tabs, int count, uint32_t total_chunks, con
   return launch_fixup<4, K32>(tabs, count, total_chunks, u, extra, st);
 }
 
-template <int NG, int ROUNDS, int NS, bool REDUCE = false, bool EXTRA = false>
+template <int NG, int PASSES, int NS, bool REDUCE = false, bool EXTRA = false>
 int launch_lane_groups_ns(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, cudaStream_t st) {
-  const size_t smem = (size_t)kPipeWarps * lane_groups_warp_bytes(NG, ROUNDS, REDUCE);
-  if (int rc = configure_smem<bwd_lane_groups_kernel<NG, ROUNDS, NS, REDUCE, EXTRA>>(smem)) return rc;
+  const size_t smem = (size_t)kPipeWarps * lane_groups_warp_bytes(NG, PASSES, REDUCE);
+  if (int rc = configure_smem<bwd_lane_groups_kernel<NG, PASSES, NS, REDUCE, EXTRA>>(smem)) return rc;
   const unsigned blocks = (unsigned)ceil_div(total_chunks, kPipeWarps);
-  bwd_lane_groups_kernel<NG, ROUNDS, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
+  bwd_lane_groups_kernel<NG, PASSES, NS, REDUCE, EXTRA><<<blocks, kPipeBlock, smem, st>>>(tabs, count, total_chunks, u.partial, u.flags, u.pstride);
   SC_LAUNCH_OK("bwd_lane_groups_kernel");
   return SC_OK;
 }
@@ -2508,13 +2508,13 @@ int launch_lane_groups_ns(const TableDesc* tabs, int count, uint32_t total_chunk
 template <int NG>
 int launch_bwd_lane_groups(const TableDesc* tabs, int count, uint32_t total_chunks, const UpdateScratch& u, int num_slots,
                            bool extra, cudaStream_t st) {
-  constexpr int ROUNDS = 4 / NG;
+  constexpr int PASSES = 4 / NG;
   int rc;
-  if (num_slots == kReduceOnly) rc = launch_lane_groups_ns<NG, ROUNDS, 0, true>(tabs, count, total_chunks, u, st);
-  else if (num_slots == 0) rc = launch_lane_groups_ns<NG, ROUNDS, 0>(tabs, count, total_chunks, u, st);
-  else if (num_slots == 1) rc = launch_lane_groups_ns<NG, ROUNDS, 1>(tabs, count, total_chunks, u, st);
-  else if (!extra) rc = launch_lane_groups_ns<NG, ROUNDS, 2>(tabs, count, total_chunks, u, st);
-  else rc = launch_lane_groups_ns<NG, ROUNDS, 2, false, true>(tabs, count, total_chunks, u, st);
+  if (num_slots == kReduceOnly) rc = launch_lane_groups_ns<NG, PASSES, 0, true>(tabs, count, total_chunks, u, st);
+  else if (num_slots == 0) rc = launch_lane_groups_ns<NG, PASSES, 0>(tabs, count, total_chunks, u, st);
+  else if (num_slots == 1) rc = launch_lane_groups_ns<NG, PASSES, 1>(tabs, count, total_chunks, u, st);
+  else if (!extra) rc = launch_lane_groups_ns<NG, PASSES, 2>(tabs, count, total_chunks, u, st);
+  else rc = launch_lane_groups_ns<NG, PASSES, 2, false, true>(tabs, count, total_chunks, u, st);
   if (rc != SC_OK) return rc;
   return launch_fixup<4, 1>(tabs, count, total_chunks, u, extra, st);
 }
