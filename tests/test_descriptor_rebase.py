@@ -105,3 +105,31 @@ def test_replayed_descriptors_follow_the_buffers_of_each_batch():
     np.testing.assert_array_equal(var[name].table.cpu().numpy(), ref_var[name].table.cpu().numpy())
     np.testing.assert_array_equal(var[name].slot[0].cpu().numpy(), ref_var[name].slot[0].cpu().numpy())
   del rng
+
+
+def test_csr_key_separates_layout_from_buffer_addresses():
+  """Two outputs of one layout share the cache key and differ in `bases`; a replaced array drops the token."""
+  from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+  from jax_tpu_embedding.sparsecore.lib.nn import embedding
+
+  layout = object()
+
+  def output(ibase, fbase):
+    dicts = []
+    for i in range(4):
+      d = pip.BufferDict({"t": np.zeros(4)})
+      d.token = (ibase, fbase, layout, False, i)
+      dicts.append(d)
+    return dicts
+
+  a, b = output(1 << 40, 2 << 40), output(3 << 40, 4 << 40)
+  key_a, bases_a = embedding._csr_key(*a, ["t"])  # pylint: disable=protected-access
+  key_b, bases_b = embedding._csr_key(*b, ["t"])  # pylint: disable=protected-access
+  assert key_a == key_b and bases_a == (1 << 40, 2 << 40) and bases_b == (3 << 40, 4 << 40)
+  # Dicts of two different outputs mixed in one call: no common pair of buffers, the full tokens key the cache.
+  mixed_key, mixed_bases = embedding._csr_key(a[0], b[1], a[2], a[3], ["t"])  # pylint: disable=protected-access
+  assert mixed_bases is None and mixed_key != key_a
+  # Replacing an array drops the token: the dict is described by its arrays (here: not device tensors -> no caching).
+  a[1]["t"] = np.ones(4)
+  assert a[1].token is None
+  assert embedding._csr_key(*a, ["t"]) == (None, None)  # pylint: disable=protected-access
