@@ -15,6 +15,9 @@
 3. optimizer_known_answers.npz - one weighted multi-hot batch updated by Adam (textbook form with
    bias-corrected moments) and by AdagradMomentum / FTRL / LaProp / F2A, in float64, from the
    formulas of the reference's primitive tests (cited at known_answer_optimizer_cases).
+4. python_preprocessing_reference.npz - outputs of the reference's pure-Python single-feature
+   preprocessing (lib/core/input_preprocessing.py, imported with numpy standing in for jax.numpy)
+   on seeded random ragged batches: the four arrays in full, padding included.
 """
 
 from __future__ import annotations
@@ -98,6 +101,59 @@ def record_reference_preprocessing(reference_root):
     manifest["calls"].append(m)
   fio.save(os.path.join(HERE, "preprocess_reference.npz"), manifest, arrays)
   print(f"preprocess_reference.npz: {len(calls)} calls from {result.testsRun} reference tests")
+
+
+def record_python_preprocessing(reference_root):
+  """Runs the reference's pure-Python preprocessing on seeded random inputs and stores inputs and outputs."""
+  import importlib.util
+  import types
+
+  # numpy stands in for jax.numpy; the module's own imports (constants, utils) resolve to this repository's package,
+  # which mirrors them.
+  saved = {k: sys.modules.get(k) for k in ("jax", "jax.numpy", "jax.sharding")}
+  jax = types.ModuleType("jax")
+  jnp = types.ModuleType("jax.numpy")
+  jnp.asarray, jnp.ndarray, jnp.int32, jnp.float32 = np.asarray, np.ndarray, np.int32, np.float32
+  sharding = types.ModuleType("jax.sharding")
+  sharding.Mesh = object
+  jax.numpy, jax.sharding = jnp, sharding
+  sys.modules.update({"jax": jax, "jax.numpy": jnp, "jax.sharding": sharding})
+  try:
+    path = os.path.join(reference_root, "jax_tpu_embedding/sparsecore/lib/core/input_preprocessing.py")
+    spec = importlib.util.spec_from_file_location("reference_python_preprocessing", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+  finally:
+    for k, v in saved.items():
+      if v is None:
+        sys.modules.pop(k, None)
+      else:
+        sys.modules[k] = v
+
+  class Mesh:
+    def __init__(self, n):
+      self.devices = list(range(n))
+
+  rng = np.random.default_rng(20240611)
+  manifest, arrays = dict(source="lib/core/input_preprocessing.py", cases=[]), {}
+  for i in range(24):
+    c, s = int(rng.choice([1, 2, 4])), int(rng.choice([1, 2, 4]))
+    batch = s * int(rng.integers(1, 9))
+    vocab = int(rng.choice([16, 64, 1000, 100000]))
+    rows = [rng.integers(0, vocab, size=rng.integers(0, 7)).astype(np.int32) for _ in range(batch)]
+    # Power-of-two weights: the reference sums the gains of duplicate ids in double, the kernels in float.
+    weights = [rng.choice([0.5, 1.0, 2.0, 0.25], size=len(r)).astype(np.float32) for r in rows]
+    rp, ids, sids, gains = ref.preprocess_sparse_dense_matmul_input(
+        rows, weights, Mesh(c), max_ids_per_partition=64, max_unique_ids_per_partition=64, num_sc_per_device=s)
+    manifest["cases"].append(dict(devices=c, num_sc_per_device=s, max_ids_per_partition=64,
+                                  max_unique_ids_per_partition=64))
+    arrays[f"p{i}_ids"] = np.concatenate(rows) if rows else np.zeros(0, np.int32)
+    arrays[f"p{i}_w"] = np.concatenate(weights) if weights else np.zeros(0, np.float32)
+    arrays[f"p{i}_len"] = np.asarray([len(r) for r in rows], np.int64)
+    arrays[f"p{i}_rp"], arrays[f"p{i}_eids"] = np.asarray(rp, np.int32), np.asarray(ids, np.int32)
+    arrays[f"p{i}_sids"], arrays[f"p{i}_gains"] = np.asarray(sids, np.int32), np.asarray(gains, np.float32)
+  fio.save(os.path.join(HERE, "python_preprocessing_reference.npz"), manifest, arrays)
+  print(f"python_preprocessing_reference.npz: {len(manifest['cases'])} cases")
 
 
 def known_answer_lookup_cases():
@@ -246,3 +302,4 @@ if __name__ == "__main__":
   known_answer_lookup_cases()
   known_answer_optimizer_cases()
   record_reference_preprocessing(args.reference)
+  record_python_preprocessing(args.reference)
