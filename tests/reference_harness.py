@@ -67,6 +67,32 @@ def load_pybind_test_module(backend):
                os.path.join(_CORE_TESTS, "pybind_input_preprocessing_test.py"))
 
 
+class _StubMesh:
+  """Stands in for jax.sharding.Mesh: the tested module reads `devices` only."""
+
+  def __init__(self, devices, axis_names=None):
+    import numpy as np
+
+    self.devices = np.asarray(devices, dtype=object)
+    self.axis_names = axis_names
+
+
+def load_python_preprocessing_test_module(backend):
+  """Imports the reference's input_preprocessing_test (tests of its pure-Python single-feature module) so that
+  `lib.core.input_preprocessing` of this repository is what it exercises, with `backend` as the preprocessor
+  behind the product's binding module."""
+  from absl import flags
+  from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+
+  if not flags.FLAGS.is_parsed():
+    flags.FLAGS(["reference_harness"])
+  pip.preprocess_sparse_dense_matmul_input = backend
+  if "jax" not in sys.modules:
+    jax = _stub("jax")
+    jax.sharding = _stub("jax.sharding", Mesh=_StubMesh)
+  return _load("reference_input_preprocessing_test", os.path.join(_CORE_TESTS, "input_preprocessing_test.py"))
+
+
 def set_reference_root(root: str) -> None:
   global REFERENCE, _CORE_TESTS
   REFERENCE = root

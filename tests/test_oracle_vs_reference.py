@@ -6,6 +6,8 @@
    product's Python interface.
 2. The oracle is compared with the reference's pure-Python preprocessing
    (lib/core/input_preprocessing.py) on random single-feature inputs.
+3. The reference's unit tests of that pure-Python module run against this repository's module of
+   the same name (oracle as the backend).
 Both need the reference checkout and are skipped where it is not mounted; the committed
 fixtures under tests/golden/ carry the same pin to machines without it.
 """
@@ -33,6 +35,24 @@ def test_reference_unit_tests_pass_on_oracle(reference_root):
   finally:
     pip.preprocess_sparse_dense_matmul_input = original
   assert result.testsRun >= 30
+  problems = [str(t) + "\n" + tb for t, tb in result.failures + result.errors]
+  assert not problems, "\n".join(problems)[:4000]
+
+
+def test_reference_tests_of_its_python_module_pass_on_this_module(reference_root):
+  """lib/core/tests/input_preprocessing_test.py (hand-written expected buffers for one and several id columns,
+  error cases) exercises `lib.core.input_preprocessing` of this repository, with the oracle behind the binding
+  module.  The minibatching test class is skipped: minibatching is not built."""
+  import reference_harness as rh
+  from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+
+  original = pip.preprocess_sparse_dense_matmul_input
+  try:
+    module = rh.load_python_preprocessing_test_module(ob.oracle_preprocess)
+    result = rh.run_cases(module, skip_classes=("InputPreprocessingMinibatchingTest",))
+  finally:
+    pip.preprocess_sparse_dense_matmul_input = original
+  assert result.testsRun >= 7
   problems = [str(t) + "\n" + tb for t, tb in result.failures + result.errors]
   assert not problems, "\n".join(problems)[:4000]
 
