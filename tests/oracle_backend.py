@@ -32,7 +32,14 @@ def oracle_preprocess(features, feature_weights, feature_specs, local_device_cou
     feats = []
     for idx, spec in members:
       w = None if feature_weights is None else feature_weights[idx]
-      f_ids, f_off, f_w = po.flatten_feature(features[idx], w)
+      feature = features[idx]
+      if isinstance(feature, pip.RaggedInput):  # flat values + row splits (what the sparse-COO front end builds)
+        splits = np.asarray(feature.row_splits).reshape(-1)
+        values = np.asarray(feature.values)
+        if feature.weights is not None:
+          w = [np.asarray(feature.weights)[a:b] for a, b in zip(splits[:-1], splits[1:])]
+        feature = [values[a:b] for a, b in zip(splits[:-1], splits[1:])]
+      f_ids, f_off, f_w = po.flatten_feature(feature, w)
       row_offset, col_offset, col_shift = pip._transform(spec)  # pylint: disable=protected-access
       feats.append(po.FeatureInput(f_ids, f_off, f_w, row_offset, col_offset, col_shift))
     out = po.preprocess_table(

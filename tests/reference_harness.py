@@ -67,6 +67,14 @@ def load_pybind_test_module(backend):
                os.path.join(_CORE_TESTS, "pybind_input_preprocessing_test.py"))
 
 
+def load_sparse_coo_test_module(backend):
+  """Imports the reference's sparse_coo_input_preprocessing_test: it calls the product's sparse-COO front end, which
+  builds row splits on the host and hands them to `backend` through the binding module."""
+  load_pybind_test_module(backend)  # same stubs and test_utils
+  return _load("reference_sparse_coo_input_preprocessing_test",
+               os.path.join(_CORE_TESTS, "sparse_coo_input_preprocessing_test.py"))
+
+
 class _StubMesh:
   """Stands in for jax.sharding.Mesh: the tested module reads `devices` only."""
 

@@ -8,6 +8,8 @@
    (lib/core/input_preprocessing.py) on random single-feature inputs.
 3. The reference's unit tests of that pure-Python module run against this repository's module of
    the same name (oracle as the backend).
+4. The reference's unit tests of the sparse-COO input run against the product's sparse-COO front end
+   (oracle as the backend).
 Both need the reference checkout and are skipped where it is not mounted; the committed
 fixtures under tests/golden/ carry the same pin to machines without it.
 """
@@ -35,6 +37,24 @@ def test_reference_unit_tests_pass_on_oracle(reference_root):
   finally:
     pip.preprocess_sparse_dense_matmul_input = original
   assert result.testsRun >= 30
+  problems = [str(t) + "\n" + tb for t, tb in result.failures + result.errors]
+  assert not problems, "\n".join(problems)[:4000]
+
+
+def test_reference_sparse_coo_tests_pass_on_this_front_end(reference_root):
+  """lib/core/tests/sparse_coo_input_preprocessing_test.py (16 cases with hand-written buffers: empty rows, column
+  transformations, feature and table stacking on one and several chips) against the product's sparse-COO front end
+  (`preprocess_sparse_dense_matmul_sparse_coo_input`), with the oracle behind it."""
+  import reference_harness as rh
+  from jax_tpu_embedding.sparsecore.lib.core import pybind_input_preprocessing as pip
+
+  original = pip.preprocess_sparse_dense_matmul_input
+  try:
+    module = rh.load_sparse_coo_test_module(ob.oracle_preprocess)
+    result = rh.run_cases(module)
+  finally:
+    pip.preprocess_sparse_dense_matmul_input = original
+  assert result.testsRun >= 16
   problems = [str(t) + "\n" + tb for t, tb in result.failures + result.errors]
   assert not problems, "\n".join(problems)[:4000]
 
