@@ -75,6 +75,27 @@ def load_sparse_coo_test_module(backend):
                os.path.join(_CORE_TESTS, "sparse_coo_input_preprocessing_test.py"))
 
 
+def load_fdo_test_module(name: str):
+  """Imports the reference's `lib/fdo/<name>.py` test module; it exercises this repository's FDO clients.
+  `etils.epath.Path` is pathlib's Path where etils is not installed."""
+  import pathlib
+
+  from absl import flags
+
+  if not flags.FLAGS.is_parsed():
+    flags.FLAGS(["reference_harness"])
+  try:
+    import etils.epath  # noqa: F401  pylint: disable=unused-import,g-import-not-at-top
+  except ImportError:
+    etils = _stub("etils")
+    etils.epath = _stub("etils.epath", Path=pathlib.Path)
+  for stale in ("jax_tpu_embedding.sparsecore.lib.fdo", "jax_tpu_embedding.sparsecore.lib.fdo.file_fdo_client"):
+    mod = sys.modules.get(stale)
+    if mod is not None and getattr(mod, "__file__", None) is None:  # a stub left by load_pybind_test_module
+      del sys.modules[stale]
+  return _load("reference_" + name, os.path.join(REFERENCE, "jax_tpu_embedding/sparsecore/lib/fdo", name + ".py"))
+
+
 class _StubMesh:
   """Stands in for jax.sharding.Mesh: the tested module reads `devices` only."""
 

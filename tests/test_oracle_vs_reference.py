@@ -10,6 +10,7 @@
    the same name (oracle as the backend).
 4. The reference's unit tests of the sparse-COO input run against the product's sparse-COO front end
    (oracle as the backend).
+5. The reference's unit tests of its FDO clients run against the FDO clients of this repository.
 Both need the reference checkout and are skipped where it is not mounted; the committed
 fixtures under tests/golden/ carry the same pin to machines without it.
 """
@@ -37,6 +38,17 @@ def test_reference_unit_tests_pass_on_oracle(reference_root):
   finally:
     pip.preprocess_sparse_dense_matmul_input = original
   assert result.testsRun >= 30
+  problems = [str(t) + "\n" + tb for t, tb in result.failures + result.errors]
+  assert not problems, "\n".join(problems)[:4000]
+
+
+@pytest.mark.parametrize("name,count", [("file_fdo_client_test", 5), ("csv_file_fdo_client_test", 6)])
+def test_reference_fdo_client_tests_pass_on_these_clients(reference_root, name, count):
+  """lib/fdo/file_fdo_client_test.py and csv_file_fdo_client_test.py against `lib/fdo` of this repository."""
+  import reference_harness as rh
+
+  result = rh.run_cases(rh.load_fdo_test_module(name))
+  assert result.testsRun >= count
   problems = [str(t) + "\n" + tb for t, tb in result.failures + result.errors]
   assert not problems, "\n".join(problems)[:4000]
 
